@@ -1,0 +1,10 @@
+"""glassbox_b200: a small, whole inference engine for one B200, for the Llama-family decoder
+that Glassbox runs (SmolLM2). See DESIGN.md at the repository root."""
+from . import models  # noqa: F401  (registers the architectures)
+from . import parts  # noqa: F401   (registers the parts)
+from .config import ConfigError, load_config, parse_config, register_architecture
+from .weights import WeightsError, write_random_model
+
+__version__ = "0.1.0"
+__all__ = ["ConfigError", "WeightsError", "load_config", "parse_config", "register_architecture",
+           "write_random_model"]

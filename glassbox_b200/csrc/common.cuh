@@ -1,0 +1,57 @@
+// Shared declarations for the kernel library: element types, error reporting, small helpers.
+//
+// Every exported function is `extern "C"`, takes raw device pointers plus a CUDA stream, and
+// returns 0 on success. On failure it returns a non-zero code and leaves a message that
+// `gb_last_error()` returns; nothing is printed and nothing traps. Kernels never assert: a bad
+// index (token id, cache slot) is recorded in a caller-supplied status word and the access is
+// skipped, so a faulty batch cannot fault the GPU.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define GB_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum GbDtype : int { GB_F32 = 0, GB_BF16 = 1 };
+
+// Bits of the device status word.
+enum GbStatusBits : int {
+    GB_STATUS_BAD_TOKEN = 1,      // a token id outside the vocabulary
+    GB_STATUS_BAD_SLOT = 2,       // a cache slot or page id outside the pool
+    GB_STATUS_BAD_POSITION = 4,   // a position outside the rotary table
+    GB_STATUS_WAIT_TIMEOUT = 8,   // a bounded wait inside a kernel gave up
+};
+
+void gb_set_error(const char* fmt, ...);
+int gb_check_launch(const char* what);
+
+#define GB_REQUIRE(cond, ...)                 \
+    do {                                      \
+        if (!(cond)) {                        \
+            gb_set_error(__VA_ARGS__);        \
+            return 1;                         \
+        }                                     \
+    } while (0)
+
+__device__ __forceinline__ float gb_to_float(float v) { return v; }
+__device__ __forceinline__ float gb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T gb_from_float(float v);
+template <> __device__ __forceinline__ float gb_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 gb_from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float gb_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float gb_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+static inline int gb_ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }

@@ -1,0 +1,95 @@
+// Next-token choice on the device: greedy argmax and temperature sampling, one block per row.
+//
+// Greedy: the first maximum wins (crates/glassbox-core/src/sampler.rs:49-57).
+// Temperature: logits are divided by the temperature, soft-maxed with the maximum subtracted
+// (sampler.rs:113-125) and the token is drawn by walking the cumulative sum until it passes
+// r * sum, with r in [0, 1) supplied per row by the host's xorshift64* generator
+// (sampler.rs:150-164). The walk goes in token-id order; Glassbox walks candidates sorted by
+// probability, which gives the same distribution but another token for the same r.
+// Every reduction has a fixed shape (thread t owns a contiguous run of the vocabulary, then a
+// serial scan over the threads' sums), so a row's result never depends on the other rows.
+#include "common.cuh"
+
+#include <float.h>
+
+constexpr int SAMPLE_THREADS = 512;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ logits, long long stride,
+                                                                const float* __restrict__ temperature,
+                                                                const float* __restrict__ uniform,
+                                                                int* __restrict__ out, int vocab) {
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* l = logits + (size_t)row * stride;
+    const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int lo = min(tid * chunk, vocab), hi = min(lo + chunk, vocab);
+    __shared__ float s_val[SAMPLE_THREADS];
+    __shared__ int s_idx[SAMPLE_THREADS];
+    __shared__ float s_pref[SAMPLE_THREADS + 1];
+
+    // Maximum and its first index. Threads own ascending runs, so "lowest thread wins ties" is
+    // "first index wins".
+    float best = -FLT_MAX;
+    int best_i = vocab;
+    for (int i = lo; i < hi; ++i) {
+        float v = l[i];
+        if (best_i == vocab || v > best) { best = v; best_i = i; }
+    }
+    s_val[tid] = best;
+    s_idx[tid] = best_i;
+    __syncthreads();
+    for (int s = SAMPLE_THREADS / 2; s > 0; s >>= 1) {
+        if (tid < s) {
+            float ov = s_val[tid + s];
+            int oi = s_idx[tid + s];
+            const int ci = s_idx[tid];
+            if (oi < vocab && (ci == vocab || ov > s_val[tid] || (ov == s_val[tid] && oi < ci))) {  // ties: lower index
+                s_val[tid] = ov;
+                s_idx[tid] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    const float vmax = s_val[0];
+    const int imax = s_idx[0];
+    const float temp = temperature ? temperature[row] : 0.f;
+    if (!(temp > 0.f)) {
+        if (tid == 0) out[row] = imax;
+        return;
+    }
+    __syncthreads();
+    const float mscaled = vmax / temp;
+    float part = 0.f;
+    for (int i = lo; i < hi; ++i) part += expf(l[i] / temp - mscaled);
+    s_val[tid] = part;
+    __syncthreads();
+    if (tid == 0) {
+        float run = 0.f;
+        for (int t = 0; t < SAMPLE_THREADS; ++t) {
+            s_pref[t] = run;
+            run += s_val[t];
+        }
+        s_pref[SAMPLE_THREADS] = run;
+        out[row] = max(vocab - 1, 0);  // fallback: the last token, as sampler.rs:163
+    }
+    __syncthreads();
+    const float target = uniform[row] * s_pref[SAMPLE_THREADS];
+    // Exactly one thread's half-open interval [pref, pref + part) holds the target (if any does).
+    if (lo < hi && target >= s_pref[tid] && target < s_pref[tid + 1]) {
+        float run = s_pref[tid];
+        int pick = hi - 1;
+        for (int i = lo; i < hi; ++i) {
+            run += expf(l[i] / temp - mscaled);
+            if (target < run) { pick = i; break; }
+        }
+        out[row] = pick;
+    }
+}
+
+GB_EXPORT int gb_sample(const float* logits, long long stride, const float* temperature, const float* uniform,
+                        int* out, int rows, int vocab, cudaStream_t stream) {
+    GB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "gb_sample: bad sizes rows=%d vocab=%d", rows, vocab);
+    GB_REQUIRE(temperature == nullptr || uniform != nullptr, "gb_sample: temperature sampling needs uniform draws");
+    if (rows == 0) return 0;
+    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, temperature, uniform, out, vocab);
+    return gb_check_launch("gb_sample");
+}

@@ -1,0 +1,83 @@
+"""What one step hands to the parts: the rows of the batch, where each row's keys go, and scratch.
+
+Rows are flat: row i is token ``tokens[i]`` of sequence ``row_seq[i]`` (an index into this
+step's sequence list) at position ``positions[i]``; rows of one sequence are consecutive and in
+order (crates/glassbox-core/src/model.rs:203-215). For every paged cache group the context
+carries the block table of each sequence of the step and the cache slot of each row.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..cache.device import DeviceCache, PagedLayerView, StateLayerView
+
+
+@dataclass
+class SeqInfo:
+    request: object      # the caller's request id
+    slot: int            # state slot of the request
+    start_pos: int       # position of its first row in this step
+    n_rows: int
+    first_row: int
+
+
+class Scratch:
+    """Named activation buffers sized for the largest step, reused by every layer."""
+
+    def __init__(self, max_rows: int, dtype: torch.dtype, device):
+        self.max_rows, self.dtype, self.device = max_rows, dtype, device
+        self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def get(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
+        """A [rows, width] view of the buffer called ``name``. Buffers hold ``max_rows`` rows, except
+        with ``grow`` (used for logits, whose row count is the number of wanted rows and whose
+        width is the vocabulary): those hold what the largest request so far needed."""
+        dtype = dtype or self.dtype
+        rows, width = shape
+        if rows > self.max_rows:
+            raise ValueError(f"a step of {rows} rows exceeds the engine's max_batch_tokens {self.max_rows}")
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.shape[1] < width or buf.shape[0] < rows:
+            cap = self.max_rows
+            if grow:
+                cap = 1
+                while cap < rows:
+                    cap *= 2
+                cap = min(cap, self.max_rows)
+            buf = torch.empty((cap, width), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        if buf.shape[1] == width:
+            return buf[:rows]
+        return buf.view(-1)[:rows * width].view(rows, width)
+
+
+class StepContext:
+    def __init__(self, *, scratch: Scratch, cache: DeviceCache, status: torch.Tensor, dtype: torch.dtype):
+        self._scratch = scratch
+        self.cache = cache
+        self.status = status
+        self.dtype = dtype
+        self.device = status.device
+        self.n = 0
+        self.num_wanted = 0
+        self.seqs: List[SeqInfo] = []
+        self.tokens = self.positions = self.row_seq = self.want_rows = None
+        self.seq_first_row = self.seq_start_pos = self.seq_slots = None
+        self.group_slots: List[torch.Tensor] = []
+        self.group_tables: List[torch.Tensor] = []
+        self.max_rows_per_seq = 0
+        self.max_context = 0
+
+    def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
+        return self._scratch.get(name, shape, dtype, grow)
+
+    def cache_view(self, cache_layer: int):
+        view = self.cache.layer_view(cache_layer)
+        if isinstance(view, PagedLayerView):
+            view.slots = self.group_slots[view.group]
+            view.block_tables = self.group_tables[view.group]
+        return view

@@ -1,0 +1,94 @@
+"""The one model class: an embedding, layers built from parts, an execution order, a final norm
+and a head. Which architecture it is shows only in its ``ModelConfig``.
+
+Forward order follows crates/glassbox-core/src/model.rs:207-362: embed every row, run the layers
+(here: the entries of ``config.schedule``), then final norm and head on the wanted rows only.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..config.specs import ModelConfig
+from ..parts import Embedding, LmHead, build_block, build_part
+from ..parts.base import Part
+from ..weights.binding import ParamSpec
+
+
+def _collect(prefix: str, part: Part, out: Dict[str, ParamSpec], owners: Dict[str, tuple]) -> None:
+    for name, spec in part.param_specs().items():
+        out[f"{prefix}.{name}"] = spec
+        owners[f"{prefix}.{name}"] = (part, name)
+    for sub_name, sub in part.sub_parts().items():
+        _collect(f"{prefix}.{sub_name}", sub, out, owners)
+
+
+class DecoderModel:
+    def __init__(self, config: ModelConfig):
+        config.validate()
+        self.config = config
+        d = config.hidden_size
+        self.embed = Embedding(config.vocab_size, d)
+        self.layers = [build_block(spec, hidden_size=d) for spec in config.layers]
+        self.final_norm = build_part("norm", config.final_norm, hidden_size=d)
+        self.head = LmHead(config.vocab_size, d)
+        self._owners: Dict[str, tuple] = {}
+        self._specs: Dict[str, ParamSpec] = {}
+        _collect("embed", self.embed, self._specs, self._owners)
+        for i, layer in enumerate(self.layers):
+            _collect(f"layers.{i}", layer, self._specs, self._owners)
+        _collect("final_norm", self.final_norm, self._specs, self._owners)
+        _collect("head", self.head, self._specs, self._owners)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return dict(self._specs)
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        grouped: Dict[int, tuple] = {}
+        for path, tensor in params.items():
+            part, name = self._owners[path]
+            grouped.setdefault(id(part), (part, {}))[1][name] = tensor
+        for part, named in grouped.values():
+            part.bind(named)
+        self.params = dict(params)
+
+    def cache_layer_specs(self) -> List[object]:
+        """The cache spec of each cache layer: that of the mixer of the run that writes it."""
+        specs: List[object] = [None] * self.config.num_cache_layers
+        for run in self.config.schedule:
+            mixer = getattr(self.layers[run.layer], "mixer", None)
+            spec = mixer.cache_spec() if mixer is not None else None
+            if run.writes_cache:
+                specs[run.cache] = spec
+        for run in self.config.schedule:
+            if not run.writes_cache:
+                mixer = getattr(self.layers[run.layer], "mixer", None)
+                spec = mixer.cache_spec() if mixer is not None else None
+                if spec != specs[run.cache]:
+                    raise ValueError(f"a run of layer {run.layer} reads cache layer {run.cache}, whose writer keeps "
+                                     f"{specs[run.cache]!r}, but needs {spec!r}")
+        return specs
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for t in self.params.values():
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    def forward(self, ctx) -> torch.Tensor:
+        """Run the rows of ``ctx`` through the model; returns float32 logits [wanted rows, vocab]."""
+        n, d = ctx.n, self.config.hidden_size
+        x = ctx.scratch("x", (n, d), torch.float32)
+        self.embed.forward(ctx, ctx.tokens, x)
+        for run in self.config.schedule:
+            self.layers[run.layer].forward(ctx, x, ctx.cache_view(run.cache), run.writes_cache)
+        w = ctx.num_wanted
+        logits = ctx.scratch("logits", (w, self.config.vocab_size), torch.float32, grow=True)
+        if w:
+            hs = ctx.scratch("hs", (w, d))
+            self.final_norm.forward(ctx, x, hs, rows=ctx.want_rows)
+            self.head.forward(ctx, hs, logits)
+        return logits

@@ -1,0 +1,199 @@
+"""Python face of the CUDA kernel library (``csrc/``), loaded with ctypes.
+
+Every function takes torch tensors that already live on the GPU, passes their addresses and the
+current CUDA stream to an ``extern "C"`` launcher, and raises ``KernelError`` if the launcher
+refuses the sizes or the launch fails. There is no CPU implementation behind these functions and
+no library stand-in: if the shared library cannot be built or loaded, the first call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a cache slot or page id outside the pool",
+               4: "a position outside the rotary table", 8: "a bounded wait inside a kernel gave up"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_lock = threading.Lock()
+_c = ctypes
+_P, _I, _LL, _F = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float
+
+_SIGNATURES = {
+    "gb_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "gb_rmsnorm": [_P, _P, _P, _P, _I, _I, _I, _F, _P],
+    "gb_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _I, _P, _P],
+    "gb_swiglu": [_P, _P, _I, _I, _I, _P],
+    "gb_copy_pages": [_P, _P, _P, _I, _LL, _LL, _I, _P],
+    "gb_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _LL, _LL, _LL, _P],
+    "gb_attention_rows": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_sample": [_P, _LL, _P, _P, _P, _I, _I, _P],
+}
+
+
+def lib():
+    """The loaded shared library; builds it at first use."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = _build.ensure_built()
+            try:
+                handle = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from None
+            handle.gb_last_error.restype = ctypes.c_char_p
+            handle.gb_last_error.argtypes = []
+            for name, args in _SIGNATURES.items():
+                fn = getattr(handle, name, None)
+                if fn is None:
+                    raise KernelError(f"{path} does not export {name}; rebuild it (csrc/build.py --force)")
+                fn.argtypes = args
+                fn.restype = ctypes.c_int
+            _lib = handle
+    return _lib
+
+
+def loaded_library_path() -> Optional[str]:
+    return _build.library_path() if _lib is not None else None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _call(name: str, *args) -> None:
+    rc = getattr(lib(), name)(*args)
+    if rc != 0:
+        raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or f"{name} failed with code {rc}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported tensor dtype {t.dtype}") from None
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel operands must be CUDA tensors; there is no CPU path")
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Read the device status word (synchronises) and raise if a kernel recorded a bad index."""
+    bits = int(status.item())
+    if bits:
+        status.zero_()
+        what = [msg for bit, msg in STATUS_BITS.items() if bits & bit]
+        raise KernelError("a kernel skipped an access: " + "; ".join(what))
+
+
+# ------------------------------------------------------------------------------------------ ops
+def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
+    """x[i, :] = table[tokens[i], :] as float32."""
+    _cuda(table, tokens, x, status)
+    n, d = x.shape
+    assert tokens.dtype == torch.int32 and x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous()
+    _call("gb_embed", _ptr(table), _dt(table), _ptr(tokens), _ptr(x), n, d, table.shape[0], _ptr(status), _stream())
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = gain * x[rows[r] or r, :] / sqrt(mean(x^2) + eps); x and gain float32."""
+    _cuda(x, gain, out, rows)
+    assert x.dtype == torch.float32 and gain.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    n, d = out.shape
+    assert x.shape[1] == d and gain.numel() == d
+    _call("gb_rmsnorm", _ptr(x), _ptr(rows), _ptr(gain), _ptr(out), _dt(out), n, d, float(eps), _stream())
+
+
+def rope_kv_write(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], positions: torch.Tensor, slots: torch.Tensor,
+                  kcache: torch.Tensor, vcache: torch.Tensor, nh: int, nkv: int, hd: int, rot: int,
+                  page_size: int, write_kv: bool, status: torch.Tensor) -> None:
+    """Rotate q and k of each row at its position (in place) and store k, v at the row's slot.
+    kcache/vcache: [pages, nkv, page_size, hd]; cos_sin: float32 [max_pos, rot/2, 2]."""
+    _cuda(qkv, cos_sin, positions, slots, kcache, vcache, status)
+    n = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * hd
+    assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype and kcache.is_contiguous() and vcache.is_contiguous()
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    _call("gb_rope_kv_write", _ptr(qkv), _dt(qkv), _ptr(cos_sin), _ptr(positions), _ptr(slots), _ptr(kcache),
+          _ptr(vcache), n, nh, nkv, hd, rot if cos_sin is not None else 0, max_pos, page_size, kcache.shape[0],
+          1 if write_kv else 0, _ptr(status), _stream())
+
+
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    _cuda(gate_up, act)
+    n, inter = act.shape
+    assert gate_up.shape == (n, 2 * inter) and gate_up.dtype == act.dtype
+    assert gate_up.is_contiguous() and act.is_contiguous()
+    _call("gb_swiglu", _ptr(gate_up), _ptr(act), _dt(act), n, inter, _stream())
+
+
+def copy_pages(kcache: torch.Tensor, vcache: torch.Tensor, pairs: torch.Tensor) -> None:
+    """kcache/vcache: [layers, pages, ...]; pairs int32 [n, 2] of (source page, destination page)."""
+    _cuda(kcache, vcache, pairs)
+    layers = kcache.shape[0]
+    layer_bytes = kcache.stride(0) * kcache.element_size()
+    page_bytes = kcache.stride(1) * kcache.element_size()
+    _call("gb_copy_pages", _ptr(kcache), _ptr(vcache), _ptr(pairs), pairs.shape[0], page_bytes, layer_bytes, layers,
+          _stream())
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False) -> None:
+    """c[M, N] (+)= a[M, K] @ w[N, K]^T with float32 FMA on the CUDA cores (rows may be strided)."""
+    _cuda(a, w, c)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    _call("gb_gemm_simt", _ptr(a), _dt(a), _ptr(w), _dt(w), _ptr(c), _dt(c), 1 if accumulate else 0, M, N, K,
+          a.stride(0), w.stride(0), c.stride(0), _stream())
+
+
+def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes these operands."""
+    return False
+
+
+def attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                   block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int,
+                   hd: int, page_size: int, scale: float, window: Optional[int], status: torch.Tensor) -> None:
+    """One warp per (row, head): softmax(q k^T * scale) v over the row's visible keys."""
+    _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, status)
+    n = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == kcache.dtype
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    _call("gb_attention_rows", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _dt(q), _ptr(kcache), _ptr(vcache),
+          _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
+          kcache.shape[0], float(scale), int(window or 0), _ptr(status), _stream())
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           uniform: Optional[torch.Tensor] = None) -> None:
+    """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or no temperatures are given), else a
+    draw from softmax(logits[r] / temperature[r]) using uniform[r] in [0, 1)."""
+    _cuda(logits, out, temperature, uniform)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    _call("gb_sample", _ptr(logits), logits.stride(0), _ptr(temperature), _ptr(uniform), _ptr(out), rows, vocab,
+          _stream())

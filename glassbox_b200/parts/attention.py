@@ -1,0 +1,64 @@
+"""Causal grouped-query attention over the paged cache
+(crates/glassbox-core/src/model.rs:260-325).
+
+h -> qkv = h Wqkv^T (q, k, v stacked by rows) -> position encoding of q and k at each row's own
+position, k and v stored at the row's cache slot (all rows of the step before any attention)
+-> per (row, head) softmax(q k^T * scale) v over the row's visible keys of its own request
+-> residual += att Wo^T. No bias anywhere. With ``writes_cache`` False the keys and values of
+this run are not stored and attention reads what the named cache layer already holds.
+"""
+from __future__ import annotations
+
+from .. import kernels
+from ..weights.binding import ParamSpec
+from .base import Mixer, PagedKvSpec, build_part, register_part
+from .linear import linear
+
+
+class GqaAttention(Mixer):
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        s = spec
+        if s.num_heads % s.num_kv_heads:
+            raise ValueError(f"num_heads {s.num_heads} is not a multiple of num_kv_heads {s.num_kv_heads}")
+        if s.head_dim % 2 or s.head_dim > 256:
+            raise ValueError(f"head_dim {s.head_dim} must be even and at most 256")
+        if s.window is not None and s.window <= 0:
+            raise ValueError(f"window {s.window} must be positive")
+        self.hidden_size = hidden_size
+        self.nh, self.nkv, self.hd = s.num_heads, s.num_kv_heads, s.head_dim
+        self.qd, self.kvd = self.nh * self.hd, self.nkv * self.hd
+        self.position = build_part("position", s.position)
+
+    def sub_parts(self):
+        return {"position": self.position}
+
+    def param_specs(self):
+        d = self.hidden_size
+        return {"wqkv": ParamSpec((self.qd + 2 * self.kvd, d), pieces=(self.qd, self.kvd, self.kvd)),
+                "wo": ParamSpec((d, self.qd))}
+
+    def cache_spec(self):
+        return PagedKvSpec(self.nkv, self.hd, self.spec.window)
+
+    def forward(self, ctx, h, residual, cache, writes_cache: bool) -> None:
+        n = h.shape[0]
+        qkv = ctx.scratch("qkv", (n, self.qd + 2 * self.kvd))
+        linear(ctx, h, self.params["wqkv"], qkv)
+        table = self.position.fused_table(qkv.device)
+        if table is None:
+            self.position.apply_qk(ctx, qkv, self.nh, self.nkv, self.hd)
+        kernels.rope_kv_write(qkv, table, ctx.positions, cache.slots, cache.k, cache.v, self.nh, self.nkv, self.hd,
+                              self.position.rotary_dim, cache.page_size, writes_cache, ctx.status)
+        att = ctx.scratch("att", (n, self.qd))
+        self.attend(ctx, qkv[:, :self.qd], att, cache)
+        linear(ctx, att, self.params["wo"], residual, accumulate=True)
+
+
+    def attend(self, ctx, q, att, cache) -> None:
+        """att[row, head, :] = softmax over the row's visible keys; picks the kernel by batch shape."""
+        kernels.attention_rows(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.nh,
+                               self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window, ctx.status)
+
+
+register_part("mixer", "gqa_attention", GqaAttention, replace=True)

@@ -1,0 +1,121 @@
+"""Interfaces of the parts a layer is put together from, and the registry that builds them.
+
+A part is built from its spec alone (sizes and constants are the spec's fields), declares the
+parameters it needs, receives them once, and is then called with a ``StepContext`` that carries
+the batch. No part knows which model it sits in, which layer it is, or what its neighbours are.
+
+Interfaces (``ctx`` is ``glassbox_b200.engine.context.StepContext``):
+
+* Norm:      ``forward(ctx, x, out, rows=None)``: ``x`` float32 [n, d] residual stream, ``out``
+             [m, d] in the activation dtype; ``rows`` (int32 [m]) picks input rows.
+* Position:  ``fused_table(device)`` -> float32 [max_position, rotary_dim/2, 2] of (cos, sin) that
+             the attention mixer's fused kernel applies, or None; ``rotary_dim``;
+             ``apply_qk(ctx, qkv, num_heads, num_kv_heads, head_dim)`` for encodings that are
+             not a rotation table (runs before keys are stored).
+* Mixer:     ``cache_spec()`` -> ``PagedKvSpec`` | ``StateSpec`` | None;
+             ``forward(ctx, h, residual, cache, writes_cache)``: reads ``h`` [n, d] (activation
+             dtype), ADDS its output into ``residual`` (float32 [n, d]). ``cache`` is the view of
+             the cache layer the schedule assigned to this run.
+* FeedForward: ``forward(ctx, h, residual)``: same contract, no cache.
+
+Registering a new part: subclass the interface, give the spec dataclass a fresh ``kind`` string,
+and call ``register_part(role, kind, cls)``. Nothing else in the framework changes.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Optional, Tuple
+
+import torch
+
+from ..weights.binding import ParamSpec
+
+
+@dataclass(frozen=True)
+class PagedKvSpec:
+    """A mixer that keeps keys and values per token, in pages. Layers with equal specs share a
+    cache group (one block table, one page pool). ``window`` None keeps every token; an integer
+    keeps only the last ``window`` tokens, and pages behind the window are given back."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """A mixer that keeps a fixed-size state per request, in a slot: ``shape`` per request,
+    zeroed when the request is admitted, overwritten in place each step."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    def __init__(self, spec: Any):
+        self.spec = spec
+        self.params: Dict[str, torch.Tensor] = {}
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        """Receive the loaded parameters (keys are the local names of ``param_specs``)."""
+        self.params = dict(params)
+
+    def sub_parts(self) -> Dict[str, "Part"]:
+        """Parts this part owns (their parameters are loaded under ``<name>.``)."""
+        return {}
+
+
+class Norm(Part):
+    def forward(self, ctx, x, out, rows=None) -> None:
+        raise NotImplementedError
+
+
+class Position(Part):
+    rotary_dim: int = 0
+
+    def fused_table(self, device) -> Optional[torch.Tensor]:
+        return None
+
+    def apply_qk(self, ctx, qkv, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+        return None
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        return None
+
+    def forward(self, ctx, h, residual, cache, writes_cache: bool) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, h, residual) -> None:
+        raise NotImplementedError
+
+
+ROLES = ("norm", "position", "mixer", "ffn", "arrangement")
+_REGISTRY: Dict[str, Dict[str, Callable[..., Any]]] = {r: {} for r in ROLES}
+
+
+def register_part(role: str, kind: str, factory: Callable[..., Any], *, replace: bool = False) -> None:
+    """``factory(spec, hidden_size=...)`` builds the part for a spec whose ``kind`` is ``kind``."""
+    if role not in _REGISTRY:
+        raise ValueError(f"unknown part role {role!r}; roles: {', '.join(ROLES)}")
+    if kind in _REGISTRY[role] and not replace:
+        raise ValueError(f"{role} {kind!r} is already registered")
+    _REGISTRY[role][kind] = factory
+
+
+def build_part(role: str, spec: Any, **kwargs):
+    kind = getattr(spec, "kind", None) if not isinstance(spec, str) else spec
+    try:
+        factory = _REGISTRY[role][kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRY[role])) or "(none)"
+        raise ValueError(f"no {role} part registered for kind {kind!r}; registered: {known}") from None
+    return factory(spec, **kwargs)
+
+
+def registered(role: str):
+    return sorted(_REGISTRY[role])

@@ -1,0 +1,39 @@
+"""A layer: a mixer and a feed-forward wired around the float32 residual stream.
+
+"pre_norm" is x += mixer(norm(x)); x += ffn(norm(x)), with no norms after the parts
+(crates/glassbox-core/src/model.rs:251-348). The arrangement is looked up by name, so another
+wiring (post-norm, parallel branches) is another registered class.
+"""
+from __future__ import annotations
+
+from .base import Part, build_part, register_part
+
+
+class PreNormBlock(Part):
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        self.hidden_size = hidden_size
+        self.mixer_norm = build_part("norm", spec.mixer_norm, hidden_size=hidden_size)
+        self.mixer = build_part("mixer", spec.mixer, hidden_size=hidden_size)
+        self.ffn_norm = build_part("norm", spec.ffn_norm, hidden_size=hidden_size)
+        self.ffn = build_part("ffn", spec.ffn, hidden_size=hidden_size)
+
+    def sub_parts(self):
+        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn}
+
+    def forward(self, ctx, x, cache, writes_cache: bool) -> None:
+        n = x.shape[0]
+        h = ctx.scratch("h", (n, self.hidden_size))
+        self.mixer_norm.forward(ctx, x, h)
+        self.mixer.forward(ctx, h, x, cache, writes_cache)
+        self.ffn_norm.forward(ctx, x, h)
+        self.ffn.forward(ctx, h, x)
+
+
+register_part("arrangement", "pre_norm", lambda kind, *, layer_spec, hidden_size: PreNormBlock(layer_spec, hidden_size=hidden_size),
+              replace=True)
+
+
+def build_block(layer_spec, *, hidden_size: int):
+    """Build the layer that ``layer_spec.arrangement`` names."""
+    return build_part("arrangement", layer_spec.arrangement, layer_spec=layer_spec, hidden_size=hidden_size)
