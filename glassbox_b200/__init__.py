@@ -5,6 +5,14 @@ from . import parts  # noqa: F401   (registers the parts)
 from .config import ConfigError, load_config, parse_config, register_architecture
 from .weights import WeightsError, write_random_model
 
+
+
+def load(model_dir, dtype="bfloat16", **kwargs):
+    """Load a model folder for generation; see ``glassbox_b200.api.LLM``."""
+    from .api import load as _load
+    return _load(model_dir, dtype, **kwargs)
+
+
 __version__ = "0.1.0"
-__all__ = ["ConfigError", "WeightsError", "load_config", "parse_config", "register_architecture",
+__all__ = ["ConfigError", "WeightsError", "load", "load_config", "parse_config", "register_architecture",
            "write_random_model"]

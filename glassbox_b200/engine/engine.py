@@ -239,6 +239,36 @@ class Engine:
         self.steps += 1
         return logits
 
+    @property
+    def max_position(self) -> int:
+        return self.config.max_position
+
+    def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers, contexts) -> List[int]:
+        """Next token for ``logits[rows[i]]`` under ``samplers[i]``. Greedy and plain temperature
+        sampling run in the device kernel (the random number comes from the request's own
+        generator); requests with further filters are sampled on the host from a copy of the row."""
+        w = logits.shape[0]
+        temps = np.zeros(w, dtype=np.float32)
+        unif = np.zeros(w, dtype=np.float32)
+        host_rows = []
+        for r, s in zip(rows, samplers):
+            if s.config.needs_host:
+                host_rows.append(r)
+            elif not s.config.greedy:
+                temps[r] = s.config.temperature
+                unif[r] = s.uniform()
+        params = torch.from_numpy(np.stack([temps, unif])).to(self.device, non_blocking=True)
+        out = self.scratch.get("sampled", (w, 1), torch.int32, grow=True).view(-1)
+        kernels.sample(logits, out, params[0], params[1])
+        picked = out.cpu().numpy()
+        result = []
+        for r, s, ctx_tokens in zip(rows, samplers, contexts):
+            if s.config.needs_host:
+                result.append(s.sample(logits[r].cpu().numpy(), ctx_tokens))
+            else:
+                result.append(int(picked[r]))
+        return result
+
     def check(self) -> None:
         """Synchronise and raise if any kernel since the last check skipped a bad index."""
         kernels.check_status(self.status)

@@ -23,6 +23,34 @@ import sys
 import numpy as np
 
 
+class Replayer:
+    """Feeds trace steps to an engine. ``run_step`` returns the step's logits (a device tensor that
+    the next step overwrites) or None when nothing was wanted."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.live = set()
+
+    def run_step(self, rec: dict):
+        from .engine import StepEntry
+        entries = []
+        for e in rec.get("entries", []):
+            rid = e["id"]
+            if rid not in self.live:
+                self.engine.add_request(rid)
+                self.live.add(rid)
+            entries.append(StepEntry(rid, e["tokens"], e.get("want", [])))
+        logits = None
+        if entries:
+            out = self.engine.step(entries)
+            logits = out if out.shape[0] else None
+            self.engine.check()
+        for rid in rec.get("end", []):
+            self.engine.free_request(rid)
+            self.live.discard(rid)
+        return logits
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
@@ -35,7 +63,7 @@ def main(argv=None) -> int:
                     help="most tokens in one step (default: max-tokens)")
     args = ap.parse_args(argv)
 
-    from .engine import Engine, StepEntry
+    from .engine import Engine
     os.makedirs(args.out, exist_ok=True)
     if 64 % args.page_size:
         print(f"trace_run: --page-size {args.page_size} must divide 64", file=sys.stderr)
@@ -43,32 +71,20 @@ def main(argv=None) -> int:
     pool_tokens = -(-args.max_tokens // 64) * 64
     engine = Engine(args.model, args.dtype, cache_tokens=pool_tokens, page_size=args.page_size,
                     max_batch_tokens=args.max_batch_tokens or max(pool_tokens, 64), max_requests=8)
-    live = set()
+    replayer = Replayer(engine)
     for line in sys.stdin:
         line = line.strip()
         if not line:
             continue
         rec = json.loads(line)
         step = rec["step"]
-        entries = []
-        for e in rec.get("entries", []):
-            rid = e["id"]
-            if rid not in live:
-                engine.add_request(rid)
-                live.add(rid)
-            entries.append(StepEntry(rid, e["tokens"], e.get("want", [])))
-        if entries:
-            logits = engine.step(entries)
-            if logits.shape[0]:
-                arr = logits.detach().cpu().numpy().astype("<f4", copy=False)
-                tmp = os.path.join(args.out, f".{step}.f32.tmp")
-                with open(tmp, "wb") as f:
-                    f.write(np.ascontiguousarray(arr).tobytes())
-                os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
-            engine.check()
-        for rid in rec.get("end", []):
-            engine.free_request(rid)
-            live.discard(rid)
+        logits = replayer.run_step(rec)
+        if logits is not None:
+            arr = logits.detach().cpu().numpy().astype("<f4", copy=False)
+            tmp = os.path.join(args.out, f".{step}.f32.tmp")
+            with open(tmp, "wb") as f:
+                f.write(np.ascontiguousarray(arr).tobytes())
+            os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
         print(f"done {step}", flush=True)
     return 0
 

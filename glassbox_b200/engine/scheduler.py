@@ -1,0 +1,294 @@
+"""Continuous batching above the step function.
+
+Policy, after crates/glassbox-server/src/scheduler.rs:239-415:
+
+1. *Admit* from the head of the FIFO queue while fewer than ``max_seqs`` requests run. A fresh
+   request needs pages for its first portion (``min(len, token_budget)`` tokens) plus one; a
+   request that was preempted before waits until its whole context plus one page fits, so it
+   does not bounce. If that many pages are not free and something is running, admission stops;
+   an empty engine always admits one (scheduler.rs:257-277).
+2. *Plan* under the token budget: requests with one token to run (decoding) first, in running
+   order, then prompt portions of ``min(remaining, budget left)`` tokens (scheduler.rs:283-298).
+3. *Reserve* pages for each planned entry. **When pages run out** the most recently admitted
+   request is preempted: its pages are freed, it keeps its tokens and its sampler state, goes
+   back to the *front* of the queue and is recomputed later as one long prompt. If the request
+   that cannot fit is the only one running, it is finished with reason "length": it is too long
+   for the cache (scheduler.rs:301-330, 228-236).
+4. *Run* one step: rows of every planned entry, logits wanted at the last row of each entry that
+   reaches the end of its known tokens (scheduler.rs:336-352).
+5. *Sample* one token per wanted row; a stop token ends the request without being emitted;
+   ``max_tokens`` or ``max_position`` end it with "length" (scheduler.rs:370-404).
+6. *Finish*: pages and the state slot go back to the pool (scheduler.rs:405-410, 210-226).
+
+The scheduler talks to a *backend* (the ``Engine``, or a stand-in in tests) through:
+``cache`` (a ``CacheManager``), ``add_request``, ``free_request``, ``reserve``,
+``step(entries, reserve=False)``, ``sample(logits, samplers, contexts)`` and ``max_position``.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence
+
+from ..cache.manager import OutOfPages
+from ..sampling.sampler import Sampler, SamplerConfig
+
+STOP, LENGTH, ABORTED = "stop", "length", "aborted"
+
+
+@dataclass
+class SchedulerConfig:
+    token_budget: int = 256   # most tokens in one step (scheduler.rs:54-74)
+    max_seqs: int = 32        # most requests running at once
+
+
+@dataclass
+class Request:
+    prompt: Sequence[int]
+    max_tokens: int = 128
+    sampler: SamplerConfig = field(default_factory=SamplerConfig)
+    stop: Sequence[int] = ()
+    on_token: Optional[Callable[[int, int], None]] = None   # (request id, token)
+    on_done: Optional[Callable[[int, str], None]] = None    # (request id, reason)
+
+
+@dataclass
+class Metrics:
+    requests_finished: int = 0
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefix_hit_tokens: int = 0
+    preemptions: int = 0
+    steps: int = 0
+    batch_tokens: int = 0
+    ttft: List[float] = field(default_factory=list)
+    itl: List[float] = field(default_factory=list)
+
+
+class _Seq:
+    def __init__(self, sid: int, req: Request, now: float):
+        self.id = sid
+        self.req = req
+        self.tokens: List[int] = [int(t) for t in req.prompt]
+        self.prompt_len = len(self.tokens)
+        self.computed = 0
+        self.sampler = Sampler(req.sampler)
+        self.arrival = now
+        self.first_token: Optional[float] = None
+        self.last_token: Optional[float] = None
+        self.admitted_before = False
+
+    @property
+    def generated(self) -> int:
+        return len(self.tokens) - self.prompt_len
+
+
+@dataclass
+class Finished:
+    tokens: List[int]
+    reason: str
+    prompt_tokens: int
+
+
+class Scheduler:
+    def __init__(self, backend, config: Optional[SchedulerConfig] = None, trace: bool = False):
+        self.backend = backend
+        self.config = config or SchedulerConfig()
+        if self.config.token_budget <= 0 or self.config.max_seqs <= 0:
+            raise ValueError("token_budget and max_seqs must be positive")
+        self.waiting: Deque[_Seq] = deque()
+        self.running: List[_Seq] = []
+        self.next_id = 1
+        self.metrics = Metrics()
+        self.finished: Dict[int, Finished] = {}
+        self.trace: Optional[List[dict]] = [] if trace else None
+
+    # ------------------------------------------------------------------------------ requests
+    def submit(self, req: Request) -> int:
+        if not len(req.prompt):
+            raise ValueError("a request needs at least one prompt token")
+        sid = self.next_id
+        self.next_id += 1
+        self.metrics.prompt_tokens += len(req.prompt)
+        self.waiting.append(_Seq(sid, req, time.perf_counter()))
+        return sid
+
+    def is_idle(self) -> bool:
+        return not self.waiting and not self.running
+
+    def abort(self, sid: int) -> None:
+        """Stop a request wherever it is; what it holds goes back to the pool
+        (scheduler.rs:200-208)."""
+        for i, s in enumerate(self.running):
+            if s.id == sid:
+                del self.running[i]
+                self._finish(s, ABORTED)
+                return
+        for s in list(self.waiting):
+            if s.id == sid:
+                self.waiting.remove(s)
+                self._finish(s, ABORTED)
+                return
+
+    def _finish(self, s: _Seq, reason: str) -> None:
+        if self.backend.cache.has(s.id):
+            self.backend.free_request(s.id)
+        if reason != ABORTED:
+            self.metrics.requests_finished += 1
+            self.metrics.generated_tokens += s.generated
+            if s.first_token is not None:
+                self.metrics.ttft.append(s.first_token - s.arrival)
+        self.finished[s.id] = Finished(tokens=s.tokens[s.prompt_len:], reason=reason, prompt_tokens=s.prompt_len)
+        if s.req.on_done:
+            s.req.on_done(s.id, reason)
+
+    def _preempt_last(self) -> int:
+        s = self.running.pop()
+        self.backend.free_request(s.id)
+        s.computed = 0
+        self.metrics.preemptions += 1
+        self.waiting.appendleft(s)
+        return s.id
+
+    def _free_pages(self) -> int:
+        cache = self.backend.cache
+        return min(cache.free_pages(g) for g in range(len(cache.groups))) if cache.groups else 1 << 30
+
+    # ---------------------------------------------------------------------------------- step
+    def step(self) -> bool:
+        """One batch through the model. Returns False when there was nothing to do."""
+        t0 = time.perf_counter()
+        cfg, cache = self.config, self.backend.cache
+        preempted: List[int] = []
+        finished: List[int] = []
+
+        while len(self.running) < cfg.max_seqs and self.waiting:
+            s = self.waiting[0]
+            span = len(s.tokens) if s.admitted_before else min(len(s.tokens), cfg.token_budget)
+            need = cache.pages_needed(span) + 1
+            if self.running and (self._free_pages() < need or not cache.free_slots):
+                break
+            self.waiting.popleft()
+            reused = self.backend.add_request(s.id, s.tokens)
+            if not s.admitted_before:
+                self.metrics.prefix_hit_tokens += min(reused, s.prompt_len)
+            s.admitted_before = True
+            s.computed = reused
+            self.running.append(s)
+        if not self.running:
+            return False
+
+        plan: List[List[int]] = []  # [running index, tokens]
+        budget = cfg.token_budget
+        order = sorted(range(len(self.running)),
+                       key=lambda i: len(self.running[i].tokens) - self.running[i].computed > 1)
+        for i in order:
+            if budget == 0:
+                break
+            s = self.running[i]
+            n = min(len(s.tokens) - s.computed, budget)
+            plan.append([i, n])
+            budget -= n
+
+        k = 0
+        while k < len(plan):
+            i, n = plan[k]
+            try:
+                self.backend.reserve(self.running[i].id, n)
+                k += 1
+            except OutOfPages:
+                if len(self.running) == 1:
+                    s = self.running.pop()
+                    finished.append(s.id)
+                    self._finish(s, LENGTH)
+                    plan = []
+                    break
+                preempted.append(self._preempt_last())
+                victim = len(self.running)
+                for p, (j, _) in enumerate(plan):
+                    if j == victim:
+                        del plan[p]
+                        if p < k:
+                            k -= 1
+                        break
+        if not plan:
+            self._record(t0, [], preempted, finished)
+            return not self.is_idle()
+
+        from .engine import StepEntry
+        entries, wants_for = [], []
+        for i, n in plan:
+            s = self.running[i]
+            last = s.computed + n == len(s.tokens)
+            entries.append(StepEntry(s.id, s.tokens[s.computed:s.computed + n], [n - 1] if last else []))
+            if last:
+                wants_for.append(i)
+        logits = self.backend.step(entries, reserve=False)
+
+        batch_desc = []
+        for i, n in plan:
+            s = self.running[i]
+            kind = "prefill" if (len(s.tokens) - s.computed > 1 or s.generated == 0) else "decode"
+            batch_desc.append((s.id, kind, n))
+            s.computed += n
+
+        done = []
+        rows, samplers, contexts = [], [], []
+        for j, i in enumerate(wants_for):
+            s = self.running[i]
+            if s.generated >= s.req.max_tokens:
+                done.append((i, LENGTH))  # max_tokens 0: the prompt is read, nothing is written
+                continue
+            rows.append(j)
+            samplers.append(s.sampler)
+            contexts.append(s.tokens)
+        tokens = self.backend.sample(logits, rows, samplers, contexts) if rows else []
+        now = time.perf_counter()
+        for j, t in zip(rows, tokens):
+            i = wants_for[j]
+            s = self.running[i]
+            if s.first_token is None:
+                s.first_token = now
+            elif s.last_token is not None:
+                self.metrics.itl.append(now - s.last_token)
+            s.last_token = now
+            stop = t in s.req.stop
+            if not stop:
+                s.tokens.append(int(t))
+                if s.req.on_token:
+                    s.req.on_token(s.id, int(t))
+            if stop:
+                done.append((i, STOP))
+            elif s.generated >= s.req.max_tokens or len(s.tokens) >= self.backend.max_position:
+                done.append((i, LENGTH))
+        for i, reason in sorted(done, reverse=True):
+            s = self.running.pop(i)
+            finished.append(s.id)
+            self._finish(s, reason)
+        self.metrics.steps += 1
+        self.metrics.batch_tokens += sum(n for _, n in plan)
+        self._record(t0, batch_desc, preempted, finished)
+        return True
+
+    def _record(self, t0, batch, preempted, finished) -> None:
+        if self.trace is None:
+            return
+        cache = self.backend.cache
+        self.trace.append({
+            "step": self.metrics.steps, "ms": (time.perf_counter() - t0) * 1e3, "batch": list(batch),
+            "preempted": preempted, "finished": finished, "waiting": len(self.waiting),
+            "kv_used": cache.used_pages(0) if cache.groups else 0,
+        })
+
+    def run_until_idle(self, max_steps: int = 1_000_000) -> None:
+        steps = 0
+        while not self.is_idle():
+            self.step()
+            steps += 1
+            if steps > max_steps:
+                raise RuntimeError("the scheduler made no progress")
+
+    def kv_utilization(self) -> float:
+        cache = self.backend.cache
+        return cache.used_pages(0) / cache.num_pages(0) if cache.groups else 0.0

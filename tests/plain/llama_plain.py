@@ -102,10 +102,19 @@ def swiglu(g, u):
 
 
 # ---------------------------------------------------------------------------------------- model
+_LOADED = {}
+
+
+def _load(model_dir):
+    key = (os.path.realpath(model_dir), os.path.getmtime(os.path.join(model_dir, "model.safetensors")))
+    if key not in _LOADED:
+        _LOADED[key] = (read_config(model_dir), read_weights(model_dir))
+    return _LOADED[key]
+
+
 def forward_logits(model_dir, tokens, window=None):
     """Whole sequence, no cache: model.rs:207-362 with every row wanted."""
-    c = read_config(model_dir)
-    w = read_weights(model_dir)
+    c, w = _load(model_dir)
     tokens = np.asarray(tokens, dtype=np.int64)
     T = tokens.shape[0]
     d, nh, nkv, hd = c["d"], c["nh"], c["nkv"], c["hd"]

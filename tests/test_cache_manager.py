@@ -1,0 +1,212 @@
+"""The cache manager on the CPU: no page lost, held twice or freed twice; prefix sharing,
+copy-on-write, fork, truncate, windows, state slots; random orders of requests.
+Unit cases mirror crates/glassbox-core/src/kv.rs:295-349."""
+import random
+
+import pytest
+
+from glassbox_b200.cache import CacheManager, GroupSpec, OutOfPages, chain_hash
+
+
+def mgr(pages=8, share=True, window=None, max_requests=8, page_size=16, groups=1):
+    return CacheManager([GroupSpec(pages, page_size, window) for _ in range(groups)], max_requests=max_requests,
+                        share_prefixes=share)
+
+
+def feed(m, rid, tokens):
+    m.reserve(rid, len(tokens))
+    m.commit(rid, tokens)
+
+
+def test_chain_hash_is_fnv1a_over_le_bytes():
+    h = 0 ^ 0xCBF29CE484222325
+    for b in (7).to_bytes(4, "little"):
+        h = ((h ^ b) * 0x100000001B3) & (2 ** 64 - 1)
+    assert chain_hash(0, [7]) == h
+    assert chain_hash(chain_hash(0, [1, 2]), [3]) != chain_hash(0, [1, 2, 3])
+
+
+def test_pages_come_in_order_and_go_back():
+    m = mgr(pages=4, share=False)
+    m.add_request("a")
+    feed(m, "a", list(range(20)))
+    assert m.table(0, "a") == [0, 1] and m.slot(0, "a", 17) == 16 + 1
+    assert m.free_pages() == 2
+    m.free_request("a")
+    assert m.free_pages() == 4
+    m.check_invariants()
+
+
+def test_prefix_pages_are_shared_and_freed():
+    m = mgr(pages=8)
+    prompt = list(range(40))
+    assert m.add_request(1, prompt) == 0
+    feed(m, 1, prompt)
+    assert m.add_request(2, prompt) == 32          # two whole pages; the last token must still run
+    assert m.table(0, 2) == m.table(0, 1)[:2]
+    assert m.ref_count(0, m.table(0, 1)[0]) == 2
+    # a prompt that is exactly two pages long may only reuse one: its last token has to run
+    assert m.add_request(3, prompt[:32]) == 16
+    m.check_invariants()
+    for r in (1, 2, 3):
+        m.free_request(r)
+    assert m.free_pages() == 8                     # cached pages count as free
+    m.check_invariants()
+    assert m.add_request(4, prompt) == 32          # ... and are found again until evicted
+    m.check_invariants()
+
+
+def test_cached_pages_are_evicted_oldest_first_when_space_is_needed():
+    m = mgr(pages=3)
+    m.add_request(1, list(range(33)))
+    feed(m, 1, list(range(33)))
+    m.free_request(1)                              # pages 0,1 cached (hashed), page 2 free
+    m.add_request(2)
+    feed(m, 2, [9] * 48)                           # needs all three pages: evicts both cached ones
+    m.check_invariants()
+    m.free_request(2)
+    assert m.add_request(3, list(range(33))) == 0  # the old prefix is gone
+    m.check_invariants()
+
+
+def test_fork_copies_on_write():
+    m = mgr(pages=6, share=False)
+    m.add_request("p")
+    feed(m, "p", list(range(20)))
+    m.fork("p", "c")
+    assert m.table(0, "c") == m.table(0, "p")
+    copies = m.reserve("c", 1)                     # the shared partial page must become private
+    assert len(copies) == 1 and copies[0][1] == m.table(0, "p")[1] and copies[0][2] == m.table(0, "c")[1]
+    assert m.table(0, "c")[0] == m.table(0, "p")[0] and m.table(0, "c")[1] != m.table(0, "p")[1]
+    assert m.slot_of("c") != m.slot_of("p")
+    m.commit("c", [99])
+    assert m.reserve("p", 1) == []                 # the parent is alone on its page again
+    m.check_invariants()
+    m.free_request("p")
+    m.free_request("c")
+    assert m.free_pages() == 6
+
+
+def test_reserve_is_all_or_nothing_and_counts_the_cow_page():
+    m = mgr(pages=3, share=False)
+    m.add_request("p")
+    feed(m, "p", list(range(20)))                  # two pages
+    m.fork("p", "c")
+    before = (list(m.table(0, "c")), m.free_pages())
+    with pytest.raises(OutOfPages):
+        m.reserve("c", 16)                         # one copy + one new page, only one page free
+    assert (m.table(0, "c"), m.free_pages()) == before
+    m.check_invariants()
+
+
+def test_truncate_unregisters_a_rewritten_hashed_page():
+    m = mgr(pages=4)
+    m.add_request(1)
+    feed(m, 1, list(range(32)))
+    m.truncate(1, 20)                              # page 1 is partial again and will be overwritten
+    feed(m, 1, [7] * 12)
+    m.free_request(1)
+    assert m.add_request(2, list(range(40))) == 16  # page 0's prefix survives, page 1's stale hash does not
+    m.check_invariants()
+
+
+def test_window_gives_pages_back_early():
+    m = mgr(pages=4, window=20, share=False)
+    m.add_request("a")
+    for _ in range(100):                           # far more tokens than 4 pages hold
+        feed(m, "a", [1])
+        m.check_invariants()
+    table = m.table(0, "a")
+    assert len(table) == 7 and table[:5] == [-1] * 5 and all(p >= 0 for p in table[5:])
+    # a query at position >= 100 sees keys 81..: page 5 (tokens 80..95) must still be there
+    assert m.used_pages() == 2
+    m.free_request("a")
+    assert m.free_pages() == 4
+
+
+def test_window_keeps_what_a_long_portion_needs():
+    m = mgr(pages=8, window=8, share=False)
+    m.add_request("a")
+    m.reserve("a", 100)                            # every row of the portion needs its own window
+    assert all(p >= 0 for p in m.table(0, "a")) and len(m.table(0, "a")) == 7
+    m.commit("a", [0] * 100)
+    assert m.table(0, "a")[:5] == [-1] * 5
+    m.check_invariants()
+
+
+def test_groups_have_pages_of_their_own():
+    m = CacheManager([GroupSpec(8, 16, None), GroupSpec(3, 16, 16)], max_requests=4)
+    m.add_request("a")
+    for _ in range(60):
+        feed(m, "a", [1])
+    assert m.used_pages(0) == 4 and m.used_pages(1) <= 2
+    m.add_request("b")
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 48)                         # fits group 0, not the small windowed group
+    assert m.table(0, "b") == [] and m.table(1, "b") == []
+    m.check_invariants()
+
+
+def test_prefix_sharing_is_off_when_unsound():
+    assert not CacheManager([GroupSpec(8, 16, 32)], share_prefixes=True).share_prefixes
+    assert not CacheManager([GroupSpec(8, 16, None)], share_prefixes=True, has_state=True).share_prefixes
+
+
+def test_state_slots():
+    m = mgr(pages=8, max_requests=2, share=False)
+    m.add_request("a")
+    m.add_request("b")
+    assert sorted(m.drain_fresh_slots()) == [0, 1] and m.drain_fresh_slots() == []
+    with pytest.raises(OutOfPages):
+        m.add_request("c")
+    m.free_request("a")
+    m.add_request("c")
+    assert m.drain_fresh_slots() == [m.slot_of("c")]
+    m.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("window, share", [(None, True), (None, False), (24, False)])
+def test_random_orders_never_lose_or_double_a_page(seed, window, share):
+    rng = random.Random(seed)
+    m = mgr(pages=12, share=share, window=window, max_requests=6)
+    live, next_id = {}, 0
+    shared = [rng.randrange(50) for _ in range(40)]
+    for _ in range(400):
+        op = rng.random()
+        try:
+            if op < 0.2 and len(live) < 6:
+                prompt = (shared[:rng.choice([16, 32, 40])] if rng.random() < 0.5 else []) + \
+                    [rng.randrange(50) for _ in range(rng.randrange(1, 30))]
+                reused = m.add_request(next_id, prompt)
+                assert reused % 16 == 0 and reused < len(prompt)
+                live[next_id] = prompt[reused:]
+                next_id += 1
+            elif op < 0.7 and live:
+                rid = rng.choice(list(live))
+                pending = live[rid]
+                n = rng.randrange(1, 20)
+                chunk = pending[:n] if pending else [rng.randrange(50) for _ in range(1)]
+                m.reserve(rid, len(chunk))
+                m.commit(rid, chunk)
+                live[rid] = pending[len(chunk):]
+            elif op < 0.8 and live and len(live) < 6:
+                parent = rng.choice(list(live))
+                m.fork(parent, next_id)
+                live[next_id] = list(live[parent])
+                next_id += 1
+            elif op < 0.85 and live and window is None:
+                rid = rng.choice(list(live))
+                m.truncate(rid, rng.randrange(0, m.length(rid) + 1))
+                live[rid] = []
+            elif live:
+                rid = rng.choice(list(live))
+                m.free_request(rid)
+                del live[rid]
+        except OutOfPages:
+            pass
+        m.check_invariants()
+    for rid in list(live):
+        m.free_request(rid)
+    m.check_invariants()
+    assert m.free_pages() == 12 and len(m.free_slots) == 6

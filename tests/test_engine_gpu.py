@@ -1,0 +1,159 @@
+"""The engine in one process: long decoding, the first tokens of a sequence, greedy and sampled
+generation through the Python entry point and the command line, the scheduler on the real engine
+(batched = alone, preemption, prefix sharing, forks), and errors that must be loud."""
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, TINY, assert_logits_close
+from plain import sampler_plain
+from plain.llama_plain import forward_logits, greedy as plain_greedy
+
+pytestmark = pytest.mark.gpu
+
+
+def make_engine(folder, dtype, **kw):
+    from glassbox_b200.engine.engine import Engine
+    kw.setdefault("cache_tokens", 1024)
+    kw.setdefault("max_batch_tokens", 256)
+    return Engine(folder, dtype, **kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_and_long_decoding(model_dirs, name, dtype):
+    from glassbox_b200.engine.engine import StepEntry
+    folder = model_dirs(name, dtype)
+    T = TINY[name]["max_position_embeddings"]
+    toks = [random.Random(1).randrange(TINY[name]["vocab_size"]) for _ in range(T)]
+    ref = forward_logits(folder, toks)
+    eng = make_engine(folder, dtype)
+    eng.add_request("a")
+    rows = [eng.step([StepEntry("a", [t], [0])])[0].cpu().numpy() for t in toks]     # every token decoded alone
+    eng.check()
+    assert_logits_close(np.stack(rows[:4]), ref[:4], dtype, "first tokens")
+    assert_logits_close(np.stack(rows), ref, dtype, "token by token up to max_position")
+    with pytest.raises(ValueError, match="max_position"):
+        eng.step([StepEntry("a", [1], [0])])
+
+
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16")])
+def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
+    import glassbox_b200
+    folder = model_dirs(name, dtype)
+    llm = glassbox_b200.load(folder, dtype, blocks=64, budget=16, max_seqs=4)
+    rng = random.Random(2)
+    prompts = [[rng.randrange(TINY[name]["vocab_size"]) for _ in range(n)] for n in (5, 17, 33)]
+    outs = llm.generate(prompts, 16)
+    for p, out in zip(prompts, outs):
+        want = plain_greedy(folder, p, 16)
+        if out != want:   # report the margin, so a near-tie can be told from a fault
+            i = next(j for j in range(16) if out[j] != want[j])
+            row = np.sort(forward_logits(folder, p + want[:i])[-1])
+            pytest.fail(f"greedy token {i} differs; top-2 margin there is {row[-1] - row[-2]:.3e}")
+    single = llm.generate(prompts[0], 4)
+    assert single == outs[0][:4]
+
+
+def test_sampled_generation_follows_the_plain_sampler(model_dirs):
+    """Tiny B, temperature 0.8, fixed per-request seeds, 24 tokens, prefill chunk 16."""
+    import glassbox_b200
+    folder = model_dirs("B", "float32")
+    llm = glassbox_b200.load(folder, "float32", blocks=64, budget=16, max_seqs=8)
+    rng = random.Random(3)
+    prompts = [[rng.randrange(512) for _ in range(n)] for n in (1, 8, 40, 64, 100)]
+    outs = llm.generate(prompts, 24, temperature=0.8, seed=100)
+    assert outs == llm.generate(prompts, 24, temperature=0.8, seed=100), "seeded runs repeat"
+    for i, (p, out) in enumerate(zip(prompts, outs)):
+        uniforms = sampler_plain.xorshift64star(100 + i)
+        toks = list(p)
+        for j, t in enumerate(out):
+            dist = sampler_plain.distribution(forward_logits(folder, toks)[-1], toks, temperature=0.8)
+            r = next(uniforms)
+            want = sampler_plain.draw(dist, r)
+            if t != want:
+                acc, lo = 0.0, None
+                for tok in sorted(dist):     # a draw within 1e-5 of an interval's edge may fall either way
+                    if tok in (t, want):
+                        lo = acc if lo is None else lo
+                    acc += dist[tok]
+                    if tok in (t, want) and lo is not None and abs(acc - r) < 1e-5:
+                        break
+                else:
+                    pytest.fail(f"request {i} token {j}: sampled {t}, the plain sampler draws {want}")
+            toks.append(t)
+    filtered = llm.generate(prompts[:2], 8, temperature=0.9, top_k=5, top_p=0.9, repetition_penalty=1.2, seed=4)
+    assert all(len(o) == 8 for o in filtered)
+
+
+@pytest.mark.parametrize("dtype", ["float32"])
+def test_scheduler_on_the_engine_batched_equals_alone_with_preemption(model_dirs, dtype):
+    import glassbox_b200
+    from glassbox_b200.api import greedy
+    folder = model_dirs("A", dtype)
+    rng = random.Random(99)
+    prompts = [[rng.randrange(256) for _ in range(rng.randrange(1, 40))] for _ in range(10)]
+    llm = glassbox_b200.load(folder, dtype, blocks=9, budget=64, max_seqs=8, prefix_cache=True)   # pages run out
+    outs, reasons = llm.generate(prompts, 20, return_reasons=True)
+    assert llm.scheduler.metrics.preemptions > 0, "the test did not exercise preemption"
+    llm.engine.cache.check_invariants()
+    assert llm.engine.cache.free_pages() == 9
+    alone = make_engine(folder, dtype)
+    for p, out in zip(prompts, outs):
+        assert out == greedy(alone, p, 20)
+
+
+def test_prefix_sharing_and_forks_do_not_change_logits(model_dirs):
+    from glassbox_b200.engine.engine import StepEntry
+    folder = model_dirs("B", "float32")
+    rng = random.Random(7)
+    prefix = [rng.randrange(512) for _ in range(70)]
+    a, b = prefix + [1, 2, 3], prefix + [9, 8, 7, 6]
+    eng = make_engine(folder, "float32", share_prefixes=True, cache_tokens=256)
+    assert eng.add_request("a", a) == 0
+    eng.step([StepEntry("a", a, [len(a) - 1])])
+    reused = eng.add_request("b", b)
+    assert reused == 64
+    got = eng.step([StepEntry("b", b[reused:], list(range(len(b) - reused)))]).cpu().numpy()
+    assert_logits_close(got, forward_logits(folder, b)[reused:], "float32", "after a shared prefix")
+    # fork: the child shares every page, writes into a copy of the partial last page
+    eng.fork("a", "c")
+    tail_c, tail_a = [5, 5, 5], [6, 6]
+    got_c = eng.step([StepEntry("c", tail_c, [0, 1, 2])]).cpu().numpy()
+    got_a = eng.step([StepEntry("a", tail_a, [0, 1])]).cpu().numpy()
+    assert_logits_close(got_c, forward_logits(folder, a + tail_c)[len(a):], "float32", "forked child")
+    assert_logits_close(got_a, forward_logits(folder, a + tail_a)[len(a):], "float32", "parent after fork")
+    eng.cache.check_invariants()
+    for r in "abc":
+        eng.free_request(r)
+    assert eng.cache.free_pages() == eng.cache.num_pages()
+
+
+def test_bad_input_is_loud_not_wrong(model_dirs):
+    from glassbox_b200.engine.engine import StepEntry
+    from glassbox_b200.kernels import KernelError
+    eng = make_engine(model_dirs("A", "float32"), "float32")
+    eng.add_request("a")
+    eng.step([StepEntry("a", [1, 2, 999], [2])])          # token id outside the vocabulary of 256
+    with pytest.raises(KernelError, match="token id"):
+        eng.check()
+    with pytest.raises(KeyError):
+        eng.step([StepEntry("nobody", [1], [0])])
+    with pytest.raises(ValueError):
+        eng.step([StepEntry("a", [1], [3])])
+
+
+def test_command_line(model_dirs):
+    folder = model_dirs("A", "float32")
+    out = subprocess.run([sys.executable, "-m", "glassbox_b200", "generate", "--model", folder, "--dtype", "f32",
+                          "--prompt", "5 17 3; 9,9,9,9", "-n", "6", "--blocks", "32"],
+                         capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = [[int(t) for t in l.split()] for l in out.stdout.strip().splitlines()]
+    assert lines == [plain_greedy(folder, [5, 17, 3], 6), plain_greedy(folder, [9, 9, 9, 9], 6)]
+    assert "tok/s" in out.stderr
+    bad = subprocess.run([sys.executable, "-m", "glassbox_b200", "generate"], capture_output=True, text=True, cwd=ROOT)
+    assert bad.returncode == 2 and "usage" in bad.stderr

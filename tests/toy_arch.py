@@ -1,0 +1,200 @@
+"""Toy parts and architectures that exist only in the tests. They are registered from here, through
+the same public calls a user would make, without touching the framework's files:
+
+* ``ProbeForCausalLM``: one attention layer between an identity "norm" and a feed-forward that adds
+  nothing, with every matrix given by the test. With 0/1-structured weights each logit says which
+  keys a row read, so a misread key, page or window edge shows at full size in any precision.
+* ``ToyStateForCausalLM``: layer 0 mixes with a decaying running sum kept in a per-request state
+  slot (no keys, no pages); layer 1 is ordinary attention. Its schedule may run a layer twice or
+  let a run read another run's cache.
+
+These are test fixtures for the framework's interfaces, not models of anything.
+"""
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from glassbox_b200.config import (GqaAttentionSpec, LayerSpec, ModelConfig, NoPositionSpec, RmsNormSpec, RopeSpec,
+                                  RunSpec, SwiGluSpec)
+from glassbox_b200.config.registry import Architecture, register_architecture
+from glassbox_b200.parts import FeedForward, Mixer, Norm, StateSpec, register_part
+from glassbox_b200.weights.binding import ParamSpec, Stacked
+
+
+# ------------------------------------------------------------------------------------ toy parts
+@dataclass(frozen=True)
+class IdentityNormSpec:
+    kind: str = "test_identity_norm"
+
+
+class IdentityNorm(Norm):
+    def __init__(self, spec, *, hidden_size):
+        super().__init__(spec)
+
+    def forward(self, ctx, x, out, rows=None):
+        out.copy_(x if rows is None else x[rows.long()])
+
+
+@dataclass(frozen=True)
+class ZeroFfnSpec:
+    kind: str = "test_zero_ffn"
+
+
+class ZeroFfn(FeedForward):
+    def __init__(self, spec, *, hidden_size):
+        super().__init__(spec)
+
+    def forward(self, ctx, h, residual):
+        return None
+
+
+@dataclass(frozen=True)
+class RunningStateSpec:
+    """out_t = W s_t with s_t = decay * s_{t-1} + h_t, s kept per request between steps."""
+    decay: float
+    kind: str = "test_running_state"
+
+
+class RunningState(Mixer):
+    def __init__(self, spec, *, hidden_size):
+        super().__init__(spec)
+        self.d = hidden_size
+
+    def param_specs(self):
+        return {"w": ParamSpec((self.d, self.d))}
+
+    def cache_spec(self):
+        return StateSpec((self.d,), torch.float32)
+
+    def forward(self, ctx, h, residual, cache, writes_cache):
+        w = self.params["w"].float()
+        for seq in ctx.seqs:                       # rows of one request are consecutive and in order
+            s = cache.state[seq.slot].clone()
+            for r in range(seq.first_row, seq.first_row + seq.n_rows):
+                s = self.spec.decay * s + h[r].float()
+                residual[r] += w @ s
+            if writes_cache:
+                cache.state[seq.slot].copy_(s)
+
+
+register_part("norm", "test_identity_norm", IdentityNorm, replace=True)
+register_part("ffn", "test_zero_ffn", ZeroFfn, replace=True)
+register_part("mixer", "test_running_state", RunningState, replace=True)
+
+
+# -------------------------------------------------------------------------------- architectures
+def _parse_probe(raw):
+    hd = raw["head_dim"]
+    position = NoPositionSpec() if raw.get("rope_theta") is None else \
+        RopeSpec(theta=float(raw["rope_theta"]), rotary_dim=raw.get("rotary_dim", hd), max_position=raw["max_position"])
+    attn = GqaAttentionSpec(num_heads=raw["num_heads"], num_kv_heads=raw["num_kv_heads"], head_dim=hd,
+                            scale=float(raw.get("scale", 1.0)), position=position, window=raw.get("window"))
+    layer = LayerSpec(mixer=attn, ffn=ZeroFfnSpec(), mixer_norm=IdentityNormSpec(), ffn_norm=IdentityNormSpec())
+    return ModelConfig(architecture="ProbeForCausalLM", vocab_size=raw["vocab_size"], hidden_size=raw["hidden_size"],
+                       max_position=raw["max_position"], tie_word_embeddings=False, layers=(layer,),
+                       schedule=(RunSpec(0, 0),), final_norm=IdentityNormSpec(), raw=dict(raw))
+
+
+def _bind_probe(config):
+    return {"embed.weight": Stacked(("embed",)), "layers.0.mixer.wqkv": Stacked(("wq", "wk", "wv")),
+            "layers.0.mixer.wo": Stacked(("wo",)), "head.weight": Stacked(("head",))}
+
+
+register_architecture(Architecture("ProbeForCausalLM", _parse_probe, _bind_probe), replace=True)
+
+
+def _parse_toy_state(raw):
+    d, hd = raw["hidden_size"], raw["head_dim"]
+    norm = RmsNormSpec(eps=raw["eps"])
+    ffn = SwiGluSpec(intermediate_size=raw["intermediate_size"])
+    rope = RopeSpec(theta=raw["rope_theta"], rotary_dim=hd, max_position=raw["max_position"])
+    attn = GqaAttentionSpec(num_heads=raw["num_heads"], num_kv_heads=raw["num_kv_heads"], head_dim=hd,
+                            scale=hd ** -0.5, position=rope, window=raw.get("window"))
+    layers = (LayerSpec(RunningStateSpec(decay=raw["decay"]), ffn, norm, norm), LayerSpec(attn, ffn, norm, norm))
+    schedule = tuple(RunSpec(*r) for r in raw.get("schedule", [(0, 0, True), (1, 1, True)]))
+    return ModelConfig(architecture="ToyStateForCausalLM", vocab_size=raw["vocab_size"], hidden_size=d,
+                       max_position=raw["max_position"], tie_word_embeddings=True, layers=layers, schedule=schedule,
+                       final_norm=norm, raw=dict(raw))
+
+
+def _bind_toy_state(config):
+    from glassbox_b200.weights.binding import Tied
+    b = {"embed.weight": Stacked(("embed",)), "head.weight": Tied("embed.weight"),
+         "final_norm.weight": Stacked(("final_norm",)), "layers.0.mixer.w": Stacked(("state_w",)),
+         "layers.1.mixer.wqkv": Stacked(("wq", "wk", "wv")), "layers.1.mixer.wo": Stacked(("wo",))}
+    for i in (0, 1):
+        b[f"layers.{i}.mixer_norm.weight"] = Stacked((f"norm{i}a",))
+        b[f"layers.{i}.ffn_norm.weight"] = Stacked((f"norm{i}b",))
+        b[f"layers.{i}.ffn.w_gate_up"] = Stacked((f"gate{i}", f"up{i}"))
+        b[f"layers.{i}.ffn.w_down"] = Stacked((f"down{i}",))
+    return b
+
+
+register_architecture(Architecture("ToyStateForCausalLM", _parse_toy_state, _bind_toy_state), replace=True)
+
+
+# ----------------------------------------------------------------- the probe model, and its truth
+ROOT = 1.25     # q and k are +-1 vectors times this: a matching pair scores ROOT^2 * head_dim, exactly
+
+
+def write_probe_model(folder, *, vocab=400, hd=32, nh=2, nkv=1, window=None, max_position=512, seed=0,
+                      store=torch.float32):
+    """Token t carries, per query head, a query direction; a key direction; and a value vector. A row
+    scores ROOT^2 * hd (50 at hd 32) against keys whose direction equals its query direction and
+    exactly 0 against all others: directions are rows of a Hadamard matrix with entries +-1, and
+    every weight is exact in bfloat16, so the softmax is the same in every precision. Logit
+    j < nh*hd is channel j of (query direction + attention output). Returns the per-token tables
+    from which ``probe_truth`` states what the logits must be."""
+    import json
+    import os
+    from glassbox_b200.weights import write_safetensors
+    rng = np.random.default_rng(seed)
+    had = np.array([[1.0]])
+    while had.shape[0] < hd:
+        had = np.block([[had, had], [had, -had]])
+    qdir = rng.integers(0, hd, size=(vocab, nh))
+    kdir = rng.integers(0, hd, size=(vocab, nkv))
+    # values: small integers / 8 are exact in bfloat16
+    val = rng.integers(-16, 17, size=(vocab, nkv, hd)).astype(np.float64) / 8.0
+    d = (nh + 2 * nkv) * hd
+    embed = np.zeros((vocab, d))
+    for h in range(nh):
+        embed[:, h * hd:(h + 1) * hd] = had[qdir[:, h]]
+    for g in range(nkv):
+        embed[:, (nh + g) * hd:(nh + g + 1) * hd] = had[kdir[:, g]]
+        embed[:, (nh + nkv + g) * hd:(nh + nkv + g + 1) * hd] = val[:, g]
+    root = ROOT
+    wq = np.zeros((nh * hd, d)); wq[:, :nh * hd] = np.eye(nh * hd) * root
+    wk = np.zeros((nkv * hd, d)); wk[:, nh * hd:(nh + nkv) * hd] = np.eye(nkv * hd) * root
+    wv = np.zeros((nkv * hd, d)); wv[:, (nh + nkv) * hd:] = np.eye(nkv * hd)
+    # the output projection adds the attention output onto the channels that hold the query
+    # directions; the head reads those channels back
+    wo = np.zeros((d, nh * hd)); wo[:nh * hd, :] = np.eye(nh * hd)
+    head = np.zeros((vocab, d)); head[:nh * hd, :nh * hd] = np.eye(nh * hd)
+    assert vocab >= nh * hd
+    os.makedirs(folder, exist_ok=True)
+    raw = {"architectures": ["ProbeForCausalLM"], "vocab_size": vocab, "hidden_size": d, "num_heads": nh,
+           "num_kv_heads": nkv, "head_dim": hd, "window": window, "scale": 1.0, "max_position": max_position,
+           "rope_theta": None}
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(raw, f)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(store)
+    write_safetensors(os.path.join(folder, "model.safetensors"),
+                      {"embed": t(embed), "wq": t(wq), "wk": t(wk), "wv": t(wv), "wo": t(wo), "head": t(head)})
+    return {"qdir": qdir, "kdir": kdir, "val": val, "had": had, "nh": nh, "nkv": nkv, "hd": hd, "window": window,
+            "vocab": vocab}
+
+
+def probe_truth(info, tokens):
+    """Expected logits[:, :nh*hd] for a whole sequence, from the plain attention part."""
+    from plain.llama_plain import attention
+    nh, nkv, hd = info["nh"], info["nkv"], info["hd"]
+    toks = np.asarray(tokens)
+    root = ROOT
+    q = np.stack([info["had"][info["qdir"][toks, h]] for h in range(nh)], axis=1) * root
+    k = np.stack([info["had"][info["kdir"][toks, g]] for g in range(nkv)], axis=1) * root
+    v = info["val"][toks]
+    att = attention(q, k, v, 1.0, info["window"]).reshape(len(toks), nh * hd)
+    return att + (q / root).reshape(len(toks), nh * hd)          # the residual carried the query part
