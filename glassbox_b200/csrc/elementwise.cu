@@ -100,6 +100,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float2* __restri
     const int qd = nh * hd, kvd = nkv * hd;
     T* base = qkv + (size_t)row * (qd + 2 * kvd);
     int pos = positions[row];
+    if (pos < 0) return;  // a padding row of a fixed-shape batch: nothing to rotate, nothing to store
     bool rotate = table != nullptr;
     if (rotate && (pos < 0 || pos >= max_pos)) {
         if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_POSITION);

@@ -71,6 +71,9 @@ class StepContext:
         self.group_tables: List[torch.Tensor] = []
         self.max_rows_per_seq = 0
         self.max_context = 0
+        self.num_seqs = 0
+        self.decode_only = False          # every sequence of the step brings exactly one row
+        self.temperature = self.uniform = None
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return self._scratch.get(name, shape, dtype, grow)

@@ -52,7 +52,7 @@ class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", *, cache_tokens: Optional[int] = None,
                  num_pages: Optional[int] = None, page_size: int = 16, max_batch_tokens: int = 2048,
                  max_requests: int = 64, share_prefixes: bool = False, device: str = "cuda:0",
-                 config: Optional[ModelConfig] = None):
+                 config: Optional[ModelConfig] = None, use_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("glassbox_b200 needs a CUDA device: every kernel is CUDA and there is no CPU path")
         self.device = torch.device(device)
@@ -87,6 +87,12 @@ class Engine:
         self._stage_events = [None] * len(self._stage)
         self._stage_next = 0
         self.steps = 0
+        self.use_graphs = bool(use_graphs)
+        self.max_graph_batch = 64
+        self._graphs: Dict[tuple, dict] = {}
+        self.graph_replays = 0
+        self.sampled: Optional[torch.Tensor] = None
+        self.h2d_bytes_last = 0
 
     # ---------------------------------------------------------------------------- requests
     def add_request(self, request, prompt: Sequence[int] = ()) -> int:
@@ -116,11 +122,13 @@ class Engine:
                 t = torch.tensor(pairs, dtype=torch.int32, device=self.device)
                 kernels.copy_pages(self.device_cache.k[g], self.device_cache.v[g], t)
 
-    def _upload(self, host: np.ndarray) -> torch.Tensor:
+    # ----------------------------------------------------------------------- step metadata
+    def _stage_copy(self, host: np.ndarray, dev: torch.Tensor) -> None:
+        """One host-to-device copy of the step's metadata through pinned staging buffers (a ring,
+        so that a buffer is not rewritten while its copy may still be in flight)."""
         n = host.size
-        if n > self._meta_dev.numel():
+        if n > self._stage[0].numel():
             cap = 1 << int(n - 1).bit_length()
-            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._stage = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(len(self._stage))]
             self._stage_events = [None] * len(self._stage)
         i = self._stage_next
@@ -129,21 +137,96 @@ class Engine:
             self._stage_events[i].synchronize()
         stage = self._stage[i]
         stage.numpy()[:n] = host
-        self._meta_dev[:n].copy_(stage[:n], non_blocking=True)
+        dev[:n].copy_(stage[:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._stage_events[i] = ev
         self.h2d_bytes_last = n * 4
-        return self._meta_dev
 
-    def step(self, entries: Sequence[StepEntry], reserve: bool = True, commit: bool = True) -> torch.Tensor:
-        """Run one batch. Returns float32 logits ``[total wanted, vocab]`` on the device, in the
-        order of the entries and of each entry's ``want``; the tensor is scratch that the next
-        step overwrites. With ``reserve`` False the caller has already reserved room for every
-        entry (the scheduler does, to decide about preemption first)."""
-        cfg = self.config
+    def _layout(self, n: int, S: int, n_want: int, max_pages: int):
+        off, cur = {}, 0
+        for name, size in (("tokens", n), ("positions", n), ("row_seq", n), ("want", n_want),
+                           ("seq_first_row", S + 1), ("seq_start_pos", S), ("seq_slots", S),
+                           ("temperature", n_want), ("uniform", n_want)):
+            off[name] = cur
+            cur += size
+        for g in range(len(self.cache.groups)):
+            off[f"slots{g}"] = cur
+            cur += n
+            off[f"tables{g}"] = cur
+            cur += S * max_pages
+        off["_size"] = cur
+        return off
+
+    def _fill(self, entries, off, n, S, max_pages, sampling=None) -> np.ndarray:
+        """Host copy of the metadata block. Rows and sequences beyond the entries (a batch padded to
+        a fixed shape) get position -1, slot -1 and empty tables: every kernel skips them."""
         ps = self.page_size
         n_groups = len(self.cache.groups)
+        host = np.zeros(off["_size"], dtype=np.int32)
+        host[off["positions"]:off["positions"] + n] = -1
+        for g in range(n_groups):
+            host[off[f"slots{g}"]:off[f"slots{g}"] + n] = -1
+            host[off[f"tables{g}"]:off[f"tables{g}"] + S * max_pages] = -1
+        seqs: List[SeqInfo] = []
+        row, wi, max_ctx = 0, off["want"], 0
+        for si, e in enumerate(entries):
+            k = len(e.tokens)
+            start = self.cache.length(e.request)
+            seqs.append(SeqInfo(request=e.request, slot=self.cache.slot_of(e.request), start_pos=start, n_rows=k,
+                                first_row=row))
+            host[off["tokens"] + row:off["tokens"] + row + k] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
+            pos = np.arange(start, start + k, dtype=np.int32)
+            host[off["positions"] + row:off["positions"] + row + k] = pos
+            host[off["row_seq"] + row:off["row_seq"] + row + k] = si
+            for w in e.want:
+                host[wi] = row + w
+                wi += 1
+            host[off["seq_first_row"] + si] = row
+            host[off["seq_start_pos"] + si] = start
+            host[off["seq_slots"] + si] = seqs[-1].slot
+            for g in range(n_groups):
+                table = np.asarray(self.cache.table(g, e.request), dtype=np.int32)
+                t0 = off[f"tables{g}"] + si * max_pages
+                host[t0:t0 + table.size] = table
+                host[off[f"slots{g}"] + row:off[f"slots{g}"] + row + k] = table[pos // ps] * ps + pos % ps
+            row += k
+            max_ctx = max(max_ctx, start + k)
+        host[off["seq_first_row"] + len(entries):off["seq_first_row"] + S + 1] = row
+        for si in range(len(entries), S):            # padding sequences: one padding row each
+            host[off["row_seq"] + row] = si
+            host[off["seq_first_row"] + si] = row
+            host[wi] = row
+            wi += 1
+            row += 1
+        host[off["seq_first_row"] + S] = row
+        if sampling is not None:
+            temps, unif = sampling
+            k = len(temps)
+            host[off["temperature"]:off["temperature"] + k] = np.asarray(temps, dtype=np.float32).view(np.int32)
+            host[off["uniform"]:off["uniform"] + k] = np.asarray(unif, dtype=np.float32).view(np.int32)
+        self._seqs, self._max_ctx = seqs, max_ctx
+        return host
+
+    def _bind(self, ctx: StepContext, dev: torch.Tensor, off, n, S, n_want, max_pages) -> None:
+        n_groups = len(self.cache.groups)
+        ctx.n, ctx.num_wanted = n, n_want
+        ctx.tokens = dev[off["tokens"]:off["tokens"] + n]
+        ctx.positions = dev[off["positions"]:off["positions"] + n]
+        ctx.row_seq = dev[off["row_seq"]:off["row_seq"] + n]
+        ctx.want_rows = dev[off["want"]:off["want"] + n_want]
+        ctx.seq_first_row = dev[off["seq_first_row"]:off["seq_first_row"] + S + 1]
+        ctx.seq_start_pos = dev[off["seq_start_pos"]:off["seq_start_pos"] + S]
+        ctx.seq_slots = dev[off["seq_slots"]:off["seq_slots"] + S]
+        ctx.temperature = dev[off["temperature"]:off["temperature"] + n_want].view(torch.float32)
+        ctx.uniform = dev[off["uniform"]:off["uniform"] + n_want].view(torch.float32)
+        ctx.group_slots = [dev[off[f"slots{g}"]:off[f"slots{g}"] + n] for g in range(n_groups)]
+        ctx.group_tables = [dev[off[f"tables{g}"]:off[f"tables{g}"] + S * max_pages].view(S, max_pages)
+                            for g in range(n_groups)]
+        ctx.num_seqs = S
+
+    def _validate(self, entries) -> int:
+        cfg = self.config
         n = sum(len(e.tokens) for e in entries)
         if n == 0:
             raise ValueError("a step needs at least one token")
@@ -165,102 +248,143 @@ class Engine:
             for w in e.want:
                 if not 0 <= w < len(e.tokens):
                     raise ValueError(f"request {e.request!r}: wanted index {w} outside its {len(e.tokens)} tokens")
+        return n
+
+    def step(self, entries: Sequence[StepEntry], reserve: bool = True, commit: bool = True,
+             sampling=None) -> torch.Tensor:
+        """Run one batch. Returns float32 logits ``[total wanted, vocab]`` on the device, in the
+        order of the entries and of each entry's ``want``; the tensor is scratch that the next
+        step overwrites. With ``reserve`` False the caller has already reserved room for every
+        entry (the scheduler does, to decide about preemption first). With ``sampling`` =
+        (temperatures, uniforms), one per wanted row, the sampling kernel runs in the same step
+        and ``self.sampled`` holds the chosen token of each wanted row (int32, on the device).
+
+        A step made only of single decoded tokens runs as a CUDA graph of fixed shape (batch and
+        table sizes rounded up to powers of two, padding rows skipped by every kernel); any other
+        step launches its kernels one by one. Both run the same kernels on the same data."""
+        n = self._validate(entries)
+        self.sampled = None
         if reserve:
             for e in entries:
                 self.reserve(e.request, len(e.tokens))
         self.device_cache.zero_slots(self.cache.drain_fresh_slots())
-
+        n_groups = len(self.cache.groups)
         S = len(entries)
         max_pages = max(max(len(self.cache.table(g, e.request)) for e in entries) for g in range(n_groups)) \
             if n_groups else 1
         n_want = sum(len(e.want) for e in entries)
-        # layout of the int32 metadata block
-        off = {}
-        cur = 0
-        for name, size in (("tokens", n), ("positions", n), ("row_seq", n), ("want", n_want),
-                           ("seq_first_row", S + 1), ("seq_start_pos", S), ("seq_slots", S)):
-            off[name] = cur
-            cur += size
-        for g in range(n_groups):
-            off[f"slots{g}"] = cur
-            cur += n
-            off[f"tables{g}"] = cur
-            cur += S * max_pages
-        host = np.empty(cur, dtype=np.int32)
-        seqs: List[SeqInfo] = []
-        row = 0
-        wi = off["want"]
-        max_ctx = 0
-        for si, e in enumerate(entries):
-            k = len(e.tokens)
-            start = self.cache.length(e.request)
-            seqs.append(SeqInfo(request=e.request, slot=self.cache.slot_of(e.request), start_pos=start, n_rows=k,
-                                first_row=row))
-            host[off["tokens"] + row:off["tokens"] + row + k] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
-            pos = np.arange(start, start + k, dtype=np.int32)
-            host[off["positions"] + row:off["positions"] + row + k] = pos
-            host[off["row_seq"] + row:off["row_seq"] + row + k] = si
-            for w in e.want:
-                host[wi] = row + w
-                wi += 1
-            host[off["seq_first_row"] + si] = row
-            host[off["seq_start_pos"] + si] = start
-            host[off["seq_slots"] + si] = seqs[-1].slot
-            for g in range(n_groups):
-                table = np.asarray(self.cache.table(g, e.request), dtype=np.int32)
-                t0 = off[f"tables{g}"] + si * max_pages
-                host[t0:t0 + max_pages] = -1
-                host[t0:t0 + table.size] = table
-                host[off[f"slots{g}"] + row:off[f"slots{g}"] + row + k] = table[pos // ps] * ps + pos % ps
-            row += k
-            max_ctx = max(max_ctx, start + k)
-        host[off["seq_first_row"] + S] = row
-        dev = self._upload(host)
-
-        ctx = self.ctx
-        ctx.n, ctx.num_wanted, ctx.seqs = n, n_want, seqs
-        ctx.tokens = dev[off["tokens"]:off["tokens"] + n]
-        ctx.positions = dev[off["positions"]:off["positions"] + n]
-        ctx.row_seq = dev[off["row_seq"]:off["row_seq"] + n]
-        ctx.want_rows = dev[off["want"]:off["want"] + n_want]
-        ctx.seq_first_row = dev[off["seq_first_row"]:off["seq_first_row"] + S + 1]
-        ctx.seq_start_pos = dev[off["seq_start_pos"]:off["seq_start_pos"] + S]
-        ctx.seq_slots = dev[off["seq_slots"]:off["seq_slots"] + S]
-        ctx.group_slots = [dev[off[f"slots{g}"]:off[f"slots{g}"] + n] for g in range(n_groups)]
-        ctx.group_tables = [dev[off[f"tables{g}"]:off[f"tables{g}"] + S * max_pages].view(S, max_pages)
-                            for g in range(n_groups)]
-        ctx.max_rows_per_seq = max(s.n_rows for s in seqs)
-        ctx.max_context = max_ctx
-
-        logits = self.model.forward(ctx)
+        decode_only = self.use_graphs and n == S and n_want == S and S <= self.max_graph_batch \
+            and not self.device_cache.has_state
+        if decode_only:
+            logits = self._step_graph(entries, S, max_pages, sampling)
+        else:
+            off = self._layout(n, S, n_want, max_pages)
+            host = self._fill(entries, off, n, S, max_pages, sampling)
+            if off["_size"] > self._meta_dev.numel():
+                self._meta_dev = torch.empty(1 << int(off["_size"] - 1).bit_length(), dtype=torch.int32,
+                                             device=self.device)
+            self._stage_copy(host, self._meta_dev)
+            ctx = self.ctx
+            self._bind(ctx, self._meta_dev, off, n, S, n_want, max_pages)
+            ctx.seqs, ctx.max_context = self._seqs, self._max_ctx
+            ctx.max_rows_per_seq = max(s.n_rows for s in self._seqs)
+            ctx.decode_only = False
+            logits = self.model.forward(ctx)
+            if sampling is not None and n_want:
+                self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
+                kernels.sample(logits, self.sampled, ctx.temperature, ctx.uniform)
         if commit:
             for e in entries:
                 self.cache.commit(e.request, e.tokens)
         self.steps += 1
         return logits
 
+    def _step_graph(self, entries, S: int, max_pages: int, sampling) -> torch.Tensor:
+        Sb = 1 << max(S - 1, 0).bit_length()
+        Pb = max(8, 1 << max(max_pages - 1, 0).bit_length())
+        key = (Sb, Pb)
+        off = self._layout(Sb, Sb, Sb, Pb)
+        if sampling is None:
+            sampling = ([0.0] * S, [0.0] * S)
+        host = self._fill(entries, off, Sb, Sb, Pb, sampling)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._capture(key, off, host)
+        self._stage_copy(host, g["meta"])
+        g["graph"].replay()
+        kernels.launch_count += g["nodes"]
+        self.sampled = g["sampled"][:S]
+        self.graph_replays += 1
+        return g["logits"][:S]
+
+    def _capture(self, key, off, host):
+        """Record the decode step for one (batch, table width) shape. The first call runs the
+        kernels once outside capture so that every scratch buffer exists, then records them."""
+        Sb, Pb = key
+        meta = torch.empty(off["_size"], dtype=torch.int32, device=self.device)
+        ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype)
+        self._bind(ctx, meta, off, Sb, Sb, Sb, Pb)
+        ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(Sb)]
+        ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, 1, True
+        pad = self._layout(Sb, Sb, Sb, Pb)
+        blank = np.zeros(pad["_size"], dtype=np.int32)      # an all-padding batch: every row skipped
+        blank[pad["positions"]:pad["positions"] + Sb] = -1
+        for gi in range(len(self.cache.groups)):
+            blank[pad[f"slots{gi}"]:pad[f"slots{gi}"] + Sb] = -1
+            blank[pad[f"tables{gi}"]:pad[f"tables{gi}"] + Sb * Pb] = -1
+        blank[pad["row_seq"]:pad["row_seq"] + Sb] = np.arange(Sb)
+        blank[pad["want"]:pad["want"] + Sb] = np.arange(Sb)
+        meta.copy_(torch.from_numpy(blank))
+        sampled = torch.zeros(Sb, dtype=torch.int32, device=self.device)
+
+        def run():
+            logits = self.model.forward(ctx)
+            kernels.sample(logits, sampled, ctx.temperature, ctx.uniform)
+            return logits
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()                                            # warm-up: allocates scratch
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = kernels.launch_count
+        with torch.cuda.graph(graph):
+            logits = run()
+        g = {"graph": graph, "meta": meta, "logits": logits, "sampled": sampled, "ctx": ctx,
+             "nodes": kernels.launch_count - before}
+        self._graphs[key] = g
+        return g
+
     @property
     def max_position(self) -> int:
         return self.config.max_position
 
+    def sampling_inputs(self, n_want: int, rows: Sequence[int], samplers):
+        """(temperatures, uniforms) per wanted row for the device kernel; rows whose sampler needs
+        the host path, and rows that are not sampled, get temperature 0 (their argmax is unused)."""
+        temps = np.zeros(n_want, dtype=np.float32)
+        unif = np.zeros(n_want, dtype=np.float32)
+        for r, s in zip(rows, samplers):
+            if not s.config.needs_host and not s.config.greedy:
+                temps[r] = s.config.temperature
+                unif[r] = s.uniform()
+        return temps, unif
+
     def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers, contexts) -> List[int]:
         """Next token for ``logits[rows[i]]`` under ``samplers[i]``. Greedy and plain temperature
         sampling run in the device kernel (the random number comes from the request's own
-        generator); requests with further filters are sampled on the host from a copy of the row."""
+        generator); requests with further filters are sampled on the host from a copy of the row.
+        If the step already ran the kernel (``step(..., sampling=...)``), its result is read."""
         w = logits.shape[0]
-        temps = np.zeros(w, dtype=np.float32)
-        unif = np.zeros(w, dtype=np.float32)
-        host_rows = []
-        for r, s in zip(rows, samplers):
-            if s.config.needs_host:
-                host_rows.append(r)
-            elif not s.config.greedy:
-                temps[r] = s.config.temperature
-                unif[r] = s.uniform()
-        params = torch.from_numpy(np.stack([temps, unif])).to(self.device, non_blocking=True)
-        out = self.scratch.get("sampled", (w, 1), torch.int32, grow=True).view(-1)
-        kernels.sample(logits, out, params[0], params[1])
-        picked = out.cpu().numpy()
+        if self.sampled is None or self.sampled.shape[0] != w:
+            temps, unif = self.sampling_inputs(w, rows, samplers)
+            params = torch.from_numpy(np.stack([temps, unif])).to(self.device, non_blocking=True)
+            self.sampled = self.scratch.get("sampled", (w, 1), torch.int32, grow=True).view(-1)
+            kernels.sample(logits, self.sampled, params[0], params[1])
+        picked = self.sampled.cpu().numpy()
+        self.sampled = None
         result = []
         for r, s, ctx_tokens in zip(rows, samplers, contexts):
             if s.config.needs_host:

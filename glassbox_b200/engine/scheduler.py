@@ -224,15 +224,6 @@ class Scheduler:
             entries.append(StepEntry(s.id, s.tokens[s.computed:s.computed + n], [n - 1] if last else []))
             if last:
                 wants_for.append(i)
-        logits = self.backend.step(entries, reserve=False)
-
-        batch_desc = []
-        for i, n in plan:
-            s = self.running[i]
-            kind = "prefill" if (len(s.tokens) - s.computed > 1 or s.generated == 0) else "decode"
-            batch_desc.append((s.id, kind, n))
-            s.computed += n
-
         done = []
         rows, samplers, contexts = [], [], []
         for j, i in enumerate(wants_for):
@@ -243,6 +234,17 @@ class Scheduler:
             rows.append(j)
             samplers.append(s.sampler)
             contexts.append(s.tokens)
+        # The device kernel samples inside the step; its random numbers are drawn here, one per row.
+        sampling = self.backend.sampling_inputs(len(wants_for), rows, samplers) if rows else None
+        logits = self.backend.step(entries, reserve=False, sampling=sampling)
+
+        batch_desc = []
+        for i, n in plan:
+            s = self.running[i]
+            kind = "prefill" if (len(s.tokens) - s.computed > 1 or s.generated == 0) else "decode"
+            batch_desc.append((s.id, kind, n))
+            s.computed += n
+
         tokens = self.backend.sample(logits, rows, samplers, contexts) if rows else []
         now = time.perf_counter()
         for j, t in zip(rows, tokens):

@@ -75,7 +75,13 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+#: kernels launched through this module since import (graph replays add their node count)
+launch_count = 0
+
+
 def _call(name: str, *args) -> None:
+    global launch_count
+    launch_count += 1
     rc = getattr(lib(), name)(*args)
     if rc != 0:
         raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or f"{name} failed with code {rc}")

@@ -70,11 +70,13 @@ def model_dirs(tmp_path_factory):
     return get
 
 
-def sharpen(folder, out, qk=24.0, vo=4.0):
-    """Copy a model folder with q/k projections scaled so that attention is peaked (single keys
-    dominate the softmax instead of hundreds averaging out) and v/o scaled so that attention
-    dominates the logits. A fault in which key a row reads, or from which page, then moves the
-    logits by far more than any tolerance."""
+def sharpen(folder, out, qk=12.0, vo=4.0):
+    """Copy a model folder with q/k projections scaled so that attention is peaked (about ten keys
+    carry the softmax, the best one a fifth of it, instead of hundreds averaging out) and v/o scaled
+    so that attention dominates the logits. A fault in which key a row reads, or from which page,
+    then moves the logits by far more than any tolerance. Scaling further (24) makes the softmax so
+    steep that float32 rounding of the scores alone moves logits by more than 1e-4, which would
+    test the conditioning of the crafted model and not the engine."""
     import shutil
     from safetensors.torch import load_file, save_file
     os.makedirs(out, exist_ok=True)

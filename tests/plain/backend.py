@@ -30,7 +30,10 @@ class PlainBackend:
     def reserve(self, rid, n):
         self.cache.reserve(rid, n)
 
-    def step(self, entries, reserve=True):
+    def sampling_inputs(self, n_want, rows, samplers):
+        return None
+
+    def step(self, entries, reserve=True, sampling=None):
         rows = []
         self.step_log.append([(e.request, len(e.tokens), list(e.want)) for e in entries])
         for e in entries:
