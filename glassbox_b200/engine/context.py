@@ -54,10 +54,25 @@ class Scratch:
             return buf[:rows]
         return buf.view(-1)[:rows * width].view(rows, width)
 
+    def zeros_once(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
+        """A flat buffer that is zero when first handed out and is never cleared again: for kernels
+        that leave their counters at zero when they finish."""
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < count:
+            buf = torch.zeros(count, dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf
+
 
 class StepContext:
-    def __init__(self, *, scratch: Scratch, cache: DeviceCache, status: torch.Tensor, dtype: torch.dtype):
+    def __init__(self, *, scratch: Scratch, cache: DeviceCache, status: torch.Tensor, dtype: torch.dtype,
+                 grow_scratch: Optional[Scratch] = None):
         self._scratch = scratch
+        # Buffers whose size depends on the step (logits, split-attention partials) may be replaced by
+        # larger ones later. A context that is recorded into a CUDA graph therefore owns its own set:
+        # the graph keeps writing to the addresses it was recorded with.
+        self._grow = grow_scratch if grow_scratch is not None else scratch
         self.cache = cache
         self.status = status
         self.dtype = dtype
@@ -76,7 +91,14 @@ class StepContext:
         self.temperature = self.uniform = None
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
-        return self._scratch.get(name, shape, dtype, grow)
+        return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)
+
+    def zeros_once(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
+        return self._scratch.zeros_once(name, count, dtype)
+
+    @property
+    def max_rows(self) -> int:
+        return self._scratch.max_rows
 
     def cache_view(self, cache_layer: int):
         view = self.cache.layer_view(cache_layer)

@@ -288,7 +288,7 @@ class Engine:
             self._bind(ctx, self._meta_dev, off, n, S, n_want, max_pages)
             ctx.seqs, ctx.max_context = self._seqs, self._max_ctx
             ctx.max_rows_per_seq = max(s.n_rows for s in self._seqs)
-            ctx.decode_only = False
+            ctx.decode_only = (n == S)
             logits = self.model.forward(ctx)
             if sampling is not None and n_want:
                 self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
@@ -322,7 +322,8 @@ class Engine:
         kernels once outside capture so that every scratch buffer exists, then records them."""
         Sb, Pb = key
         meta = torch.empty(off["_size"], dtype=torch.int32, device=self.device)
-        ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype)
+        ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype,
+                          grow_scratch=Scratch(self.max_batch_tokens, self.dtype, self.device))
         self._bind(ctx, meta, off, Sb, Sb, Sb, Pb)
         ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(Sb)]
         ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, 1, True

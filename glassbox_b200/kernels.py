@@ -40,6 +40,9 @@ _SIGNATURES = {
     "gb_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _LL, _LL, _LL, _P],
     "gb_attention_rows": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_sample": [_P, _LL, _P, _P, _P, _I, _I, _P],
+    "gb_attention_decode": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
+                            _P, _P, _P],
+    "gb_attention_decode_counters": [_I, _I, _I],
 }
 
 
@@ -192,6 +195,38 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vca
     _call("gb_attention_rows", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _dt(q), _ptr(kcache), _ptr(vcache),
           _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
           kcache.shape[0], float(scale), int(window or 0), _ptr(status), _stream())
+
+
+DECODE_KEYS_PER_TILE = 64
+
+
+def decode_splits(n: int, nh: int, nkv: int, max_context: int, target_blocks: int = 148 * 4) -> int:
+    """How many blocks share the keys of one (row, kv head): enough to fill the GPU, never more than
+    there are 64-key tiles. Depends on the batch shape only, so a captured graph can fix it."""
+    per_split = lib().gb_attention_decode_counters(n, nh, nkv)
+    tiles = max(1, -(-max_context // DECODE_KEYS_PER_TILE))
+    return max(1, min(-(-target_blocks // max(per_split, 1)), tiles))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                     block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int,
+                     hd: int, page_size: int, scale: float, window: Optional[int], splits: int,
+                     part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
+                     counters: Optional[torch.Tensor], status: torch.Tensor) -> None:
+    """Split-key attention for rows with few queries per request. Scratch (needed when splits > 1):
+    part_acc float32 [n, nh, splits, hd], part_ml float32 [n, nh, splits, 2], counters int32
+    [gb_attention_decode_counters(n, nh, nkv)] that are zero on entry and left zero."""
+    _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, part_acc, part_ml, counters, status)
+    n = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == kcache.dtype
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    if splits > 1:
+        assert part_acc.numel() >= n * nh * splits * hd and part_ml.numel() >= n * nh * splits * 2
+        assert counters.numel() >= lib().gb_attention_decode_counters(n, nh, nkv)
+    _call("gb_attention_decode", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _dt(q), _ptr(kcache), _ptr(vcache),
+          _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
+          kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml),
+          _ptr(counters), _ptr(status), _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

@@ -9,6 +9,8 @@ this run are not stored and attention reads what the named cache layer already h
 """
 from __future__ import annotations
 
+import torch
+
 from .. import kernels
 from ..weights.binding import ParamSpec
 from .base import Mixer, PagedKvSpec, build_part, register_part
@@ -56,7 +58,21 @@ class GqaAttention(Mixer):
 
 
     def attend(self, ctx, q, att, cache) -> None:
-        """att[row, head, :] = softmax over the row's visible keys; picks the kernel by batch shape."""
+        """att[row, head, :] = softmax over the row's visible keys; the kernel is picked by the shape
+        of the batch: rows that are single decoded tokens share the keys of a request between
+        several blocks; anything else takes the one-warp-per-(row, head) kernel."""
+        n = q.shape[0]
+        if ctx.decode_only and self.hd % 16 == 0 and self.hd >= 16:
+            splits = kernels.decode_splits(n, self.nh, self.nkv, ctx.max_context)
+            part_acc = part_ml = counters = None
+            if splits > 1:
+                part_acc = ctx.scratch("decode_part_acc", (n, self.nh * splits * self.hd), torch.float32, grow=True)
+                part_ml = ctx.scratch("decode_part_ml", (n, self.nh * splits * 2), torch.float32, grow=True)
+                counters = ctx.zeros_once("decode_counters", ctx.max_rows * self.nh, torch.int32)
+            kernels.attention_decode(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
+                                     self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window,
+                                     splits, part_acc, part_ml, counters, ctx.status)
+            return
         kernels.attention_rows(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.nh,
                                self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window, ctx.status)
 

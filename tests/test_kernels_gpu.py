@@ -1,0 +1,336 @@
+"""Each CUDA kernel alone against a plain float32/float64 PyTorch statement of the same operation, at
+sizes other than the engine's: awkward lengths, head sizes in steps of 16, any number of heads and
+groups, widths and vocabularies that are no power of two (after the method of
+crates/glassbox-core/src/kernels.rs:675-720)."""
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n, d, vocab", [(1, 16, 7), (5, 576, 301), (33, 100, 49153)])
+def test_embed(dtype, n, d, vocab):
+    from glassbox_b200 import kernels
+    table = torch.randn(vocab, d, device=DEV).to(dtype)
+    toks = torch.randint(0, vocab, (n,), device=DEV, dtype=torch.int32)
+    x = torch.empty(n, d, device=DEV)
+    st = status()
+    kernels.embed(table, toks, x, st)
+    assert torch.equal(x, table[toks.long()].float()) and int(st) == 0
+    toks[0] = vocab
+    kernels.embed(table, toks, x, st)
+    assert int(st) == 1 and float(x[0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n, d, eps", [(1, 7, 1e-5), (3, 576, 1e-6), (17, 1537, 3e-6), (9, 8192, 1e-5)])
+def test_rmsnorm(dtype, n, d, eps):
+    from glassbox_b200 import kernels
+    x = torch.randn(n + 3, d, device=DEV) * 3
+    gain = 1 + 0.1 * torch.randn(d, device=DEV)
+    rows = torch.randperm(n + 3, device=DEV)[:n].to(torch.int32)
+    out = torch.empty(n, d, device=DEV, dtype=dtype)
+    kernels.rmsnorm(x, gain, out, eps, rows)
+    xs = x[rows.long()].double()
+    ref = gain.double() * (xs / torch.sqrt((xs * xs).mean(-1, keepdim=True) + eps))
+    assert (out.double() - ref).abs().max() <= tol(dtype, 4)
+    out2 = torch.empty(n + 3, d, device=DEV, dtype=dtype)
+    kernels.rmsnorm(x, gain, out2, eps)
+    assert torch.equal(out2[rows.long()], out)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n, inter", [(1, 1), (3, 176), (17, 1537)])
+def test_swiglu(dtype, n, inter):
+    from glassbox_b200 import kernels
+    gu = (torch.randn(n, 2 * inter, device=DEV) * 2).to(dtype)
+    act = torch.empty(n, inter, device=DEV, dtype=dtype)
+    kernels.swiglu(gu, act)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert (act.double() - ref).abs().max() <= tol(dtype, 4)
+
+
+@pytest.mark.parametrize("a_dt, w_dt, c_dt", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                              (torch.bfloat16, torch.bfloat16, torch.float32),
+                                              (torch.bfloat16, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("M, N, K", [(1, 32, 32), (1, 7, 1537), (2, 100, 33), (3, 960, 576), (8, 17, 31),
+                                     (9, 65, 63), (17, 160, 50), (70, 130, 100), (128, 49, 576)])
+def test_gemm_simt(a_dt, w_dt, c_dt, M, N, K):
+    from glassbox_b200 import kernels
+    a = torch.randn(M, K, device=DEV).to(a_dt)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(w_dt)
+    c = torch.empty(M, N, device=DEV, dtype=c_dt)
+    kernels.gemm_simt(a, w, c)
+    ref = a.double() @ w.double().T
+    assert (c.double() - ref).abs().max() <= tol(c_dt, 2)
+    if c_dt == torch.float32:
+        base = torch.randn(M, N, device=DEV)
+        c2 = base.clone()
+        kernels.gemm_simt(a, w, c2, accumulate=True)
+        assert (c2.double() - (base.double() + ref)).abs().max() <= tol(c_dt, 2)
+    # strided operands: a and c are column slices of wider buffers (as q inside qkv)
+    wide_a = torch.randn(M, K + 8, device=DEV).to(a_dt)
+    wide_c = torch.zeros(M, N + 5, device=DEV, dtype=c_dt)
+    kernels.gemm_simt(wide_a[:, 8:], w, wide_c[:, :N])
+    assert (wide_c[:, :N].double() - wide_a[:, 8:].double() @ w.double().T).abs().max() <= tol(c_dt, 2)
+    assert float(wide_c[:, N:].abs().max()) == 0.0
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    """The float32 product of a row is bit-identical whatever else is in the batch (same kernel)."""
+    from glassbox_b200 import kernels
+    a = torch.randn(8, 576, device=DEV)
+    w = torch.randn(200, 576, device=DEV)
+    full = torch.empty(8, 200, device=DEV)
+    kernels.gemm_simt(a, w, full)
+    for m in (1, 3):
+        part = torch.empty(m, 200, device=DEV)
+        kernels.gemm_simt(a[:m].contiguous(), w, part)
+        assert torch.equal(part, full[:m])
+
+
+def make_cache(dtype, n_seqs, lens, nkv, hd, page_size, extra_pages=3, seed=0):
+    """Random K/V scattered over shuffled pages; returns cache tensors, tables, and dense copies."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    pages_per = [-(-l // page_size) for l in lens]
+    num_pages = sum(pages_per) + extra_pages
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    k = torch.randn(num_pages, nkv, page_size, hd, generator=g).to(dtype)
+    v = torch.randn(num_pages, nkv, page_size, hd, generator=g).to(dtype)
+    max_pages = max(pages_per) + 1
+    tables = torch.full((n_seqs, max_pages), -1, dtype=torch.int32)
+    dense = []
+    at = 0
+    for s, l in enumerate(lens):
+        ids = perm[at:at + pages_per[s]]
+        at += pages_per[s]
+        tables[s, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+        kk = torch.cat([k[p] for p in ids], dim=1)[:, :l].double()      # [nkv, l, hd]
+        vv = torch.cat([v[p] for p in ids], dim=1)[:, :l].double()
+        dense.append((kk, vv))
+    return k.to(DEV), v.to(DEV), tables.to(DEV), dense
+
+
+def ref_attention(q, dense, row_seq, positions, nh, nkv, scale, window):
+    out = torch.zeros(q.shape[0], nh, q.shape[-1], dtype=torch.float64)
+    group = nh // nkv
+    for r in range(q.shape[0]):
+        kk, vv = dense[row_seq[r]]
+        p = positions[r]
+        lo = max(0, p + 1 - window) if window else 0
+        for h in range(nh):
+            s = (kk[h // group, lo:p + 1] @ q[r, h].double()) * scale
+            out[r, h] = torch.softmax(s, dim=0) @ vv[h // group, lo:p + 1]
+    return out
+
+
+ATT_CASES = [  # nh, nkv, hd, page_size, window, lens
+    (4, 2, 16, 16, None, [5, 17, 33]),
+    (3, 1, 32, 16, None, [1, 100, 64, 257]),
+    (5, 5, 48, 16, 37, [300, 48, 17]),
+    (9, 3, 64, 32, None, [700, 65]),
+    (12, 2, 80, 16, 100, [130, 250]),       # six query heads per kv head: two sub-groups
+    (2, 1, 256, 64, None, [129]),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATT_CASES)
+def test_attention_rows(dtype, case):
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps, window, lens = case
+    k, v, tables, dense = make_cache(dtype, len(lens), lens, nkv, hd, ps)
+    rng = random.Random(1)
+    row_seq, positions = [], []
+    for s, l in enumerate(lens):                       # several rows per sequence, anywhere in it
+        for p in sorted({0, l - 1, l // 2, rng.randrange(l), min(l - 1, ps - 1), min(l - 1, ps)}):
+            row_seq.append(s)
+            positions.append(p)
+    n = len(row_seq)
+    q = torch.randn(n, nh, hd).to(dtype)
+    qd = q.to(DEV).reshape(n, nh * hd)
+    out = torch.empty(n, nh * hd, device=DEV, dtype=dtype)
+    st = status()
+    kernels.attention_rows(qd, out, k, v, tables, torch.tensor(row_seq, dtype=torch.int32, device=DEV),
+                           torch.tensor(positions, dtype=torch.int32, device=DEV), nh, nkv, hd, ps, hd ** -0.5, window, st)
+    ref = ref_attention(q, dense, row_seq, positions, nh, nkv, hd ** -0.5, window)
+    assert int(st) == 0
+    assert (out.cpu().double().reshape(n, nh, hd) - ref).abs().max() <= tol(dtype, 2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [1, 2, 5, 40])
+@pytest.mark.parametrize("case", ATT_CASES)
+def test_attention_decode(dtype, case, splits):
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps, window, lens = case
+    k, v, tables, dense = make_cache(dtype, len(lens), lens, nkv, hd, ps, seed=2)
+    n = len(lens) + 1                                      # one row per sequence, plus a padding row
+    row_seq = list(range(len(lens))) + [0]
+    positions = [l - 1 for l in lens] + [-1]
+    q = torch.randn(n, nh, hd).to(dtype)
+    out = torch.full((n, nh * hd), 7.0, device=DEV, dtype=dtype)
+    part_acc = torch.empty(n * nh * splits * hd, device=DEV)
+    part_ml = torch.empty(n * nh * splits * 2, device=DEV)
+    counters = torch.zeros(n * nh, dtype=torch.int32, device=DEV)
+    st = status()
+    for _ in range(2):                                     # twice: the counters must come back to zero
+        kernels.attention_decode(q.to(DEV).reshape(n, nh * hd), out, k, v, tables,
+                                 torch.tensor(row_seq, dtype=torch.int32, device=DEV),
+                                 torch.tensor(positions, dtype=torch.int32, device=DEV), nh, nkv, hd, ps, hd ** -0.5,
+                                 window, splits, part_acc, part_ml, counters, st)
+        ref = ref_attention(q[:-1], dense, row_seq[:-1], positions[:-1], nh, nkv, hd ** -0.5, window)
+        got = out.cpu().double().reshape(n, nh, hd)
+        assert int(st) == 0 and int(counters.abs().max()) == 0
+        assert (got[:-1] - ref).abs().max() <= tol(dtype, 2)
+        assert float(got[-1].abs().max()) == 0.0            # the padding row is zeroed, nothing else
+        out.fill_(7.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_one_far_key_stands_out(dtype):
+    """Among hundreds of keys one far key's score stands out by 30: the output must be its value,
+    through either kernel, wherever the page boundary falls."""
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps = 2, 1, 64, 16
+    for far in (0, 15, 16, 250, 499):
+        L = 500
+        k, v, tables, dense = make_cache(dtype, 1, [L], nkv, hd, ps, seed=far)
+        q = torch.zeros(1, nh, hd)
+        kk, vv = dense[0]
+        q[0, :] = (kk[0, far] / kk[0, far].norm() ** 2 * 60.0 * 8.0).float()   # score 60 at `far`, ~N(0, 8) elsewhere
+        q = q.to(dtype)
+        ref = ref_attention(q, dense, [0], [L - 1], nh, nkv, hd ** -0.5, None)
+        assert (ref[0, 0] - vv[0, far]).abs().max() < 1e-3, "the crafted score does not dominate"
+        args = (k, v, tables, torch.zeros(1, dtype=torch.int32, device=DEV),
+                torch.tensor([L - 1], dtype=torch.int32, device=DEV), nh, nkv, hd, ps, hd ** -0.5, None)
+        out = torch.empty(1, nh * hd, device=DEV, dtype=dtype)
+        kernels.attention_rows(q.to(DEV).reshape(1, -1), out, *args, status())
+        assert (out.cpu().double().reshape(nh, hd) - ref[0]).abs().max() <= tol(dtype, 2)
+        splits = 4
+        kernels.attention_decode(q.to(DEV).reshape(1, -1), out, *args, splits, torch.empty(nh * splits * hd, device=DEV),
+                                 torch.empty(nh * splits * 2, device=DEV), torch.zeros(nh, dtype=torch.int32, device=DEV),
+                                 status())
+        assert (out.cpu().double().reshape(nh, hd) - ref[0]).abs().max() <= tol(dtype, 2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh, nkv, hd, rot, ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 16), (5, 5, 48, 24, 32), (9, 3, 64, 64, 16)])
+def test_rope_and_cache_write(dtype, nh, nkv, hd, rot, ps):
+    from glassbox_b200 import kernels
+    from glassbox_b200.parts.rope import rotary_table
+    from plain.llama_plain import rope_angles
+    n, max_pos, pages = 11, 300, 9
+    table = rotary_table(123456.0, rot, max_pos).to(DEV)
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd).to(dtype)
+    positions = torch.tensor([0, 1, 2, 17, 299, 150, 31, 32, 33, -1, 64], dtype=torch.int32)
+    slots = torch.tensor([5, 0, 143, 17, 100, 33, 64, 65, 66, -1, 1], dtype=torch.int32)
+    kc = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    dev = qkv.to(DEV).clone()
+    st = status()
+    kernels.rope_kv_write(dev, table, positions.to(DEV), slots.to(DEV), kc, vc, nh, nkv, hd, rot, ps, True, st)
+    assert int(st) == 0
+    got = dev.cpu().double()
+    cos, sin = rope_angles(positions.clamp(min=0).numpy(), rot, float(np.float32(123456.0)))
+    src = qkv.double()
+    for r in range(n):
+        if positions[r] < 0:                                # padding row: untouched, nothing stored
+            assert torch.equal(got[r], src[r])
+            continue
+        heads = src[r, :(nh + nkv) * hd].reshape(nh + nkv, hd).clone()
+        x0, x1 = heads[:, :rot // 2].clone(), heads[:, rot // 2:rot].clone()
+        c, s = torch.from_numpy(cos[r]), torch.from_numpy(sin[r])
+        heads[:, :rot // 2] = x0 * c - x1 * s
+        heads[:, rot // 2:rot] = x1 * c + x0 * s
+        assert (got[r, :(nh + nkv) * hd].reshape(nh + nkv, hd) - heads).abs().max() <= tol(dtype, 4)
+        page, off = int(slots[r]) // ps, int(slots[r]) % ps
+        assert (kc[page, :, off].cpu().double() - heads[nh:]).abs().max() <= tol(dtype, 4)
+        assert torch.equal(vc[page, :, off].cpu(), qkv[r, (nh + nkv) * hd:].reshape(nkv, hd))
+    written = {int(s) for s, p in zip(slots, positions) if p >= 0}
+    mask = torch.ones(pages * ps, dtype=torch.bool)
+    mask[list(written)] = False
+    assert float(kc.permute(0, 2, 1, 3).reshape(pages * ps, -1)[mask.to(DEV)].abs().max()) == 0.0
+    # bad indices are recorded and skipped, never followed
+    bad = status()
+    kernels.rope_kv_write(dev, table, torch.full((n,), 300, dtype=torch.int32, device=DEV), slots.to(DEV).abs(), kc, vc,
+                          nh, nkv, hd, rot, ps, True, bad)
+    assert int(bad) & 4
+    bad.zero_()
+    kernels.rope_kv_write(dev, table, positions.to(DEV).clamp(min=0), torch.full((n,), pages * ps, dtype=torch.int32, device=DEV),
+                          kc, vc, nh, nkv, hd, rot, ps, True, bad)
+    assert int(bad) & 2
+
+
+@pytest.mark.parametrize("vocab", [5, 256, 49152, 50001])
+def test_sampling(vocab):
+    from glassbox_b200 import kernels
+    from plain import sampler_plain
+    rows = 6
+    g = torch.Generator().manual_seed(vocab)
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    logits[1, vocab // 2] = logits[1].max() + 1
+    logits[2, 3] = logits[2, vocab - 1] = logits[2].max() + 2          # a tie: the first index wins
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    kernels.sample(logits.to(DEV), out)
+    assert out.tolist() == [int(torch.argmax(r)) for r in logits] and out[2] == 3
+    temps = torch.tensor([0.0, 0.8, 1.0, 1.7, 0.3, 1.0])
+    for trial in range(20):
+        unif = torch.rand(rows, generator=g)
+        kernels.sample(logits.to(DEV), out, temps.to(DEV), unif.to(DEV))
+        for r in range(rows):
+            dist = sampler_plain.distribution(logits[r].tolist(), [], temperature=float(temps[r]))
+            want = sampler_plain.draw(dist, float(unif[r]))
+            if int(out[r]) != want:                     # only an edge of the cumulative sum may differ
+                acc = 0.0
+                for t in sorted(dist):
+                    acc += dist[t]
+                    if t in (int(out[r]), want):
+                        assert abs(acc - float(unif[r])) < 1e-4 or abs(acc - dist[t] - float(unif[r])) < 1e-4
+                        break
+
+
+def test_copy_pages():
+    from glassbox_b200 import kernels
+    k = torch.randn(3, 10, 2, 16, 48, device=DEV).to(torch.bfloat16)
+    v = torch.randn_like(k)
+    k0, v0 = k.clone(), v.clone()
+    kernels.copy_pages(k, v, torch.tensor([[1, 7], [4, 0]], dtype=torch.int32, device=DEV))
+    for src, dst in ((1, 7), (4, 0)):
+        assert torch.equal(k[:, dst], k0[:, src]) and torch.equal(v[:, dst], v0[:, src])
+    keep = [p for p in range(10) if p not in (7, 0)]
+    assert torch.equal(k[:, keep], k0[:, keep])
+
+
+def test_sizes_outside_the_kernels_range_are_refused():
+    from glassbox_b200 import kernels
+    q = torch.zeros(1, 2 * 24, device=DEV)
+    kc = torch.zeros(4, 1, 16, 24, device=DEV)
+    with pytest.raises(kernels.KernelError, match="multiple of 16"):
+        kernels.attention_decode(q, q.clone(), kc, kc, torch.zeros(1, 4, dtype=torch.int32, device=DEV),
+                                 torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                                 2, 1, 24, 16, 1.0, None, 1, None, None, None, status())
+    with pytest.raises(kernels.KernelError, match="multiple"):
+        kernels.attention_rows(torch.zeros(1, 3 * 16, device=DEV), torch.zeros(1, 3 * 16, device=DEV),
+                               torch.zeros(4, 2, 16, 16, device=DEV), torch.zeros(4, 2, 16, 16, device=DEV),
+                               torch.zeros(1, 4, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                               torch.zeros(1, dtype=torch.int32, device=DEV), 3, 2, 16, 16, 1.0, None, status())
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_simt(torch.zeros(2, 4), torch.zeros(3, 4), torch.zeros(2, 3))      # CPU tensors: no CPU path
