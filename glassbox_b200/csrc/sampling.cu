@@ -26,13 +26,12 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     __shared__ int s_idx[SAMPLE_THREADS];
     __shared__ float s_pref[SAMPLE_THREADS + 1];
 
-    // Maximum and its first index. Threads own ascending runs, so "lowest thread wins ties" is
-    // "first index wins".
+    // Maximum and its first index: coalesced strided reads, ties go to the lower index.
     float best = -FLT_MAX;
     int best_i = vocab;
-    for (int i = lo; i < hi; ++i) {
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
         float v = l[i];
-        if (best_i == vocab || v > best) { best = v; best_i = i; }
+        if (best_i == vocab || v > best) { best = v; best_i = i; }   // i ascends, so ties keep the lower index
     }
     s_val[tid] = best;
     s_idx[tid] = best_i;

@@ -43,6 +43,10 @@ _SIGNATURES = {
     "gb_attention_decode": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                             _P, _P, _P],
     "gb_attention_decode_counters": [_I, _I, _I],
+    "gb_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P],
+    "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
+                                _P, _P],
+    "gb_attention_decode_mma_supported": [_I, _I, _I],
 }
 
 
@@ -179,6 +183,35 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
           a.stride(0), w.stride(0), c.stride(0), _stream())
 
 
+STREAM_MAX_ROWS = 64
+
+
+def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel (few rows, bfloat16) takes these operands."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= STREAM_MAX_ROWS
+            and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, gated: bool = False) -> None:
+    """c[M, N] (+)= a[M, K] @ w[N, K]^T for M <= 64 on the tensor cores, streaming w once. With
+    ``gated``, w is [2I, K] (gate rows, then up rows) and c[M, I] = silu(a gate^T) * (a up^T)."""
+    _cuda(a, w, c)
+    M, K = a.shape
+    N = w.shape[0] // 2 if gated else w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    if gated:
+        assert c.dtype == torch.bfloat16 and not accumulate
+        mode = 3
+    elif accumulate:
+        assert c.dtype == torch.float32
+        mode = 2
+    else:
+        mode = 0 if c.dtype == torch.bfloat16 else 1
+        assert c.dtype in (torch.bfloat16, torch.float32)
+    _call("gb_gemm_stream", _ptr(a), _ptr(w), _ptr(c), mode, M, N, K, a.stride(0), w.stride(0), c.stride(0), _stream())
+
+
 def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:
     """Whether the tensor-core kernel takes these operands."""
     return False
@@ -227,6 +260,40 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
           _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
           kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml),
           _ptr(counters), _ptr(status), _stream())
+
+
+def attention_decode_mma_supported(dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int = 16) -> bool:
+    return (dtype == torch.bfloat16 and page_size >= 16 and page_size & (page_size - 1) == 0
+            and bool(lib().gb_attention_decode_mma_supported(nh, nkv, hd)))
+
+
+def decode_mma_splits(n: int, nkv: int, hd: int, max_context: int) -> int:
+    """Blocks per (row, kv head) for the tensor-core decode kernel: enough to give every SM a block,
+    but each block keeps at least 512 keys (128 per warp), below which the fixed cost of a block
+    and of the merge outweighs the extra parallelism. Depends on the batch shape and the longest
+    context the step allows, never on the data, so a captured graph can fix it."""
+    most = max(1, -(-max_context // 512))
+    return max(1, min(-(-148 // max(n * nkv, 1)), most))
+
+
+def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                         block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int,
+                         hd: int, page_size: int, scale: float, window: Optional[int], splits: int,
+                         part_acc: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
+                         status: torch.Tensor) -> None:
+    """bfloat16 split-key decode attention on the tensor cores. Scratch: part_acc float32
+    [n, nh, 4*splits, hd], part_ml float32 [n, nh, 4*splits, 2], counters int32 [n*nkv], zero on entry
+    and left zero."""
+    _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, part_acc, part_ml, counters, status)
+    n = q.shape[0]
+    assert q.dtype == out.dtype == kcache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    assert part_acc.numel() >= n * nh * 4 * splits * hd and part_ml.numel() >= n * nh * 4 * splits * 2
+    assert counters.numel() >= n * nkv
+    _call("gb_attention_decode_mma", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
+          _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
+          kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml), _ptr(counters),
+          _ptr(status), _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

@@ -60,8 +60,18 @@ class GqaAttention(Mixer):
     def attend(self, ctx, q, att, cache) -> None:
         """att[row, head, :] = softmax over the row's visible keys; the kernel is picked by the shape
         of the batch: rows that are single decoded tokens share the keys of a request between
-        several blocks; anything else takes the one-warp-per-(row, head) kernel."""
+        several blocks (on the tensor cores in bfloat16 where the head size is one the kernel is built
+        for, else with float32 FMA); anything else takes the one-warp-per-(row, head) kernel."""
         n = q.shape[0]
+        if ctx.decode_only and kernels.attention_decode_mma_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size):
+            splits = kernels.decode_mma_splits(n, self.nkv, self.hd, ctx.max_context)
+            part_acc = ctx.scratch("decode_part_acc", (n, self.nh * 4 * splits * self.hd), torch.float32, grow=True)
+            part_ml = ctx.scratch("decode_part_ml", (n, self.nh * 4 * splits * 2), torch.float32, grow=True)
+            counters = ctx.zeros_once("decode_counters", ctx.max_rows * self.nh, torch.int32)
+            kernels.attention_decode_mma(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
+                                         self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale,
+                                         self.spec.window, splits, part_acc, part_ml, counters, ctx.status)
+            return
         if ctx.decode_only and self.hd % 16 == 0 and self.hd >= 16:
             splits = kernels.decode_splits(n, self.nh, self.nkv, ctx.max_context)
             part_acc = part_ml = counters = None

@@ -6,7 +6,7 @@ from __future__ import annotations
 from .. import kernels
 from ..weights.binding import ParamSpec
 from .base import FeedForward, register_part
-from .linear import linear
+from .linear import gated_linear, linear
 
 
 class SwiGlu(FeedForward):
@@ -21,10 +21,11 @@ class SwiGlu(FeedForward):
 
     def forward(self, ctx, h, residual) -> None:
         n = h.shape[0]
-        gate_up = ctx.scratch("gate_up", (n, 2 * self.inter))
-        linear(ctx, h, self.params["w_gate_up"], gate_up)
         act = ctx.scratch("act", (n, self.inter))
-        kernels.swiglu(gate_up, act)
+        if not gated_linear(ctx, h, self.params["w_gate_up"], act):
+            gate_up = ctx.scratch("gate_up", (n, 2 * self.inter))
+            linear(ctx, h, self.params["w_gate_up"], gate_up)
+            kernels.swiglu(gate_up, act)
         linear(ctx, act, self.params["w_down"], residual, accumulate=True)
 
 

@@ -334,3 +334,117 @@ def test_sizes_outside_the_kernels_range_are_refused():
                                torch.zeros(1, dtype=torch.int32, device=DEV), 3, 2, 16, 16, 1.0, None, status())
     with pytest.raises(kernels.KernelError):
         kernels.gemm_simt(torch.zeros(2, 4), torch.zeros(3, 4), torch.zeros(2, 3))      # CPU tensors: no CPU path
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 31, 33, 64])
+@pytest.mark.parametrize("N, K", [(16, 8), (100, 40), (576, 576), (960, 264), (49, 1544), (3072, 576)])
+def test_gemm_stream(M, N, K):
+    from glassbox_b200 import kernels
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    assert kernels.gemm_stream_supported(a, w)
+    ref = a.double() @ w.double().T
+    c = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_stream(a, w, c)
+    assert (c.double() - ref).abs().max() <= tol(torch.bfloat16, 2)
+    c32 = torch.empty(M, N, device=DEV)
+    kernels.gemm_stream(a, w, c32)
+    assert (c32.double() - ref).abs().max() <= 2e-5 * math.sqrt(K)
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    kernels.gemm_stream(a, w, acc, accumulate=True)
+    assert (acc.double() - base.double() - ref).abs().max() <= 2e-5 * math.sqrt(K)
+    # the same row gives the same bits whatever else is in the batch
+    one = torch.empty(1, N, device=DEV)
+    kernels.gemm_stream(a[:1], w, one)
+    assert torch.equal(one[0], c32[0])
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 24, 64])
+@pytest.mark.parametrize("inter, K", [(16, 16), (176, 64), (1536, 576), (48, 1000)])
+def test_gemm_stream_gated(M, inter, K):
+    from glassbox_b200 import kernels
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, device=DEV) * (2.0 / math.sqrt(K))).to(torch.bfloat16)
+    act = torch.empty(M, inter, device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_stream(a, w, act, gated=True)
+    gu = a.double() @ w.double().T
+    g, u = gu[:, :inter], gu[:, inter:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert ((act.double() - ref).abs() / (1 + ref.abs())).max() <= tol(torch.bfloat16, 1)   # relative: values reach ~10
+
+
+def test_gemm_stream_refuses_what_it_cannot_do():
+    from glassbox_b200 import kernels
+    a = torch.zeros(65, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(32, 64, device=DEV, dtype=torch.bfloat16)
+    assert not kernels.gemm_stream_supported(a, w)
+    assert not kernels.gemm_stream_supported(a[:4, :60], w[:, :60])
+    with pytest.raises(kernels.KernelError, match="M <= 64"):
+        kernels.gemm_stream(a, w, torch.zeros(65, 32, device=DEV))
+
+
+MMA_CASES = [  # nh, nkv, hd, page_size, window, lens
+    (4, 2, 16, 16, None, [5, 17, 33, 64]),
+    (3, 1, 32, 16, None, [1, 100, 64, 257]),
+    (9, 3, 64, 16, None, [700, 65, 31, 32, 33]),
+    (9, 3, 64, 32, 100, [700, 99, 100, 101]),
+    (32, 2, 64, 16, None, [300]),                # sixteen query heads per kv head
+    (5, 5, 128, 64, 37, [300, 48, 17]),
+    (2, 1, 128, 16, None, [129, 1000]),
+]
+
+
+@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("case", MMA_CASES)
+def test_attention_decode_mma(case, splits):
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps, window, lens = case
+    dtype = torch.bfloat16
+    assert kernels.attention_decode_mma_supported(dtype, nh, nkv, hd)
+    k, v, tables, dense = make_cache(dtype, len(lens), lens, nkv, hd, ps, seed=3)
+    n = len(lens) + 1
+    row_seq = list(range(len(lens))) + [0]
+    positions = [l - 1 for l in lens] + [-1]
+    q = torch.randn(n, nh, hd).to(dtype)
+    out = torch.full((n, nh * hd), 7.0, device=DEV, dtype=dtype)
+    part_acc = torch.empty(n * nh * 4 * splits * hd, device=DEV)
+    part_ml = torch.empty(n * nh * 4 * splits * 2, device=DEV)
+    counters = torch.zeros(n * nkv, dtype=torch.int32, device=DEV)
+    st = status()
+    ref = ref_attention(q[:-1], dense, row_seq[:-1], positions[:-1], nh, nkv, hd ** -0.5, window)
+    for _ in range(2):
+        kernels.attention_decode_mma(q.to(DEV).reshape(n, nh * hd), out, k, v, tables,
+                                     torch.tensor(row_seq, dtype=torch.int32, device=DEV),
+                                     torch.tensor(positions, dtype=torch.int32, device=DEV), nh, nkv, hd, ps, hd ** -0.5,
+                                     window, splits, part_acc, part_ml, counters, st)
+        got = out.cpu().double().reshape(n, nh, hd)
+        assert int(st) == 0 and int(counters.abs().max()) == 0
+        assert (got[:-1] - ref).abs().max() <= tol(dtype, 2)
+        assert float(got[-1].abs().max()) == 0.0
+        out.fill_(7.0)
+
+
+def test_attention_decode_mma_one_far_key_stands_out():
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps, dtype = 6, 2, 64, 16, torch.bfloat16
+    for far in (0, 15, 16, 31, 32, 250, 499):
+        L = 500
+        k, v, tables, dense = make_cache(dtype, 1, [L], nkv, hd, ps, seed=far)
+        kk, vv = dense[0]
+        q = torch.zeros(1, nh, hd)
+        for h in range(nh):                         # heads of kv head 0 look for `far`, of kv head 1 for far/2
+            target = far if h < 3 else far // 2
+            key = kk[h // 3, target]
+            q[0, h] = (key / key.norm() ** 2 * 60.0 * 8.0).float()
+        q = q.to(dtype)
+        ref = ref_attention(q, dense, [0], [L - 1], nh, nkv, hd ** -0.5, None)
+        assert (ref[0, 0] - vv[0, far]).abs().max() < 1e-3 and (ref[0, 5] - vv[1, far // 2]).abs().max() < 1e-3
+        out = torch.empty(1, nh * hd, device=DEV, dtype=dtype)
+        splits = 3
+        kernels.attention_decode_mma(q.to(DEV).reshape(1, -1), out, k, v, tables, torch.zeros(1, dtype=torch.int32, device=DEV),
+                                     torch.tensor([L - 1], dtype=torch.int32, device=DEV), nh, nkv, hd, ps, hd ** -0.5, None,
+                                     splits, torch.empty(nh * 4 * splits * hd, device=DEV),
+                                     torch.empty(nh * 4 * splits * 2, device=DEV),
+                                     torch.zeros(nkv, dtype=torch.int32, device=DEV), status())
+        assert (out.cpu().double().reshape(nh, hd) - ref[0]).abs().max() <= tol(dtype, 2)
