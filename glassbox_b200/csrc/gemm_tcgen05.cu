@@ -1,0 +1,332 @@
+// C[M, N] (+)= A[M, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores (sm_100a):
+// operands staged in shared memory by TMA, tcgen05.mma issued by one thread, the float32
+// accumulator in tensor memory (TMEM), read back with tcgen05.ld for the epilogue.
+//
+// One block computes one 128 x BN tile of C (BN = 64 or 128).
+//   warp 0, one lane: producer. For each 64-wide k-block it waits until the stage is free, arms the
+//       stage's "full" mbarrier with the bytes to come and issues two TMA loads (A box 128 x 64,
+//       W box BN x 64, 128-byte swizzle; rows or columns outside the matrices are zero-filled by
+//       the TMA unit, so M, N and K need not be multiples of the tile).
+//   warp 1, one lane: issues 4 tcgen05.mma (M 128, N BN, K 16) per k-block from shared-memory matrix
+//       descriptors, then tcgen05.commit to the stage's "empty" mbarrier (the stage is free once the
+//       tensor core has read it) and, after the last k-block, to the "accumulator ready" mbarrier.
+//   warps 0-3: epilogue. Warp w reads TMEM lanes 32w..32w+31 (rows of the tile), 32 columns at a
+//       time, and stores bfloat16 / float32 or adds into float32 (the residual stream).
+// Both operands are K-major ([rows, K] with K contiguous), exactly as activations and [out, in]
+// weights are stored (crates/glassbox-core/src/kernels.rs:381), so nothing is transposed.
+//
+// Every wait is bounded: a wait that exceeds its limit sets GB_STATUS_WAIT_TIMEOUT in the status
+// word and the block winds down (waits, again bounded, for its own TMA copies, frees its TMEM,
+// returns) instead of hanging the GPU. TMA loads use no multicast.
+#include "common.cuh"
+
+#include <cuda.h>
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;        // 64 bfloat16 = 128 bytes = one swizzle row
+constexpr int TC_STAGES = 4;
+constexpr long long TC_WAIT_CYCLES = 400ll * 1000 * 1000;   // about 0.2 s: far beyond any real wait
+
+enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2 };
+
+// ------------------------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and records it) if the limit passes or another thread gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TC_WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicOr(status, GB_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand in 128-byte-swizzled rows: 8-row groups are 1024
+// bytes apart (stride byte offset); the leading byte offset is unused for this layout (set to 1).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
+    d |= (uint64_t)1 << 46;                               // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bfloat16 A and B (both K-major), float32 accumulator, M x N tile.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo_bits), __uint_as_float(hi_bits));
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct __align__(8) TcShared {
+    uint64_t full[TC_STAGES];
+    uint64_t empty[TC_STAGES];
+    uint64_t accum;
+    uint32_t tmem_base;
+    int abort_flag;
+    int issued;      // k-blocks whose TMA loads were issued
+    int consumed;    // k-blocks whose full barrier the MMA thread has passed
+};
+
+template <int BN>
+__global__ void __launch_bounds__(128) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                           const __grid_constant__ CUtensorMap map_w, void* __restrict__ C,
+                                                           int mode, int M, int N, int K, long long ldc,
+                                                           int* __restrict__ status) {
+    extern __shared__ unsigned char smem_dyn[];
+    // 128-byte-swizzled tiles want 1024-byte alignment
+    unsigned char* tiles = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    constexpr int A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    __shared__ TcShared sh;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&sh.full[s], 1);
+            mbar_init(&sh.empty[s], 1);
+        }
+        mbar_init(&sh.accum, 1);
+        sh.abort_flag = 0;
+        sh.issued = 0;
+        sh.consumed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    if (warp == 0) {   // one warp allocates BN columns of tensor memory for the accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    volatile int* abort_flag = &sh.abort_flag;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------------------- producer
+        for (int kb = 0; kb < kblocks; ++kb) {
+            const int s = kb % TC_STAGES;
+            if (kb >= TC_STAGES && !mbar_wait(&sh.empty[s], ((kb / TC_STAGES) - 1) & 1, abort_flag, status)) break;
+            unsigned char* a_dst = tiles + s * STAGE_BYTES;
+            mbar_expect_tx(&sh.full[s], STAGE_BYTES);
+            tma_load_2d(a_dst, &map_a, &sh.full[s], kb * TC_BK, m0);
+            tma_load_2d(a_dst + A_BYTES, &map_w, &sh.full[s], kb * TC_BK, n0);
+            sh.issued = kb + 1;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------------------- MMA issuer
+        const uint32_t idesc = umma_idesc(TC_BM, BN);
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+            const int s = kb % TC_STAGES;
+            if (!mbar_wait(&sh.full[s], (kb / TC_STAGES) & 1, abort_flag, status)) { ok = false; break; }
+            sh.consumed = kb + 1;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+            const uint32_t w_addr = a_addr + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k) {
+                // 16 bfloat16 = 32 bytes further along K inside the swizzled row
+                umma_bf16(tmem, umma_desc(a_addr + k * 32), umma_desc(w_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+            }
+            umma_commit(&sh.empty[s]);       // arrives when the MMAs above have read the stage
+        }
+        if (ok) umma_commit(&sh.accum);      // arrives when every MMA has finished
+    }
+    __syncwarp();
+
+    // ------------------------------------------------------------------------------- epilogue
+    bool ready = true;
+    if (kblocks > 0) ready = mbar_wait(&sh.accum, 0, abort_flag, status);
+    tc_fence_after();
+    if (ready) {
+        const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            if (kblocks > 0) {
+                tmem_load32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);   // warp-wide: no divergence before it
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            if (row < M) {
+                const int col0 = n0 + c0;
+                if (mode == TC_STORE_BF16) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + col0;
+                    if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 v;
+                            v.x = pack2(r[j], r[j + 1]); v.y = pack2(r[j + 2], r[j + 3]);
+                            v.z = pack2(r[j + 4], r[j + 5]); v.w = pack2(r[j + 6], r[j + 7]);
+                            *reinterpret_cast<uint4*>(dst + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                } else {
+                    float* dst = reinterpret_cast<float*>(C) + (size_t)row * ldc + col0;
+                    const bool add = mode == TC_ADD_F32;
+                    if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            if (add) {
+                                const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) dst[j] = (add ? dst[j] : 0.f) + __uint_as_float(r[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------------------- wind down
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        if (lane == 0 && sh.abort_flag) {
+            // copies that were issued but never consumed may still be in flight: wait for them (bounded)
+            for (int kb = sh.consumed; kb < sh.issued; ++kb) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&sh.full[kb % TC_STAGES], (kb / TC_STAGES) & 1) && clock64() - t0 < TC_WAIT_CYCLES) {}
+            }
+        }
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// [rows, K] bfloat16, K contiguous, `ld` elements between rows; boxes of box_rows x 64, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    GB_REQUIRE(fn != nullptr, "gb_gemm_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    GB_REQUIRE(r == CUDA_SUCCESS, "gb_gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+template <int BN>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int mode, int M, int N, int K,
+                     long long ldc, int* status, cudaStream_t stream) {
+    constexpr int smem = TC_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    auto kernel = gemm_tcgen05_kernel<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        GB_REQUIRE(e == cudaSuccess, "gb_gemm_tcgen05: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(gb_ceil_div(N, BN), gb_ceil_div(M, TC_BM));
+    kernel<<<grid, 128, smem, stream>>>(ma, mw, c, mode, M, N, K, ldc, status);
+    return gb_check_launch("gb_gemm_tcgen05");
+}
+
+// 1 if the operands satisfy what TMA needs (16-byte aligned bases, row strides that are multiples of
+// 8 elements).
+GB_EXPORT int gb_gemm_tcgen05_supported(const void* a, const void* w, int M, int N, int K, long long lda,
+                                        long long ldw) {
+    return M > 0 && N > 0 && K > 0 && lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K &&
+           (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0;
+}
+
+// mode: 0 store bfloat16, 1 store float32, 2 add into float32.
+GB_EXPORT int gb_gemm_tcgen05(const void* a, const void* w, void* c, int mode, int M, int N, int K, long long lda,
+                              long long ldw, long long ldc, int* status, cudaStream_t stream) {
+    GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, N, K, lda, ldw),
+               "gb_gemm_tcgen05: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d N=%d K=%d)",
+               M, N, K);
+    GB_REQUIRE(mode >= 0 && mode <= 2 && ldc >= N && status != nullptr, "gb_gemm_tcgen05: bad mode, ldc or status");
+    // Narrow tiles when wide ones would leave most SMs idle.
+    const bool wide = (long long)gb_ceil_div(N, 128) * gb_ceil_div(M, TC_BM) >= 120;
+    CUtensorMap ma, mw;
+    if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
+    if (make_map(&mw, w, N, K, ldw, wide ? 128 : 64)) return 1;
+    return wide ? launch_tc<128>(ma, mw, c, mode, M, N, K, ldc, status, stream)
+                : launch_tc<64>(ma, mw, c, mode, M, N, K, ldc, status, stream);
+}

@@ -47,6 +47,10 @@ _SIGNATURES = {
     "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
                                 _P, _P],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
+    "gb_attention_prefill": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_attention_prefill_supported": [_I, _I, _I, _I],
+    "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P],
+    "gb_gemm_tcgen05_supported": [_P, _P, _I, _I, _I, _LL, _LL],
 }
 
 
@@ -213,8 +217,35 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
 
 
 def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:
-    """Whether the tensor-core kernel takes these operands."""
-    return False
+    """Whether the tcgen05 kernel takes these operands (bfloat16, TMA-aligned)."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or c.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    return bool(lib().gb_gemm_tcgen05_supported(_ptr(a), _ptr(w), a.shape[0], w.shape[0], a.shape[1], a.stride(0),
+                                                w.stride(0)))
+
+
+_tc_status = {}
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False,
+            status: Optional[torch.Tensor] = None) -> None:
+    """c[M, N] (+)= a[M, K] @ w[N, K]^T with TMA + tcgen05.mma + TMEM. ``status`` receives the
+    wait-timeout bit if a bounded wait inside the kernel ever gives up."""
+    _cuda(a, w, c, status)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    if status is None:
+        status = _tc_status.get(a.device)
+        if status is None:
+            status = _tc_status[a.device] = torch.zeros(1, dtype=torch.int32, device=a.device)
+    if accumulate:
+        assert c.dtype == torch.float32
+        mode = 2
+    else:
+        mode = 0 if c.dtype == torch.bfloat16 else 1
+    _call("gb_gemm_tcgen05", _ptr(a), _ptr(w), _ptr(c), mode, M, N, K, a.stride(0), w.stride(0), c.stride(0),
+          _ptr(status), _stream())
 
 
 def attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -294,6 +325,26 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
           _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
           kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml), _ptr(counters),
           _ptr(status), _stream())
+
+
+def attention_prefill_supported(dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().gb_attention_prefill_supported(nh, nkv, hd, page_size))
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                      block_tables: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor,
+                      max_rows_per_seq: int, nh: int, nkv: int, hd: int, page_size: int, scale: float,
+                      window: Optional[int], status: torch.Tensor) -> None:
+    """bfloat16 flash attention for batches whose requests bring runs of consecutive rows.
+    seq_first_row int32 [S+1], seq_start_pos int32 [S]; block_tables int32 [S, max_pages]."""
+    _cuda(q, out, kcache, vcache, block_tables, seq_first_row, seq_start_pos, status)
+    assert q.dtype == out.dtype == kcache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    S = block_tables.shape[0]
+    assert seq_first_row.numel() == S + 1 and seq_start_pos.numel() == S
+    _call("gb_attention_prefill", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
+          _ptr(block_tables), block_tables.shape[1], _ptr(seq_first_row), _ptr(seq_start_pos), S, int(max_rows_per_seq),
+          nh, nkv, hd, page_size, kcache.shape[0], float(scale), int(window or 0), _ptr(status), _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

@@ -61,7 +61,8 @@ class GqaAttention(Mixer):
         """att[row, head, :] = softmax over the row's visible keys; the kernel is picked by the shape
         of the batch: rows that are single decoded tokens share the keys of a request between
         several blocks (on the tensor cores in bfloat16 where the head size is one the kernel is built
-        for, else with float32 FMA); anything else takes the one-warp-per-(row, head) kernel."""
+        for, else with float32 FMA); prompt portions take the flash kernel in bfloat16 at head sizes it
+        is built for; anything else takes the one-warp-per-(row, head) kernel."""
         n = q.shape[0]
         if ctx.decode_only and kernels.attention_decode_mma_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size):
             splits = kernels.decode_mma_splits(n, self.nkv, self.hd, ctx.max_context)
@@ -82,6 +83,12 @@ class GqaAttention(Mixer):
             kernels.attention_decode(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
                                      self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window,
                                      splits, part_acc, part_ml, counters, ctx.status)
+            return
+        if not ctx.decode_only and kernels.attention_prefill_supported(q.dtype, self.nh, self.nkv, self.hd,
+                                                                       cache.page_size):
+            kernels.attention_prefill(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row,
+                                      ctx.seq_start_pos, ctx.max_rows_per_seq, self.nh, self.nkv, self.hd,
+                                      cache.page_size, self.spec.scale, self.spec.window, ctx.status)
             return
         kernels.attention_rows(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.nh,
                                self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window, ctx.status)

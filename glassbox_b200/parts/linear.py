@@ -17,7 +17,7 @@ def linear(ctx, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
     if kernels.gemm_stream_supported(a, w):
         kernels.gemm_stream(a, w, out, accumulate)
     elif a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and kernels.gemm_tc_supported(a, w, out):
-        kernels.gemm_tc(a, w, out, accumulate)
+        kernels.gemm_tc(a, w, out, accumulate, ctx.status)
     else:
         kernels.gemm_simt(a, w, out, accumulate)
 

@@ -42,6 +42,11 @@ TINY = {
     "C": dict(hidden_size=80, intermediate_size=136, num_hidden_layers=1, num_attention_heads=5,
               num_key_value_heads=5, head_dim=48, vocab_size=301, rope_theta=500000.0, rms_norm_eps=3e-6,
               tie_word_embeddings=False, max_position_embeddings=320),
+    # head size 64, the size the tensor-core attention kernels are built for, so that whole-model
+    # tests run them too (the other configurations take the float32-FMA kernels of any head size)
+    "D": dict(hidden_size=128, intermediate_size=208, num_hidden_layers=2, num_attention_heads=2,
+              num_key_value_heads=1, vocab_size=300, rope_theta=100000.0, rms_norm_eps=1e-5,
+              tie_word_embeddings=True, max_position_embeddings=320),
 }
 
 

@@ -23,7 +23,7 @@ def make_engine(folder, dtype, **kw):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_first_tokens_and_long_decoding(model_dirs, name, dtype):
     from glassbox_b200.engine.engine import StepEntry
     folder = model_dirs(name, dtype)
@@ -40,7 +40,7 @@ def test_first_tokens_and_long_decoding(model_dirs, name, dtype):
         eng.step([StepEntry("a", [1], [0])])
 
 
-@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16")])
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("D", "float32")])
 def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
     import glassbox_b200
     folder = model_dirs(name, dtype)

@@ -13,7 +13,8 @@ import replay_util as ru
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 33, 128, 5, 90, 64, 17], "B": [100, 1, 256, 40, 64, 8, 129], "C": [300, 48, 17, 130, 65]}
+LENGTHS = {"A": [70, 33, 128, 5, 90, 64, 17], "B": [100, 1, 256, 40, 64, 8, 129], "C": [300, 48, 17, 130, 65],
+           "D": [320, 65, 2, 129, 200, 64]}
 
 
 def make_requests(name, seed=0):
@@ -35,7 +36,7 @@ def check(model_dir, dtype, got, requests, what, only_wanted=False):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_tail_and_portions(model_dirs, tmp_path, name, dtype):
     folder = model_dirs(name, dtype)
     requests = make_requests(name)
@@ -46,7 +47,7 @@ def test_whole_tail_and_portions(model_dirs, tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_mixed_batches_reuse_pages(model_dirs, sharp_dirs, tmp_path, name, dtype):
     requests = make_requests(name, seed=3)
     kinds = [("random-weights", model_dirs(name, dtype))]
