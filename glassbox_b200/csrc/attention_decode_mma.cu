@@ -85,9 +85,14 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(
     const int S4 = splits * 4;
     __shared__ int is_last;
 
+    // Let the next kernel in the stream begin its prologue. This kernel's own prologue (positions,
+    // block table: step metadata that no kernel writes) runs before it waits for its predecessor,
+    // which wrote the queries and this step's keys and values.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int pos = positions[row];
     __nv_bfloat16* orow = out + (size_t)row * out_stride;
     if (pos < 0) {  // padding row
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (split == 0)
             for (int i = tid; i < G * HD; i += 128) orow[head0 * HD + i] = __float2bfloat16_rn(0.f);
         return;
@@ -100,20 +105,6 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(
     const int k_begin = first_aligned + split * chunk;
     const int k_end = min(pos + 1, k_begin + chunk);
     const int nblocks = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
-
-    // Q as the A operand: rows g and g+8 are query heads head0+g and head0+g+8 (zero beyond G).
-    uint32_t qf[KS][4];
-    {
-        const __nv_bfloat16* q0 = q + (size_t)row * q_stride + (size_t)(head0 + g) * HD;
-        const __nv_bfloat16* q1 = q0 + 8 * HD;
-#pragma unroll
-        for (int s = 0; s < KS; ++s) {
-            uint2 a = make_uint2(0, 0), b = make_uint2(0, 0);
-            if (g < G) a = *reinterpret_cast<const uint2*>(q0 + 16 * s + 4 * t);
-            if (g + 8 < G) b = *reinterpret_cast<const uint2*>(q1 + 16 * s + 4 * t);
-            qf[s][0] = a.x; qf[s][1] = b.x; qf[s][2] = a.y; qf[s][3] = b.y;
-        }
-    }
 
     float m_run[2] = {MMA_NEG_BIG, MMA_NEG_BIG}, l_run[2] = {0.f, 0.f};
     float acc[NT][4];
@@ -147,6 +138,21 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(
         }
         __syncthreads();
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the predecessor's writes (q, this step's K/V) are visible from here
+    // Q as the A operand: rows g and g+8 are query heads head0+g and head0+g+8 (zero beyond G).
+    uint32_t qf[KS][4];
+    {
+        const __nv_bfloat16* q0 = q + (size_t)row * q_stride + (size_t)(head0 + g) * HD;
+        const __nv_bfloat16* q1 = q0 + 8 * HD;
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+            uint2 a = make_uint2(0, 0), b = make_uint2(0, 0);
+            if (g < G) a = *reinterpret_cast<const uint2*>(q0 + 16 * s + 4 * t);
+            if (g + 8 < G) b = *reinterpret_cast<const uint2*>(q1 + 16 * s + 4 * t);
+            qf[s][0] = a.x; qf[s][1] = b.x; qf[s][2] = a.y; qf[s][3] = b.y;
+        }
+    }
+
     // row index (in units of cache rows) of the first key of the 16-key half-block starting at `key`
     auto half_block_row = [&](int key) -> int {
         const int pi = min(key >> page_shift, page_lo + n_pages - 1);
@@ -331,15 +337,28 @@ template <int HD, int BK>
 static int launch_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
                       const void* vcache, const int* block_tables, int max_pages, const int* row_seq,
                       const int* positions, int n, int nh, int nkv, int page_size, long long num_pages, float scale,
-                      int window, int splits, float* part_acc, float* part_ml, int* counters, int* status,
+                      int window, int splits, float* part_acc, float* part_ml, int* counters, int* status, int pdl,
                       cudaStream_t stream) {
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    dim3 grid(splits, nkv, n);
-    attention_decode_mma_kernel<HD, BK><<<grid, 128, 0, stream>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kcache,
-        (const __nv_bfloat16*)vcache, block_tables, max_pages, row_seq, positions, nh, nkv, page_size, page_shift,
-        num_pages, scale, window, splits, part_acc, part_ml, counters, status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, nkv, n);
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, BK>, (const __nv_bfloat16*)q, q_stride,
+                                       (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kcache,
+                                       (const __nv_bfloat16*)vcache, block_tables, max_pages, row_seq, positions, nh, nkv,
+                                       page_size, page_shift, num_pages, scale, window, splits, part_acc, part_ml, counters,
+                                       status);
+    if (e != cudaSuccess) {
+        gb_set_error("gb_attention_decode_mma: launch failed: %s", cudaGetErrorString(e));
+        return 2;
+    }
     return gb_check_launch("gb_attention_decode_mma");
 }
 
@@ -349,12 +368,15 @@ GB_EXPORT int gb_attention_decode_mma_supported(int nh, int nkv, int hd) {
     return (hd == 16 || hd == 32 || hd == 64 || hd == 128) && nh / nkv <= 16;
 }
 
-GB_EXPORT int gb_attention_decode_mma(const void* q, long long q_stride, void* out, long long out_stride,
-                                      const void* kcache, const void* vcache, const int* block_tables, int max_pages,
-                                      const int* row_seq, const int* positions, int n, int nh, int nkv, int hd,
-                                      int page_size, long long num_pages, float scale, int window, int splits,
-                                      float* part_acc, float* part_ml, int* counters, int* status,
-                                      cudaStream_t stream) {
+// As gb_attention_decode_mma, with the choice of launching under programmatic stream serialisation
+// (pdl != 0): the kernel then starts while its predecessor in the stream still runs, reads only step
+// metadata until the predecessor has finished, and releases its own successor at once.
+GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, void* out, long long out_stride,
+                                          const void* kcache, const void* vcache, const int* block_tables,
+                                          int max_pages, const int* row_seq, const int* positions, int n, int nh,
+                                          int nkv, int hd, int page_size, long long num_pages, float scale, int window,
+                                          int splits, float* part_acc, float* part_ml, int* counters, int* status,
+                                          int pdl, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_decode_mma_supported(nh, nkv, hd),
                "gb_attention_decode_mma: head size %d with %d heads per kv head is not built (16/32/64/128, <= 16)", hd,
                nkv > 0 ? nh / nkv : 0);
@@ -369,10 +391,21 @@ GB_EXPORT int gb_attention_decode_mma(const void* q, long long q_stride, void* o
 #define GB_MMA(HH, BB)                                                                                             \
     return launch_mma<HH, BB>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, row_seq, positions, \
                               n, nh, nkv, page_size, num_pages, scale, window, splits, part_acc, part_ml, counters,       \
-                              status, stream);
+                              status, pdl, stream);
     if (hd == 16) { GB_MMA(16, 32) }
     if (hd == 32) { GB_MMA(32, 32) }
     if (hd == 64) { GB_MMA(64, 32) }
     GB_MMA(128, 16)
 #undef GB_MMA
+}
+
+GB_EXPORT int gb_attention_decode_mma(const void* q, long long q_stride, void* out, long long out_stride,
+                                      const void* kcache, const void* vcache, const int* block_tables, int max_pages,
+                                      const int* row_seq, const int* positions, int n, int nh, int nkv, int hd,
+                                      int page_size, long long num_pages, float scale, int window, int splits,
+                                      float* part_acc, float* part_ml, int* counters, int* status,
+                                      cudaStream_t stream) {
+    return gb_attention_decode_mma_pdl(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, row_seq,
+                                       positions, n, nh, nkv, hd, page_size, num_pages, scale, window, splits, part_acc,
+                                       part_ml, counters, status, 0, stream);
 }

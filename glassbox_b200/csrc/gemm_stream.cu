@@ -1,32 +1,65 @@
-// C[M, N] (+)= X[M, K] * W[N, K]^T for few rows (M <= 64, decoding): a weight-streaming kernel.
+// C[M, N] (+)= X[M, K] * W[N, K]^T for few rows (M <= 64, decoding): a weight-streaming kernel
+// with the neighbouring element-wise work folded in.
 //
 // The weights are the big operand and each is needed once, so the kernel is organised around
-// reading W from HBM at full speed: every warp owns a strip of 16 weight rows and pulls them with
-// 16-byte loads straight into the register layout of the tensor-core instruction
-// (mma.sync m16n8k16, bfloat16 in, float32 accumulate); the few activation rows sit in shared
-// memory as the other operand. Inside each block of 32 k-values a thread's 16 bytes are 8
-// consecutive k; the instruction's k index is a fixed permutation of them, applied to both
-// operands, so every dot product still sums the same products (in an order that depends only on
-// K and the kernel variant, never on M or on a row's place in the batch).
+// reading W from HBM at full speed: a block owns a strip of 16 weight rows (or a pair of strips),
+// its four warps take interleaved blocks of 32 k-values and pull them with 16-byte loads straight
+// into the register layout of the tensor-core instruction (mma.sync m16n8k16, bfloat16 in, float32
+// accumulate); the few activation rows sit in shared memory as the other operand; the four
+// partial sums are added through shared memory. Inside each block of 32 k-values a thread's 16
+// bytes are 8 consecutive k; the instruction's k index is a fixed permutation of them, applied to
+// both operands, so every dot product still sums the same products, in an order that depends only
+// on K, never on M or on a row's place in the batch.
 //
-// One strip per block: the four warps take interleaved k-blocks and their partial sums are added
-// through shared memory, so even a 576-row matrix puts 36 x 4 warps to work. Output modes: store bfloat16 / float32,
-// add into float32 (the residual stream), or gated: strips of the gate rows and of the up rows
-// (I rows further down) are accumulated side by side and act = silu(gate) * up is stored
-// (crates/glassbox-core/src/model.rs:335-340), which spares a kernel and the [M, 2I] round trip.
+// Folded in:
+//  * prologue: RMSNorm. Instead of bfloat16 activations the kernel can take the float32 residual
+//    rows and a gain: it computes 1/sqrt(mean(x^2)+eps) per row and stages gain*(x*s) rounded to
+//    bfloat16, exactly what the separate norm kernel would have written
+//    (crates/glassbox-core/src/model.rs:94-100).
+//  * epilogue: store bfloat16 / float32, add into float32 (the residual stream), gated
+//    (act = silu(gate) * up with the gate strip and the up strip I rows apart, model.rs:335-340), or
+//    rotary + cache write for a stacked QKV matrix: the two strips of a pair are hd/2 rows apart,
+//    i.e. the two halves (i, i + hd/2) of one head; q is rotated and stored, k is rotated and
+//    written to the row's cache slot, v is written to the cache slot (model.rs:266-276).
+//  * programmatic dependent launch: the first weights are requested before the kernel waits for
+//    its predecessor in the stream (they do not depend on it), and the successor is released at
+//    once, so consecutive small kernels overlap their start-up with each other's tails.
 #include "common.cuh"
 
-#include <mma.h>
+enum { WS_STORE_BF16 = 0, WS_STORE_F32 = 1, WS_ADD_F32 = 2, WS_GLU_BF16 = 3, WS_ROPE_QKV = 4 };
 
-enum { WS_STORE_BF16 = 0, WS_STORE_F32 = 1, WS_ADD_F32 = 2, WS_GLU_BF16 = 3 };
-
-constexpr int WS_KC = 256;            // k per shared-memory chunk
-constexpr int WS_PAD = 32;            // padding per activation row: row stride = 16 banks mod 32, so the
-                                      // 16-byte operand loads of a quarter-warp never collide
+constexpr int WS_KC = 256;             // k per shared-memory chunk
+constexpr int WS_PAD = 32;             // padding per activation row: row stride = 16 banks mod 32, so the
+                                       // 16-byte operand loads of a quarter-warp never collide
 constexpr int WS_BLOCKS = WS_KC / 32;  // k32 blocks per chunk
+constexpr int WS_BPW = WS_BLOCKS / 4;  // k32 blocks per warp per chunk
 
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
+struct StreamArgs {
+    const __nv_bfloat16* X;   // [M, K] bfloat16 activations, or nullptr when `xres` is normalised instead
+    long long ldx;
+    const float* xres;        // [M, K] float32 rows to RMS-normalise (with X == nullptr)
+    long long ldr;
+    const float* gain;        // [K]
+    float eps;
+    const __nv_bfloat16* W;   // [N (+ pair rows), K]
+    long long ldw;
+    void* C;
+    long long ldc;
+    int mode, M, N, K;
+    int pair_offset;          // rows between the two strips of a pair (gated: N; rotary: hd/2)
+    // rotary + cache write
+    const float2* rope;       // [max_pos, hd/2] (cos, sin) or nullptr (no rotation)
+    const int* positions;     // [M]; a negative position marks a padding row
+    const int* slots;         // [M]: page * page_size + offset
+    __nv_bfloat16* kcache;    // [pages, nkv, page_size, hd]
+    __nv_bfloat16* vcache;
+    int nh, nkv, hd, page_size, max_pos, write_kv;
+    long long num_slots;
+    int* status;
+};
+
+__device__ __forceinline__ void ws_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -40,24 +73,35 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
-template <int NT, int KSPLIT, bool GLU>
-__global__ void __launch_bounds__(128) gemm_stream_kernel(const __nv_bfloat16* __restrict__ X,
-                                                          const __nv_bfloat16* __restrict__ W, void* __restrict__ C,
-                                                          int mode, int M, int N, int K, long long ldx, long long ldw,
-                                                          long long ldc, int glu_offset) {
-    constexpr int ROWS = NT * 8;                          // activation rows held
-    constexpr int BPW = WS_BLOCKS / KSPLIT;               // k32 blocks per warp per chunk
-    constexpr int SETS = GLU ? 2 : 1;
+__device__ __forceinline__ uint32_t ws_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int NT, bool PAIR>
+__global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
+    constexpr int ROWS = NT * 8;   // activation rows held
+    constexpr int SETS = PAIR ? 2 : 1;
     __shared__ __align__(16) __nv_bfloat16 xs[ROWS][WS_KC + WS_PAD];
+    __shared__ float srow[ROWS];
     // the partial sums of the four warps reuse the activation tile once the k loop is over
     static_assert(sizeof(float) * 4 * SETS * 16 * ROWS <= sizeof(__nv_bfloat16) * ROWS * (WS_KC + WS_PAD), "red fits in xs");
     float* red = reinterpret_cast<float*>(&xs[0][0]);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane >> 2, t = lane & 3;
-    const int strip = KSPLIT == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
-    const int n0 = strip * 16;
-    // With GLU, N is the number of gate rows (= I) and the up rows start glu_offset rows below.
-    const bool strip_live = n0 < N;
+    const int M = a.M, N = a.N, K = a.K;
+
+    // let the next kernel in the stream start its own prologue
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // first weight row of this block's strip (of its first strip, for a pair)
+    int n0;
+    if (a.mode == WS_ROPE_QKV) {
+        const int per_head = a.hd / 32;   // strip pairs per head
+        n0 = (blockIdx.x / per_head) * a.hd + (blockIdx.x % per_head) * 16;
+    } else {
+        n0 = blockIdx.x * 16;
+    }
 
     float acc[SETS][NT][4];
 #pragma unroll
@@ -68,22 +112,21 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const __nv_bfloat16* _
             for (int j = 0; j < 4; ++j) acc[s][i][j] = 0.f;
 
     const int row_a = n0 + r, row_b = n0 + r + 8;
-    const bool live_a = strip_live && row_a < N, live_b = strip_live && row_b < N;
+    const bool live_a = row_a < N, live_b = row_b < N;
     const __nv_bfloat16* wa[SETS];
     const __nv_bfloat16* wb[SETS];
 #pragma unroll
     for (int s = 0; s < SETS; ++s) {
-        wa[s] = W + (size_t)(row_a + s * glu_offset) * ldw;
-        wb[s] = W + (size_t)(row_b + s * glu_offset) * ldw;
+        wa[s] = a.W + (size_t)(row_a + s * a.pair_offset) * a.ldw;
+        wb[s] = a.W + (size_t)(row_b + s * a.pair_offset) * a.ldw;
     }
 
     const int nchunks = (K + WS_KC - 1) / WS_KC;
-    uint4 fa[SETS][BPW], fb[SETS][BPW];
+    uint4 fa[SETS][WS_BPW], fb[SETS][WS_BPW];
     auto fetch = [&](int chunk) {
 #pragma unroll
-        for (int j = 0; j < BPW; ++j) {
-            const int blk = KSPLIT == 1 ? j : j * KSPLIT + warp;
-            const int k = chunk * WS_KC + blk * 32 + 8 * t;
+        for (int j = 0; j < WS_BPW; ++j) {
+            const int k = chunk * WS_KC + (j * 4 + warp) * 32 + 8 * t;
             const bool in = k < K;
 #pragma unroll
             for (int s = 0; s < SETS; ++s) {
@@ -93,121 +136,224 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const __nv_bfloat16* _
         }
     };
 
-    fetch(0);
+    fetch(0);   // weights do not depend on the previous kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // everything below reads what it wrote
+
+    const bool normalise = a.X == nullptr;
+    if (normalise) {
+        for (int m = warp; m < ROWS; m += 4) {
+            float ss = 0.f;
+            if (m < M) {
+                const float* xr = a.xres + (size_t)m * a.ldr;
+                for (int k = lane * 4; k < K; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(xr + k);
+                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                }
+            }
+            ss = gb_warp_sum(ss);
+            if (lane == 0) srow[m] = 1.0f / sqrtf(ss / (float)K + a.eps);
+        }
+    }
+
     for (int chunk = 0; chunk < nchunks; ++chunk) {
-        // stage the activations of this chunk: ROWS x 256, 16 bytes per thread and copy
+        // stage the activations of this chunk: ROWS x 256, 8 values per thread and copy
         __syncthreads();
         for (int c = tid; c < ROWS * (WS_KC / 8); c += 128) {
             const int row = c / (WS_KC / 8), col = (c % (WS_KC / 8)) * 8;
             const int k = chunk * WS_KC + col;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (row < M && k < K) v = *reinterpret_cast<const uint4*>(X + (size_t)row * ldx + k);
+            if (row < M && k < K) {
+                if (normalise) {
+                    const float* xr = a.xres + (size_t)row * a.ldr + k;
+                    const float4 x0 = *reinterpret_cast<const float4*>(xr), x1 = *reinterpret_cast<const float4*>(xr + 4);
+                    const float4 g0 = *reinterpret_cast<const float4*>(a.gain + k);
+                    const float4 g1 = *reinterpret_cast<const float4*>(a.gain + k + 4);
+                    const float s = srow[row];
+                    v.x = ws_pack(g0.x * (x0.x * s), g0.y * (x0.y * s));
+                    v.y = ws_pack(g0.z * (x0.z * s), g0.w * (x0.w * s));
+                    v.z = ws_pack(g1.x * (x1.x * s), g1.y * (x1.y * s));
+                    v.w = ws_pack(g1.z * (x1.z * s), g1.w * (x1.w * s));
+                } else {
+                    v = *reinterpret_cast<const uint4*>(a.X + (size_t)row * a.ldx + k);
+                }
+            }
             *reinterpret_cast<uint4*>(&xs[row][col]) = v;
         }
         __syncthreads();
-        uint4 ca[SETS][BPW], cb[SETS][BPW];
+        uint4 ca[SETS][WS_BPW], cb[SETS][WS_BPW];
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
 #pragma unroll
-            for (int j = 0; j < BPW; ++j) {
+            for (int j = 0; j < WS_BPW; ++j) {
                 ca[s][j] = fa[s][j];
                 cb[s][j] = fb[s][j];
             }
         if (chunk + 1 < nchunks) fetch(chunk + 1);   // next chunk's weights fly while this one is used
 #pragma unroll
-        for (int j = 0; j < BPW; ++j) {
-            const int blk = KSPLIT == 1 ? j : j * KSPLIT + warp;
-            const int kb = blk * 32 + 8 * t;
+        for (int j = 0; j < WS_BPW; ++j) {
+            const int kb = (j * 4 + warp) * 32 + 8 * t;
 #pragma unroll
             for (int i = 0; i < NT; ++i) {
                 // this thread's 8 consecutive k of token (8i + r): two k16 steps of 4 each
                 const uint4 xv = *reinterpret_cast<const uint4*>(&xs[i * 8 + r][kb]);
 #pragma unroll
                 for (int s = 0; s < SETS; ++s) {
-                    mma_bf16_16816(acc[s][i], ca[s][j].x, cb[s][j].x, ca[s][j].y, cb[s][j].y, xv.x, xv.y);
-                    mma_bf16_16816(acc[s][i], ca[s][j].z, cb[s][j].z, ca[s][j].w, cb[s][j].w, xv.z, xv.w);
+                    ws_mma(acc[s][i], ca[s][j].x, cb[s][j].x, ca[s][j].y, cb[s][j].y, xv.x, xv.y);
+                    ws_mma(acc[s][i], ca[s][j].z, cb[s][j].z, ca[s][j].w, cb[s][j].w, xv.z, xv.w);
                 }
             }
         }
     }
 
     // acc[s][i] = {(row r, token 8i+2t), (row r, token 8i+2t+1), (row r+8, ...), (row r+8, ...)}
-    if (KSPLIT != 1) {
-        __syncthreads();
+    __syncthreads();
 #pragma unroll
-        for (int s = 0; s < SETS; ++s)
-#pragma unroll
-            for (int i = 0; i < NT; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int row = r + (j >> 1) * 8, tok = i * 8 + 2 * t + (j & 1);
-                    red[((warp * SETS + s) * 16 + row) * ROWS + tok] = acc[s][i][j];
-                }
-        __syncthreads();
-    }
-    auto emit = [&](int row, int tok, float v0, float v1) {
-        const int n = n0 + row;
-        if (n >= N || tok >= M) return;
-        if (mode == WS_GLU_BF16) {
-            float a = v0 / (1.0f + __expf(-v0)) * v1;
-            reinterpret_cast<__nv_bfloat16*>(C)[(size_t)tok * ldc + n] = __float2bfloat16_rn(a);
-        } else if (mode == WS_STORE_BF16) {
-            reinterpret_cast<__nv_bfloat16*>(C)[(size_t)tok * ldc + n] = __float2bfloat16_rn(v0);
-        } else if (mode == WS_STORE_F32) {
-            reinterpret_cast<float*>(C)[(size_t)tok * ldc + n] = v0;
-        } else {
-            float* p = reinterpret_cast<float*>(C) + (size_t)tok * ldc + n;
-            *p += v0;
-        }
-    };
-    if (KSPLIT == 1) {
-        if (!strip_live) return;
+    for (int s = 0; s < SETS; ++s)
 #pragma unroll
         for (int i = 0; i < NT; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                emit(r + (j >> 1) * 8, i * 8 + 2 * t + (j & 1), acc[0][i][j], GLU ? acc[SETS - 1][i][j] : 0.f);
-    } else {
-        for (int e = tid; e < 16 * ROWS; e += 128) {
-            const int row = e % 16, tok = e / 16;        // consecutive threads -> consecutive n
-            float v[2] = {0.f, 0.f};
+            for (int j = 0; j < 4; ++j) {
+                const int row = r + (j >> 1) * 8, tok = i * 8 + 2 * t + (j & 1);
+                red[((warp * SETS + s) * 16 + row) * ROWS + tok] = acc[s][i][j];
+            }
+    __syncthreads();
+    for (int e = tid; e < 16 * ROWS; e += 128) {
+        const int row = e % 16, tok = e / 16;   // consecutive threads -> consecutive n
+        const int n = n0 + row;
+        if (n >= N || tok >= M) continue;
+        float v[2] = {0.f, 0.f};
 #pragma unroll
-            for (int s = 0; s < SETS; ++s)
+        for (int s = 0; s < SETS; ++s)
 #pragma unroll
-                for (int w = 0; w < 4; ++w) v[s] += red[((w * SETS + s) * 16 + row) * ROWS + tok];
-            emit(row, tok, v[0], v[1]);
+            for (int w = 0; w < 4; ++w) v[s] += red[((w * SETS + s) * 16 + row) * ROWS + tok];
+        if (a.mode == WS_ROPE_QKV) {
+            const int pos = a.positions[tok];
+            if (pos < 0) continue;               // padding row
+            const int half = a.hd / 2;
+            const int head = n / a.hd, i = n % a.hd;   // i < hd/2: this thread holds channels i and i + hd/2
+            float y0 = v[0], y1 = v[1];
+            if (head < a.nh + a.nkv && a.rope != nullptr) {
+                if (pos >= a.max_pos) {
+                    atomicOr(a.status, GB_STATUS_BAD_POSITION);
+                } else {
+                    const float2 cs = a.rope[(size_t)pos * half + i];
+                    y0 = v[0] * cs.x - v[1] * cs.y;
+                    y1 = v[1] * cs.x + v[0] * cs.y;
+                }
+            }
+            if (head < a.nh) {
+                __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)tok * a.ldc + (size_t)head * a.hd;
+                q[i] = __float2bfloat16_rn(y0);
+                q[i + half] = __float2bfloat16_rn(y1);
+            } else if (a.write_kv) {
+                const long long slot = a.slots[tok];
+                if (slot < 0 || slot >= a.num_slots) {
+                    atomicOr(a.status, GB_STATUS_BAD_SLOT);
+                } else {
+                    const bool is_k = head < a.nh + a.nkv;
+                    const int kvh = is_k ? head - a.nh : head - a.nh - a.nkv;
+                    __nv_bfloat16* base = is_k ? a.kcache : a.vcache;
+                    __nv_bfloat16* dst = base + (((slot / a.page_size) * a.nkv + kvh) * a.page_size + slot % a.page_size) * a.hd;
+                    dst[i] = __float2bfloat16_rn(y0);
+                    dst[i + half] = __float2bfloat16_rn(y1);
+                }
+            }
+        } else if (a.mode == WS_GLU_BF16) {
+            const float g = v[0] / (1.0f + __expf(-v[0])) * v[1];
+            reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(g);
+        } else if (a.mode == WS_STORE_BF16) {
+            reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(v[0]);
+        } else if (a.mode == WS_STORE_F32) {
+            reinterpret_cast<float*>(a.C)[(size_t)tok * a.ldc + n] = v[0];
+        } else {
+            float* p = reinterpret_cast<float*>(a.C) + (size_t)tok * a.ldc + n;
+            *p += v[0];
         }
     }
 }
 
-template <int NT, bool GLU>
-static int launch_stream(const void* x, const void* w, void* c, int mode, int M, int N, int K, long long ldx,
-                         long long ldw, long long ldc, int glu_offset, cudaStream_t stream) {
-    const int strips = (N + 15) / 16;
-    const __nv_bfloat16* X = (const __nv_bfloat16*)x;
-    const __nv_bfloat16* W = (const __nv_bfloat16*)w;
-    gemm_stream_kernel<NT, 4, GLU><<<strips, 128, 0, stream>>>(X, W, c, mode, M, N, K, ldx, ldw, ldc, glu_offset);
+template <int NT, bool PAIR>
+static int launch_stream(const StreamArgs& a, int blocks, int pdl, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, PAIR>, a);
+    if (e != cudaSuccess) {
+        gb_set_error("gb_gemm_stream: launch failed: %s", cudaGetErrorString(e));
+        return 2;
+    }
     return gb_check_launch("gb_gemm_stream");
 }
 
-// mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated (W = [gate rows; up rows],
-// N = number of gate rows, c = bfloat16 [M, N]).
-GB_EXPORT int gb_gemm_stream(const void* x, const void* w, void* c, int mode, int M, int N, int K, long long ldx,
-                             long long ldw, long long ldc, cudaStream_t stream) {
-    GB_REQUIRE(M >= 0 && M <= 64 && N > 0 && K > 0, "gb_gemm_stream: sizes M=%d N=%d K=%d outside its range (M <= 64)", M, N, K);
-    GB_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gb_gemm_stream: K and the row strides must be multiples of 8");
-    GB_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, "gb_gemm_stream: operands must be 16-byte aligned");
-    GB_REQUIRE(mode >= 0 && mode <= 3, "gb_gemm_stream: unknown mode %d", mode);
-    GB_REQUIRE(mode != WS_GLU_BF16 || N % 16 == 0, "gb_gemm_stream: the gated mode needs N to be a multiple of 16");
-    if (M == 0) return 0;
-    const int nt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-    const bool glu = mode == WS_GLU_BF16;
-#define GB_WS(NTT)                                                                                         \
-    return glu ? launch_stream<NTT, true>(x, w, c, mode, M, N, K, ldx, ldw, ldc, N, stream)                 \
-               : launch_stream<NTT, false>(x, w, c, mode, M, N, K, ldx, ldw, ldc, 0, stream);
+static int dispatch_stream(const StreamArgs& a, int blocks, bool pair, int pdl, cudaStream_t stream) {
+    const int nt = a.M <= 8 ? 1 : a.M <= 16 ? 2 : a.M <= 32 ? 4 : 8;
+#define GB_WS(NTT) return pair ? launch_stream<NTT, true>(a, blocks, pdl, stream) : launch_stream<NTT, false>(a, blocks, pdl, stream);
     if (nt == 1) { GB_WS(1) }
     if (nt == 2) { GB_WS(2) }
     if (nt == 4) { GB_WS(4) }
     GB_WS(8)
 #undef GB_WS
+}
+
+static int check_common(const char* who, const void* x, const float* xres, const void* w, int M, int N, int K,
+                        long long ldx, long long ldr, long long ldw) {
+    GB_REQUIRE(M >= 0 && M <= 64 && N > 0 && K > 0, "%s: sizes M=%d N=%d K=%d outside its range (M <= 64)", who, M, N, K);
+    GB_REQUIRE(K % 8 == 0 && ldw % 8 == 0 && (uintptr_t)w % 16 == 0, "%s: K and the weight row stride must be multiples of 8, the weights 16-byte aligned", who);
+    if (x != nullptr)
+        GB_REQUIRE(ldx % 8 == 0 && (uintptr_t)x % 16 == 0, "%s: activations must be 16-byte aligned with a row stride that is a multiple of 8", who);
+    else
+        GB_REQUIRE(xres != nullptr && ldr % 4 == 0 && (uintptr_t)xres % 16 == 0, "%s: float32 rows to normalise must be 16-byte aligned", who);
+    return 0;
+}
+
+// mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated (W = [gate rows; up rows],
+// N = number of gate rows, c = bfloat16 [M, N]). With x == nullptr the float32 rows `xres` are
+// RMS-normalised with `gain` and `eps` on the way in. pdl != 0 launches with programmatic stream
+// serialisation (the kernel waits for its predecessor itself, after prefetching weights).
+GB_EXPORT int gb_gemm_stream(const void* x, long long ldx, const float* xres, long long ldr, const float* gain, float eps,
+                             const void* w, long long ldw, void* c, long long ldc, int mode, int M, int N, int K,
+                             int pdl, cudaStream_t stream) {
+    if (check_common("gb_gemm_stream", x, xres, w, M, N, K, ldx, ldr, ldw)) return 1;
+    GB_REQUIRE(mode >= 0 && mode <= 3, "gb_gemm_stream: unknown mode %d", mode);
+    GB_REQUIRE(mode != WS_GLU_BF16 || N % 16 == 0, "gb_gemm_stream: the gated mode needs N to be a multiple of 16");
+    GB_REQUIRE(x != nullptr || gain != nullptr, "gb_gemm_stream: normalising needs a gain");
+    if (M == 0) return 0;
+    StreamArgs a = {};
+    a.X = (const __nv_bfloat16*)x; a.ldx = ldx; a.xres = xres; a.ldr = ldr; a.gain = gain; a.eps = eps;
+    a.W = (const __nv_bfloat16*)w; a.ldw = ldw; a.C = c; a.ldc = ldc; a.mode = mode; a.M = M; a.N = N; a.K = K;
+    a.pair_offset = mode == WS_GLU_BF16 ? N : 0;
+    return dispatch_stream(a, (N + 15) / 16, mode == WS_GLU_BF16, pdl, stream);
+}
+
+// Stacked QKV projection with rotary encoding and cache write in the epilogue. W = [q rows; k rows; v
+// rows] ((nh + 2 nkv) * hd rows); q_out bfloat16 [M, >= nh*hd] receives the rotated queries; rotated keys
+// and the values go to the cache slot of each row (unless write_kv == 0). hd must be a multiple of 32;
+// rope == nullptr stores without rotation.
+GB_EXPORT int gb_gemm_stream_qkv(const void* x, long long ldx, const float* xres, long long ldr, const float* gain,
+                                 float eps, const void* w, long long ldw, void* q_out, long long ldq, int M, int K,
+                                 const float* rope, int max_pos, const int* positions, const int* slots, void* kcache,
+                                 void* vcache, int nh, int nkv, int hd, int page_size, long long num_pages, int write_kv,
+                                 int* status, int pdl, cudaStream_t stream) {
+    const int N = (nh + 2 * nkv) * hd;
+    if (check_common("gb_gemm_stream_qkv", x, xres, w, M, N, K, ldx, ldr, ldw)) return 1;
+    GB_REQUIRE(hd > 0 && hd % 32 == 0 && nh > 0 && nkv > 0, "gb_gemm_stream_qkv: head size %d must be a multiple of 32", hd);
+    GB_REQUIRE(x != nullptr || gain != nullptr, "gb_gemm_stream_qkv: normalising needs a gain");
+    GB_REQUIRE(page_size > 0 && positions && slots && status && ldq >= (long long)nh * hd, "gb_gemm_stream_qkv: bad arguments");
+    if (M == 0) return 0;
+    StreamArgs a = {};
+    a.X = (const __nv_bfloat16*)x; a.ldx = ldx; a.xres = xres; a.ldr = ldr; a.gain = gain; a.eps = eps;
+    a.W = (const __nv_bfloat16*)w; a.ldw = ldw; a.C = q_out; a.ldc = ldq; a.mode = WS_ROPE_QKV; a.M = M; a.N = N; a.K = K;
+    a.pair_offset = hd / 2;
+    a.rope = (const float2*)rope; a.positions = positions; a.slots = slots;
+    a.kcache = (__nv_bfloat16*)kcache; a.vcache = (__nv_bfloat16*)vcache;
+    a.nh = nh; a.nkv = nkv; a.hd = hd; a.page_size = page_size; a.max_pos = max_pos; a.write_kv = write_kv;
+    a.num_slots = num_pages * page_size; a.status = status;
+    return dispatch_stream(a, (nh + 2 * nkv) * (hd / 32), true, pdl, stream);
 }

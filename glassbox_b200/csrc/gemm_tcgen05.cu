@@ -192,20 +192,26 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(const __grid_constant
     if (kblocks > 0) ready = mbar_wait(&sh.accum, 0, abort_flag, status);
     tc_fence_after();
     if (ready) {
-        const int row = m0 + warp * 32 + lane;
+        // Each thread holds one row of 32 columns after tcgen05.ld. Writing rows per thread would touch
+        // 32 rows with 16 bytes each per instruction, so the chunk goes through shared memory (the
+        // pipeline stages are free by now) and comes back transposed: one row per instruction, lanes
+        // across 32 consecutive columns, 128 contiguous bytes.
+        float* stage = reinterpret_cast<float*>(tiles) + warp * (32 * 33);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
             uint32_t r[32];
             if (kblocks > 0) {
-                tmem_load32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);   // warp-wide: no divergence before it
+                tmem_load32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = 0u;
             }
-            if (row < M) {
+            if (mode == TC_STORE_BF16) {
+                // a thread's 32 columns are 64 contiguous bytes: store them directly, 16 bytes at a time
+                const int row = m0 + warp * 32 + lane;
                 const int col0 = n0 + c0;
-                if (mode == TC_STORE_BF16) {
-                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + col0;
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + col0;
+                if (row < M) {
                     if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
@@ -219,27 +225,31 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(const __grid_constant
                         for (int j = 0; j < 32; ++j)
                             if (col0 + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
                     }
+                }
+                continue;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
+            __syncwarp();
+            const int col = n0 + c0 + lane;
+            if (col < N) {
+                float* base = reinterpret_cast<float*>(C) + (size_t)(m0 + warp * 32) * ldc + col;
+                const int rows = min(32, M - (m0 + warp * 32));
+                if (mode == TC_ADD_F32) {
+                    // read the 32 residual values first (independent loads), then add and write
+                    float old[32];
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) old[rr] = rr < rows ? base[(size_t)rr * ldc] : 0.f;
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr)
+                        if (rr < rows) base[(size_t)rr * ldc] = old[rr] + stage[rr * 33 + lane];
                 } else {
-                    float* dst = reinterpret_cast<float*>(C) + (size_t)row * ldc + col0;
-                    const bool add = mode == TC_ADD_F32;
-                    if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            if (add) {
-                                const float4 o = *reinterpret_cast<const float4*>(dst + j);
-                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                            }
-                            *reinterpret_cast<float4*>(dst + j) = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] = (add ? dst[j] : 0.f) + __uint_as_float(r[j]);
-                    }
+                    for (int rr = 0; rr < 32; ++rr)
+                        if (rr < rows) base[(size_t)rr * ldc] = stage[rr * 33 + lane];
                 }
             }
+            __syncwarp();
         }
     }
 

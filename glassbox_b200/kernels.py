@@ -43,7 +43,11 @@ _SIGNATURES = {
     "gb_attention_decode": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                             _P, _P, _P],
     "gb_attention_decode_counters": [_I, _I, _I],
-    "gb_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P],
+    "gb_gemm_stream": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _I, _I, _P],
+    "gb_gemm_stream_qkv": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
+                           _LL, _I, _P, _I, _P],
+    "gb_attention_decode_mma_pdl": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
+                                    _P, _P, _I, _P],
     "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
                                 _P, _P],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
@@ -188,18 +192,43 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
 
 
 STREAM_MAX_ROWS = 64
+#: above this many rows the norm is not folded into the stream kernels (every block would repeat
+#: the normalisation of all rows) and QKV keeps one strip per block (twice the blocks)
+STREAM_FUSE_MAX_ROWS = 16
 
 
-def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the weight-streaming kernel (few rows, bfloat16) takes these operands."""
-    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= STREAM_MAX_ROWS
-            and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+#: launch the decode-path kernels under programmatic stream serialisation (they wait for their
+#: predecessor themselves, after work that does not depend on it)
+USE_PDL = True
 
 
-def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, gated: bool = False) -> None:
+def gemm_stream_supported(a, w: torch.Tensor, rows: Optional[int] = None) -> bool:
+    """Whether the weight-streaming kernel (few rows, bfloat16 weights) takes these operands. ``a``
+    is a bfloat16 [M, K] tensor, or a float32 one that the kernel normalises on the way in."""
+    M, K = a.shape
+    if w.dtype != torch.bfloat16 or M > STREAM_MAX_ROWS or K % 8 or w.stride(0) % 8 or w.data_ptr() % 16:
+        return False
+    if a.dtype == torch.bfloat16:
+        return a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+    return a.dtype == torch.float32 and a.stride(0) % 4 == 0 and a.data_ptr() % 16 == 0
+
+
+def _stream_input(a: torch.Tensor, norm):
+    """(x, ldx, xres, ldr, gain, eps) for the stream kernels: bfloat16 activations as they are, or
+    float32 rows with the (gain, eps) of an RMSNorm to apply on the way in."""
+    if norm is None:
+        assert a.dtype == torch.bfloat16
+        return _ptr(a), a.stride(0), 0, 0, 0, 0.0
+    gain, eps = norm
+    assert a.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == a.shape[1]
+    return 0, 0, _ptr(a), a.stride(0), _ptr(gain), float(eps)
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, gated: bool = False,
+                norm=None) -> None:
     """c[M, N] (+)= a[M, K] @ w[N, K]^T for M <= 64 on the tensor cores, streaming w once. With
-    ``gated``, w is [2I, K] (gate rows, then up rows) and c[M, I] = silu(a gate^T) * (a up^T)."""
+    ``gated``, w is [2I, K] (gate rows, then up rows) and c[M, I] = silu(a gate^T) * (a up^T). With
+    ``norm`` = (gain, eps), ``a`` is the float32 residual and is RMS-normalised on the way in."""
     _cuda(a, w, c)
     M, K = a.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
@@ -213,7 +242,33 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
     else:
         mode = 0 if c.dtype == torch.bfloat16 else 1
         assert c.dtype in (torch.bfloat16, torch.float32)
-    _call("gb_gemm_stream", _ptr(a), _ptr(w), _ptr(c), mode, M, N, K, a.stride(0), w.stride(0), c.stride(0), _stream())
+    x, ldx, xres, ldr, gain, eps = _stream_input(a, norm)
+    _call("gb_gemm_stream", x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(c), c.stride(0), mode, M, N, K,
+          1 if USE_PDL else 0, _stream())
+
+
+def gemm_stream_qkv_supported(a, w: torch.Tensor, hd: int, q_out: torch.Tensor) -> bool:
+    return (gemm_stream_supported(a, w) and a.shape[0] <= STREAM_FUSE_MAX_ROWS and hd % 32 == 0
+            and q_out.dtype == torch.bfloat16)
+
+
+def gemm_stream_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[torch.Tensor],
+                    positions: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nh: int,
+                    nkv: int, hd: int, page_size: int, write_kv: bool, status: torch.Tensor, norm=None) -> None:
+    """Stacked QKV projection for M <= 64 with rotary encoding and the cache write in its epilogue:
+    q_out[:, :nh*hd] receives the rotated queries, rotated keys and values go to each row's cache slot.
+    Full rotary (table [max_pos, hd/2, 2]) or none (cos_sin None)."""
+    _cuda(a, w, q_out, cos_sin, positions, slots, kcache, vcache, status)
+    M, K = a.shape
+    assert w.shape == ((nh + 2 * nkv) * hd, K) and q_out.stride(1) == 1 and q_out.shape[0] == M
+    assert kcache.dtype == vcache.dtype == torch.bfloat16 and kcache.is_contiguous() and vcache.is_contiguous()
+    if cos_sin is not None:
+        assert cos_sin.shape[1] == hd // 2
+    x, ldx, xres, ldr, gain, eps = _stream_input(a, norm)
+    _call("gb_gemm_stream_qkv", x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(q_out), q_out.stride(0), M, K,
+          _ptr(cos_sin), cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slots), _ptr(kcache),
+          _ptr(vcache), nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status),
+          1 if USE_PDL else 0, _stream())
 
 
 def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:
@@ -321,10 +376,10 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
     assert part_acc.numel() >= n * nh * 4 * splits * hd and part_ml.numel() >= n * nh * 4 * splits * 2
     assert counters.numel() >= n * nkv
-    _call("gb_attention_decode_mma", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
+    _call("gb_attention_decode_mma_pdl", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
           _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
           kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml), _ptr(counters),
-          _ptr(status), _stream())
+          _ptr(status), 1 if USE_PDL else 0, _stream())
 
 
 def attention_prefill_supported(dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:

@@ -13,11 +13,13 @@ import torch
 
 from .. import kernels
 from ..weights.binding import ParamSpec
-from .base import Mixer, PagedKvSpec, build_part, register_part
-from .linear import linear
+from .base import Mixer, PagedKvSpec, Position, build_part, register_part
+from .linear import _resolve, linear
 
 
 class GqaAttention(Mixer):
+    accepts_deferred_input = True
+
     def __init__(self, spec, *, hidden_size: int):
         super().__init__(spec)
         s = spec
@@ -46,12 +48,21 @@ class GqaAttention(Mixer):
     def forward(self, ctx, h, residual, cache, writes_cache: bool) -> None:
         n = h.shape[0]
         qkv = ctx.scratch("qkv", (n, self.qd + 2 * self.kvd))
-        linear(ctx, h, self.params["wqkv"], qkv)
         table = self.position.fused_table(qkv.device)
-        if table is None:
-            self.position.apply_qk(ctx, qkv, self.nh, self.nkv, self.hd)
-        kernels.rope_kv_write(qkv, table, ctx.positions, cache.slots, cache.k, cache.v, self.nh, self.nkv, self.hd,
-                              self.position.rotary_dim, cache.page_size, writes_cache, ctx.status)
+        x, norm, _ = _resolve(h)
+        plain_rotary = (table is not None and self.position.rotary_dim == self.hd) or \
+            (table is None and type(self.position).apply_qk is Position.apply_qk)
+        if (plain_rotary and (norm is not None or x.dtype == torch.bfloat16)
+                and kernels.gemm_stream_qkv_supported(x, self.params["wqkv"], self.hd, qkv)):
+            # few rows: one kernel normalises, projects, rotates and writes the cache
+            kernels.gemm_stream_qkv(x, self.params["wqkv"], qkv, table, ctx.positions, cache.slots, cache.k, cache.v,
+                                    self.nh, self.nkv, self.hd, cache.page_size, writes_cache, ctx.status, norm=norm)
+        else:
+            linear(ctx, h, self.params["wqkv"], qkv)
+            if table is None:
+                self.position.apply_qk(ctx, qkv, self.nh, self.nkv, self.hd)
+            kernels.rope_kv_write(qkv, table, ctx.positions, cache.slots, cache.k, cache.v, self.nh, self.nkv, self.hd,
+                                  self.position.rotary_dim, cache.page_size, writes_cache, ctx.status)
         att = ctx.scratch("att", (n, self.qd))
         self.attend(ctx, qkv[:, :self.qd], att, cache)
         linear(ctx, att, self.params["wo"], residual, accumulate=True)

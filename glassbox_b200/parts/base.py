@@ -70,6 +70,29 @@ class Norm(Part):
     def forward(self, ctx, x, out, rows=None) -> None:
         raise NotImplementedError
 
+    def as_rms(self):
+        """(gain, eps) if this norm is a plain RMSNorm that a GEMM kernel may apply on the way in, else
+        None (the norm then always runs as its own kernel)."""
+        return None
+
+
+class DeferredNorm:
+    """The normalised input of a mixer or feed-forward, not yet computed. A part that sets
+    ``accepts_deferred_input`` receives this instead of a tensor and hands it to ``linear``, which
+    either folds the norm into the product (few rows, RMSNorm) or calls ``tensor()``; a part that
+    needs the activations themselves calls ``tensor()`` and gets them (computed once)."""
+
+    def __init__(self, ctx, norm: "Norm", x: torch.Tensor, name: str = "h"):
+        self.ctx, self.norm, self.x, self.name = ctx, norm, x, name
+        self._tensor = None
+        self.shape = x.shape
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self.ctx.scratch(self.name, tuple(self.x.shape))
+            self.norm.forward(self.ctx, self.x, self._tensor)
+        return self._tensor
+
 
 class Position(Part):
     rotary_dim: int = 0
@@ -82,6 +105,9 @@ class Position(Part):
 
 
 class Mixer(Part):
+    #: set by parts whose ``forward`` can take a ``DeferredNorm`` as ``h``
+    accepts_deferred_input = False
+
     def cache_spec(self):
         return None
 
@@ -90,6 +116,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_deferred_input = False
+
     def forward(self, ctx, h, residual) -> None:
         raise NotImplementedError
 

@@ -6,7 +6,7 @@ wiring (post-norm, parallel branches) is another registered class.
 """
 from __future__ import annotations
 
-from .base import Part, build_part, register_part
+from .base import DeferredNorm, Part, build_part, register_part
 
 
 class PreNormBlock(Part):
@@ -22,12 +22,10 @@ class PreNormBlock(Part):
         return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn}
 
     def forward(self, ctx, x, cache, writes_cache: bool) -> None:
-        n = x.shape[0]
-        h = ctx.scratch("h", (n, self.hidden_size))
-        self.mixer_norm.forward(ctx, x, h)
-        self.mixer.forward(ctx, h, x, cache, writes_cache)
-        self.ffn_norm.forward(ctx, x, h)
-        self.ffn.forward(ctx, h, x)
+        h = DeferredNorm(ctx, self.mixer_norm, x)
+        self.mixer.forward(ctx, h if self.mixer.accepts_deferred_input else h.tensor(), x, cache, writes_cache)
+        h = DeferredNorm(ctx, self.ffn_norm, x)
+        self.ffn.forward(ctx, h if self.ffn.accepts_deferred_input else h.tensor(), x)
 
 
 register_part("arrangement", "pre_norm", lambda kind, *, layer_spec, hidden_size: PreNormBlock(layer_spec, hidden_size=hidden_size),

@@ -11,22 +11,42 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from .base import DeferredNorm
 
 
-def linear(ctx, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-    if kernels.gemm_stream_supported(a, w):
-        kernels.gemm_stream(a, w, out, accumulate)
-    elif a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and kernels.gemm_tc_supported(a, w, out):
-        kernels.gemm_tc(a, w, out, accumulate, ctx.status)
+def _resolve(a):
+    """(tensor the stream kernel can take, norm or None, deferred or None) for an input that may be a
+    ``DeferredNorm``."""
+    if isinstance(a, DeferredNorm):
+        rms = a.norm.as_rms()
+        if rms is not None and a._tensor is None and a.x.shape[0] <= kernels.STREAM_FUSE_MAX_ROWS:
+            return a.x, rms, a
+        return a.tensor(), None, None
+    return a, None, None
+
+
+def linear(ctx, a, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """``a`` is a tensor or a ``DeferredNorm``; the latter is folded into the weight-streaming kernel
+    when that kernel runs, and computed first otherwise."""
+    x, norm, deferred = _resolve(a)
+    if kernels.gemm_stream_supported(x, w) and (norm is not None or x.dtype == torch.bfloat16):
+        kernels.gemm_stream(x, w, out, accumulate, norm=norm)
+        return
+    if deferred is not None:
+        x = deferred.tensor()
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and kernels.gemm_tc_supported(x, w, out):
+        kernels.gemm_tc(x, w, out, accumulate, ctx.status)
     else:
-        kernels.gemm_simt(a, w, out, accumulate)
+        kernels.gemm_simt(x, w, out, accumulate)
 
 
-def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
+def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
     """act = silu(a Wgate^T) * (a Wup^T) in one kernel when the shape allows; returns False (and
     does nothing) otherwise, and the caller runs the product and the activation separately."""
     inter = w_gate_up.shape[0] // 2
-    if kernels.gemm_stream_supported(a, w_gate_up) and inter % 16 == 0 and act.dtype == torch.bfloat16:
-        kernels.gemm_stream(a, w_gate_up, act, gated=True)
+    x, norm, _ = _resolve(a)
+    if (kernels.gemm_stream_supported(x, w_gate_up) and (norm is not None or x.dtype == torch.bfloat16)
+            and inter % 16 == 0 and act.dtype == torch.bfloat16):
+        kernels.gemm_stream(x, w_gate_up, act, gated=True, norm=norm)
         return True
     return False

@@ -10,6 +10,8 @@ from .linear import gated_linear, linear
 
 
 class SwiGlu(FeedForward):
+    accepts_deferred_input = True
+
     def __init__(self, spec, *, hidden_size: int):
         super().__init__(spec)
         self.hidden_size = hidden_size

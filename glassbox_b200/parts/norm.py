@@ -19,5 +19,8 @@ class RmsNorm(Norm):
     def forward(self, ctx, x, out, rows=None) -> None:
         kernels.rmsnorm(x, self.params["weight"], out, self.eps, rows)
 
+    def as_rms(self):
+        return self.params["weight"], self.eps
+
 
 register_part("norm", "rmsnorm", RmsNorm, replace=True)

@@ -548,3 +548,69 @@ def test_attention_prefill_each_row_finds_its_own_far_key():
     ref = ref_attention(q, dense, [0] * L, list(range(L)), nh, nkv, hd ** -0.5, None)
     diff = (out.cpu().double().reshape(L, nh, hd) - ref).abs().amax(dim=(1, 2))
     assert diff.max() <= tol(dtype, 2), f"position {int(diff.argmax())} (target {targets[int(diff.argmax())]})"
+
+
+@pytest.mark.parametrize("M", [1, 8, 23, 64])
+@pytest.mark.parametrize("N, K", [(576, 576), (100, 264), (3072, 1544)])
+def test_gemm_stream_with_the_norm_folded_in(M, N, K):
+    from glassbox_b200 import kernels
+    x = torch.randn(M, K, device=DEV) * 3
+    gain = 1 + 0.1 * torch.randn(K, device=DEV)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    h = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+    kernels.rmsnorm(x, gain, h, 1e-5)
+    want = torch.empty(M, N, device=DEV)
+    kernels.gemm_stream(h, w, want)                           # the two-kernel way
+    got = torch.empty(M, N, device=DEV)
+    assert kernels.gemm_stream_supported(x, w)
+    kernels.gemm_stream(x, w, got, norm=(gain, 1e-5))         # the folded way
+    xd = x.double()
+    ref = (gain.double() * (xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5))) @ w.double().T
+    assert (got.double() - ref).abs().max() <= tol(torch.bfloat16, 2)
+    assert (got - want).abs().max() <= tol(torch.bfloat16, 1)   # same roundings up to the order of one sum
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 33, 64])
+@pytest.mark.parametrize("nh, nkv, hd, d, ps, rotary", [(9, 3, 64, 576, 16, True), (2, 1, 32, 96, 32, True), (4, 4, 128, 256, 16, False)])
+def test_gemm_stream_qkv_with_norm_rotary_and_cache_write(M, nh, nkv, hd, d, ps, rotary):
+    from glassbox_b200 import kernels
+    from glassbox_b200.parts.rope import rotary_table
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(M)
+    x = (torch.randn(M, d, generator=g) * 2).to(DEV)
+    gain = (1 + 0.1 * torch.randn(d, generator=g)).to(DEV)
+    w = (torch.randn((nh + 2 * nkv) * hd, d, generator=g) / math.sqrt(d)).to(dtype).to(DEV)
+    table = rotary_table(1e5, hd, 400).to(DEV) if rotary else None
+    positions = torch.randint(0, 400, (M,), generator=g).to(torch.int32)
+    pages = 12
+    slots = torch.randperm(pages * ps, generator=g)[:M].to(torch.int32)
+    if M > 2:
+        positions[1] = -1                                  # a padding row: nothing may be stored for it
+    # the separate kernels
+    h = torch.empty(M, d, device=DEV, dtype=dtype)
+    kernels.rmsnorm(x, gain, h, 1e-6)
+    qkv = torch.empty(M, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
+    kernels.gemm_stream(h, w, qkv)
+    kc = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    st = status()
+    kernels.rope_kv_write(qkv, table, positions.to(DEV), slots.to(DEV), kc, vc, nh, nkv, hd, hd, ps, True, st)
+    # the one kernel
+    q2 = torch.zeros(M, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    assert kernels.gemm_stream_qkv_supported(x, w, hd, q2)
+    kernels.gemm_stream_qkv(x, w, q2, table, positions.to(DEV), slots.to(DEV), kc2, vc2, nh, nkv, hd, ps, True, st,
+                            norm=(gain, 1e-6))
+    assert int(st) == 0
+    live = positions >= 0
+    t = tol(dtype, 2)
+    assert (q2[live.to(DEV), :nh * hd].float() - qkv[live.to(DEV), :nh * hd].float()).abs().max() <= t
+    assert (kc2.float() - kc.float()).abs().max() <= t and (vc2.float() - vc.float()).abs().max() <= t
+    assert float(q2[~live.to(DEV)].abs().max() if (~live).any() else 0.0) == 0.0
+    written = kc2.abs().sum(dim=(1, 3)).flatten().nonzero().numel()     # (page, offset) rows touched
+    assert written == int(live.sum())
+    # write_kv off: queries only
+    kc3, vc3 = torch.zeros_like(kc), torch.zeros_like(vc)
+    kernels.gemm_stream_qkv(x, w, q2, table, positions.to(DEV), slots.to(DEV), kc3, vc3, nh, nkv, hd, ps, False, st,
+                            norm=(gain, 1e-6))
+    assert float(kc3.abs().max()) == 0.0 and float(vc3.abs().max()) == 0.0
