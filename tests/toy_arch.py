@@ -79,6 +79,20 @@ class RunningState(Mixer):
                 cache.state[seq.slot].copy_(s)
 
 
+@dataclass(frozen=True)
+class ZeroMixerSpec:
+    kind: str = "test_zero_mixer"
+
+
+class ZeroMixer(Mixer):
+    def __init__(self, spec, *, hidden_size):
+        super().__init__(spec)
+
+    def forward(self, ctx, h, residual, cache, writes_cache):
+        return None
+
+
+register_part("mixer", "test_zero_mixer", ZeroMixer, replace=True)
 register_part("norm", "test_identity_norm", IdentityNorm, replace=True)
 register_part("ffn", "test_zero_ffn", ZeroFfn, replace=True)
 register_part("mixer", "test_running_state", RunningState, replace=True)
@@ -133,6 +147,48 @@ def _bind_toy_state(config):
 
 
 register_architecture(Architecture("ToyStateForCausalLM", _parse_toy_state, _bind_toy_state), replace=True)
+
+
+def _parse_one_part(raw):
+    """``OnePartForCausalLM``: a single layer in which exactly one part is real and every other part
+    is an identity or adds nothing; the embedding table holds the test's input vectors (token i is
+    input i) and the head is the identity, so the logits ARE the part's output (plus its input, the
+    residual). raw["part"] is "norm" | "ffn" | "mixer" | "block"."""
+    d, hd = raw["hidden_size"], raw.get("head_dim", 16)
+    part = raw["part"]
+    ident, real_norm = IdentityNormSpec(), RmsNormSpec(eps=raw.get("eps", 1e-5))
+    position = NoPositionSpec() if raw.get("rope_theta") is None else \
+        RopeSpec(theta=float(raw["rope_theta"]), rotary_dim=hd, max_position=raw["max_position"])
+    attn = GqaAttentionSpec(num_heads=raw.get("num_heads", 1), num_kv_heads=raw.get("num_kv_heads", 1), head_dim=hd,
+                            scale=float(raw.get("scale", hd ** -0.5)), position=position, window=raw.get("window"))
+    ffn = SwiGluSpec(intermediate_size=raw.get("intermediate_size", 16))
+    layer = LayerSpec(mixer=attn if part in ("mixer", "block") else ZeroMixerSpec(),
+                      ffn=ffn if part in ("ffn", "block") else ZeroFfnSpec(),
+                      mixer_norm=real_norm if part == "block" else ident,
+                      ffn_norm=real_norm if part == "block" else ident)
+    return ModelConfig(architecture="OnePartForCausalLM", vocab_size=raw["vocab_size"], hidden_size=d,
+                       max_position=raw["max_position"], tie_word_embeddings=False, layers=(layer,),
+                       schedule=(RunSpec(0, 0),), final_norm=real_norm if part == "norm" else ident, raw=dict(raw))
+
+
+def _bind_one_part(config):
+    b = {"embed.weight": Stacked(("embed",)), "head.weight": Stacked(("head",))}
+    part = config.raw["part"]
+    if part in ("mixer", "block"):
+        b["layers.0.mixer.wqkv"] = Stacked(("wq", "wk", "wv"))
+        b["layers.0.mixer.wo"] = Stacked(("wo",))
+    if part in ("ffn", "block"):
+        b["layers.0.ffn.w_gate_up"] = Stacked(("gate", "up"))
+        b["layers.0.ffn.w_down"] = Stacked(("down",))
+    if part == "block":
+        b["layers.0.mixer_norm.weight"] = Stacked(("norm_a",))
+        b["layers.0.ffn_norm.weight"] = Stacked(("norm_b",))
+    if part == "norm":
+        b["final_norm.weight"] = Stacked(("norm",))
+    return b
+
+
+register_architecture(Architecture("OnePartForCausalLM", _parse_one_part, _bind_one_part), replace=True)
 
 
 # ----------------------------------------------------------------- the probe model, and its truth
