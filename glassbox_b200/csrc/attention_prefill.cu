@@ -1,11 +1,14 @@
 // Causal grouped-query flash attention for prompt portions, over the paged cache, in bfloat16 on
 // the tensor cores (mma.sync m16n8k16, float32 softmax statistics and accumulators).
 //
-// One block = 64 consecutive query rows of one request for one query head; its four warps own 16
-// rows each. Keys and values are read from the cache pages through the request's block table (the
+// One block = 64 consecutive query rows of one request for one query head, eight warps in two groups:
+// within a group the four warps own 16 rows each; the groups take alternate tiles of 64 keys (what
+// bounds a causal kernel is its longest block, the one with the most key tiles, so the tiles of one
+// block are worked on by two groups at once) and their results are merged at the end. Keys and values are read from the cache pages through the request's block table (the
 // rows of this very step were stored there before this kernel runs, so a portion attends to the
 // pages earlier portions left and to itself alike), 64 keys at a time, staged in shared memory with
-// cp.async (double buffered, 16-byte chunks XOR-swizzled by row so that ldmatrix is conflict free).
+// cp.async (three buffers: loads run two tiles ahead; 16-byte chunks XOR-swizzled by row so that
+// ldmatrix is conflict free).
 // A query at position p sees keys max(0, p-window+1) .. p (crates/glassbox-core/src/model.rs:278-317);
 // tiles of keys that no row of the block can see are never loaded.
 // Row-wise online softmax: m and l per row, O rescaled when m grows; P is rounded to bfloat16 for
@@ -15,6 +18,7 @@
 #include <cuda_pipeline.h>
 
 constexpr int PF_BM = 64, PF_BN = 64;
+constexpr int PF_STAGES = 3;   // key/value tiles in flight: loads run two tiles ahead of the arithmetic
 constexpr int PF_MAX_PAGES = 1024;
 constexpr float PF_NEG_BIG = -1.0e30f;
 
@@ -38,7 +42,7 @@ __device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(128) attention_prefill_kernel(
+__global__ void __launch_bounds__(256) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out, long long out_stride,
     const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
     const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_first_row,
@@ -47,13 +51,16 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(
     constexpr int KS = HD / 16, NT = HD / 8, CPR = HD / 8;   // k16 steps, n8 tiles, 16-byte chunks per row
     extern __shared__ __align__(128) unsigned char pf_smem[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(pf_smem);   // [64][HD]
-    __nv_bfloat16* Ks = Qs + PF_BM * HD;                             // [2][64][HD]
-    __nv_bfloat16* Vs = Ks + 2 * PF_BN * HD;                         // [2][64][HD]
     __shared__ int pages_s[PF_MAX_PAGES];
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int group = threadIdx.x >> 7;                    // which half of the key tiles
+    const int tid = threadIdx.x & 127, lane = tid & 31, warp = tid >> 5;   // within the group
+    __nv_bfloat16* Ks = Qs + PF_BM * HD + group * (2 * PF_STAGES * PF_BN * HD);   // [PF_STAGES][64][HD], per group
+    __nv_bfloat16* Vs = Ks + PF_STAGES * PF_BN * HD;                               // [PF_STAGES][64][HD]
+    auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); };
     const int g = lane >> 2, t = lane & 3;
-    const int qt = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+    const int qt = gridDim.x - 1 - blockIdx.x;   // later tiles see more keys: start the longest blocks first
+    const int head = blockIdx.y, seq = blockIdx.z;
     const int row0 = seq_first_row[seq];
     const int nrows = seq_first_row[seq + 1] - row0;
     if (qt * PF_BM >= nrows) return;
@@ -71,7 +78,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(
     const bool staged = n_pages <= PF_MAX_PAGES;
     int bad = 0;
     if (staged) {
-        for (int i = tid; i < n_pages; i += 128) {
+        for (int i = threadIdx.x; i < n_pages; i += 256) {
             int page = table[page_lo + i];
             if (page < 0 || page >= num_pages) {
                 if (((page_lo + i + 1) << page_shift) > key_lo) bad = 1;   // pages behind the window may be gone
@@ -115,17 +122,21 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(
         }
     };
 
-    // Q tile
-    for (int c = tid; c < PF_BM * CPR; c += 128) {
-        const int r = c / CPR, ch = c % CPR;
-        const int dst = swz(r, ch);
-        if (q_lo + r < nrows)
-            __pipeline_memcpy_async(Qs + dst, q + (size_t)(row0 + q_lo + r) * q_stride + (size_t)head * HD + ch * 8, 16);
-        else
-            *reinterpret_cast<uint4*>(Qs + dst) = make_uint4(0, 0, 0, 0);
-    }
-    load_kv(kt_begin, 0);
+    // this group's tiles are kt_first, kt_first + 2, ...; the first two are requested at once
+    const int kt_first = kt_begin + group;
+    if (kt_first <= kt_end) load_kv(kt_first, 0);
     __pipeline_commit();
+    if (kt_first + 2 <= kt_end) load_kv(kt_first + 2, 1);
+    __pipeline_commit();   // (possibly empty groups: the waits below count groups)
+    // Q tile: plain loads by all 256 threads, visible to both groups after the barrier
+    for (int c = threadIdx.x; c < PF_BM * CPR; c += 256) {
+        const int r = c / CPR, ch = c % CPR;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (q_lo + r < nrows)
+            v = *reinterpret_cast<const uint4*>(q + (size_t)(row0 + q_lo + r) * q_stride + (size_t)head * HD + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + swz(r, ch)) = v;
+    }
+    __syncthreads();
 
     const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(Qs);
     const uint32_t ks_addr = (uint32_t)__cvta_generic_to_shared(Ks);
@@ -146,25 +157,23 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(
     const int warp_pos_lo = pos_lo + warp * 16;
     const int warp_key_lo = (window > 0 && warp_pos_lo + 1 > window) ? warp_pos_lo + 1 - window : 0;
 
-    for (int kt = kt_begin; kt <= kt_end; ++kt) {
-        const int buf = (kt - kt_begin) & 1;
-        if (kt + 1 <= kt_end) {
-            load_kv(kt + 1, buf ^ 1);
-            __pipeline_commit();
-            __pipeline_wait_prior(1);
-        } else {
-            __pipeline_wait_prior(0);
-        }
-        __syncthreads();
-        if (kt == kt_begin) {
-            // A fragments of Q: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+    // A fragments of Q: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
 #pragma unroll
-            for (int s = 0; s < KS; ++s) {
-                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                const int ch = 2 * s + (lane >> 4);
-                ldmatrix_x4(qf[s], qs_addr + (uint32_t)swz(r, ch) * 2);
-            }
-        }
+    for (int s = 0; s < KS; ++s) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int ch = 2 * s + (lane >> 4);
+        ldmatrix_x4(qf[s], qs_addr + (uint32_t)swz(r, ch) * 2);
+    }
+
+    for (int kt = kt_first; kt <= kt_end; kt += 2) {
+        const int li = (kt - kt_first) >> 1;   // index among this group's tiles
+        const int buf = li % PF_STAGES;
+        // the tile two ahead goes into the buffer of the tile before this one; the whole group passed
+        // the barrier at the end of that iteration, so it is free
+        if (kt + 4 <= kt_end) load_kv(kt + 4, (li + 2) % PF_STAGES);
+        __pipeline_commit();
+        __pipeline_wait_prior(2);   // all but the two newest groups: tile kt has landed
+        group_sync();
         const int key0 = kt * PF_BN;
         // a warp whose rows all lie before this tile, or whose window lies after it, has nothing to do
         if (key0 <= warp_pos_hi && key0 + PF_BN > warp_key_lo) {
@@ -247,16 +256,47 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(
                 }
             }
         }
-        __syncthreads();
+        group_sync();
     }
     if (bad) atomicOr(status, GB_STATUS_BAD_SLOT);
 
-    // normalise and store
+    // merge the two groups: group 1 parks its state in shared memory (the tiles are no longer needed),
+    // group 0 combines it with its own
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
+    __syncthreads();
+    float* park = reinterpret_cast<float*>(Qs + PF_BM * HD);   // [128 threads][NT*4 + 4]
+    if (group == 1) {
+        float* mine = park + tid * (NT * 4 + 4);
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mine[j * 4 + e] = o[j][e];
+        mine[NT * 4] = m_run[0]; mine[NT * 4 + 1] = m_run[1];
+        mine[NT * 4 + 2] = l_run[0]; mine[NT * 4 + 3] = l_run[1];
+    }
+    __syncthreads();
+    if (group == 1) return;
+    {
+        const float* other = park + tid * (NT * 4 + 4);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float m1 = other[NT * 4 + h], l1 = other[NT * 4 + 2 + h];
+            const float m = fmaxf(m_run[h], m1);
+            const float a0 = exp2f((m_run[h] - m) * sl2), a1 = exp2f((m1 - m) * sl2);
+            l_run[h] = l_run[h] * a0 + l1 * a1;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                o[j][2 * h] = o[j][2 * h] * a0 + other[j * 4 + 2 * h] * a1;
+                o[j][2 * h + 1] = o[j][2 * h + 1] * a0 + other[j * 4 + 2 * h + 1] * a1;
+            }
+        }
+    }
+
+    // normalise and store
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = q_lo + warp * 16 + g + 8 * h;
@@ -275,7 +315,7 @@ static int launch_prefill(const void* q, long long q_stride, void* out, long lon
                           const void* vcache, const int* block_tables, int max_pages, const int* seq_first_row,
                           const int* seq_start_pos, int num_seqs, int max_rows_per_seq, int nh, int nkv, int page_size,
                           long long num_pages, float scale, int window, int* status, cudaStream_t stream) {
-    constexpr int smem = (PF_BM * HD + 4 * PF_BN * HD) * 2;
+    constexpr int smem = (PF_BM * HD + 2 * 2 * PF_STAGES * PF_BN * HD) * 2;   // Q, and K/V stages of both groups
     auto kernel = attention_prefill_kernel<HD>;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
@@ -286,7 +326,7 @@ static int launch_prefill(const void* q, long long q_stride, void* out, long lon
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
     dim3 grid(gb_ceil_div(max_rows_per_seq, PF_BM), nh, num_seqs);
-    kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+    kernel<<<grid, 256, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                                         (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
                                         max_pages, seq_first_row, seq_start_pos, nh, nkv, page_size, page_shift,
                                         num_pages, scale, window, status);
