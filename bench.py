@@ -223,7 +223,7 @@ def main():
             T = 2048
             toks = rng.integers(0, vocab, size=T).tolist()
             times = []
-            for rep in range(4):
+            for rep in range(8):
                 eng.add_request("p")
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -232,7 +232,7 @@ def main():
                 e1.record()
                 torch.cuda.synchronize()
                 eng.free_request("p")
-                if rep:
+                if rep >= 3:     # three warm-up repetitions (the second one records the step's CUDA graph)
                     times.append(e0.elapsed_time(e1))
             pms = sum(times) / len(times)
             flops = prefill_flops(shape, T)

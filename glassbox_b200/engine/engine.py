@@ -90,6 +90,8 @@ class Engine:
         self.use_graphs = bool(use_graphs)
         self.max_graph_batch = 64
         self._graphs: Dict[tuple, dict] = {}
+        self._seen: Dict[tuple, int] = {}
+        self.max_graphs = 48
         self.graph_replays = 0
         self.sampled: Optional[torch.Tensor] = None
         self.h2d_bytes_last = 0
@@ -278,21 +280,49 @@ class Engine:
         if decode_only:
             logits = self._step_graph(entries, S, max_pages, sampling)
         else:
-            off = self._layout(n, S, n_want, max_pages)
-            host = self._fill(entries, off, n, S, max_pages, sampling)
-            if off["_size"] > self._meta_dev.numel():
-                self._meta_dev = torch.empty(1 << int(off["_size"] - 1).bit_length(), dtype=torch.int32,
-                                             device=self.device)
-            self._stage_copy(host, self._meta_dev)
-            ctx = self.ctx
-            self._bind(ctx, self._meta_dev, off, n, S, n_want, max_pages)
-            ctx.seqs, ctx.max_context = self._seqs, self._max_ctx
-            ctx.max_rows_per_seq = max(s.n_rows for s in self._seqs)
-            ctx.decode_only = (n == S)
-            logits = self.model.forward(ctx)
-            if sampling is not None and n_want:
-                self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
-                kernels.sample(logits, self.sampled, ctx.temperature, ctx.uniform)
+            logits = None
+            max_rows = max(len(e.tokens) for e in entries)
+            small_logits = n_want * self.config.vocab_size * 4 <= (64 << 20)   # each graph owns its logits buffer
+            if self.use_graphs and not self.device_cache.has_state and small_logits:
+                # A step whose shape (rows, requests, longest run, wanted rows, table width) has been seen
+                # before is recorded once and replayed from then on: chunked prompts repeat their shape.
+                Pb = max(8, 1 << max(max_pages - 1, 0).bit_length())
+                key = ("step", n, S, max_rows, n_want, Pb)
+                g = self._graphs.get(key)
+                off = self._layout(n, S, n_want, Pb)
+                if g is None:
+                    if len(self._seen) > 4096:
+                        self._seen.clear()
+                    self._seen[key] = self._seen.get(key, 0) + 1
+                    if self._seen[key] >= 2 and len(self._graphs) < self.max_graphs:
+                        host = self._fill(entries, off, n, S, Pb, sampling)
+                        g = self._capture(key, off, host, n, S, n_want, Pb, max_rows, decode_only=(n == S))
+                        self.sampled = g["sampled"][:n_want] if sampling is not None else None
+                        logits = g["logits"][:n_want]       # the warm-up run of the capture computed this step
+                else:
+                    host = self._fill(entries, off, n, S, Pb, sampling)
+                    self._stage_copy(host, g["meta"])
+                    g["graph"].replay()
+                    kernels.launch_count += g["nodes"]
+                    self.graph_replays += 1
+                    self.sampled = g["sampled"][:n_want] if sampling is not None else None
+                    logits = g["logits"][:n_want]
+            if logits is None:
+                off = self._layout(n, S, n_want, max_pages)
+                host = self._fill(entries, off, n, S, max_pages, sampling)
+                if off["_size"] > self._meta_dev.numel():
+                    self._meta_dev = torch.empty(1 << int(off["_size"] - 1).bit_length(), dtype=torch.int32,
+                                                 device=self.device)
+                self._stage_copy(host, self._meta_dev)
+                ctx = self.ctx
+                self._bind(ctx, self._meta_dev, off, n, S, n_want, max_pages)
+                ctx.seqs, ctx.max_context = self._seqs, self._max_ctx
+                ctx.max_rows_per_seq = max_rows
+                ctx.decode_only = (n == S)
+                logits = self.model.forward(ctx)
+                if sampling is not None and n_want:
+                    self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
+                    kernels.sample(logits, self.sampled, ctx.temperature, ctx.uniform)
         if commit:
             for e in entries:
                 self.cache.commit(e.request, e.tokens)
@@ -309,7 +339,15 @@ class Engine:
         host = self._fill(entries, off, Sb, Sb, Pb, sampling)
         g = self._graphs.get(key)
         if g is None:
-            g = self._capture(key, off, host)
+            blank = np.zeros(off["_size"], dtype=np.int32)      # an all-padding batch: every row skipped
+            blank[off["positions"]:off["positions"] + Sb] = -1
+            for gi in range(len(self.cache.groups)):
+                blank[off[f"slots{gi}"]:off[f"slots{gi}"] + Sb] = -1
+                blank[off[f"tables{gi}"]:off[f"tables{gi}"] + Sb * Pb] = -1
+            blank[off["row_seq"]:off["row_seq"] + Sb] = np.arange(Sb)
+            blank[off["want"]:off["want"] + Sb] = np.arange(Sb)
+            blank[off["seq_first_row"]:off["seq_first_row"] + Sb + 1] = np.arange(Sb + 1)
+            g = self._capture(key, off, blank, Sb, Sb, Sb, Pb, 1, decode_only=True)
         self._stage_copy(host, g["meta"])
         g["graph"].replay()
         kernels.launch_count += g["nodes"]
@@ -317,30 +355,23 @@ class Engine:
         self.graph_replays += 1
         return g["logits"][:S]
 
-    def _capture(self, key, off, host):
-        """Record the decode step for one (batch, table width) shape. The first call runs the
-        kernels once outside capture so that every scratch buffer exists, then records them."""
-        Sb, Pb = key
+    def _capture(self, key, off, host, n, S, n_want, Pb, max_rows, decode_only):
+        """Record the kernels of one step shape into a CUDA graph with a metadata block, logits and
+        scratch of its own. The kernels run once outside capture first, on the metadata given (for a
+        decode shape an all-padding batch; otherwise the real step, which is thereby computed), so
+        that every scratch buffer exists; then they are recorded."""
         meta = torch.empty(off["_size"], dtype=torch.int32, device=self.device)
         ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype,
                           grow_scratch=Scratch(self.max_batch_tokens, self.dtype, self.device))
-        self._bind(ctx, meta, off, Sb, Sb, Sb, Pb)
-        ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(Sb)]
-        ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, 1, True
-        pad = self._layout(Sb, Sb, Sb, Pb)
-        blank = np.zeros(pad["_size"], dtype=np.int32)      # an all-padding batch: every row skipped
-        blank[pad["positions"]:pad["positions"] + Sb] = -1
-        for gi in range(len(self.cache.groups)):
-            blank[pad[f"slots{gi}"]:pad[f"slots{gi}"] + Sb] = -1
-            blank[pad[f"tables{gi}"]:pad[f"tables{gi}"] + Sb * Pb] = -1
-        blank[pad["row_seq"]:pad["row_seq"] + Sb] = np.arange(Sb)
-        blank[pad["want"]:pad["want"] + Sb] = np.arange(Sb)
-        meta.copy_(torch.from_numpy(blank))
-        sampled = torch.zeros(Sb, dtype=torch.int32, device=self.device)
+        self._bind(ctx, meta, off, n, S, n_want, Pb)
+        ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(S)]
+        ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, max_rows, decode_only
+        meta.copy_(torch.from_numpy(host))
+        sampled = torch.zeros(max(n_want, 1), dtype=torch.int32, device=self.device)
 
         def run():
             logits = self.model.forward(ctx)
-            kernels.sample(logits, sampled, ctx.temperature, ctx.uniform)
+            kernels.sample(logits, sampled[:n_want], ctx.temperature, ctx.uniform)
             return logits
 
         side = torch.cuda.Stream()
