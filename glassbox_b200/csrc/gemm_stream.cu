@@ -56,6 +56,9 @@ struct StreamArgs {
     int nh, nkv, hd, page_size, max_pos, write_kv;
     long long num_slots;
     int* status;
+    // a region to pull into L2 for a later kernel (its weights), or nullptr
+    const unsigned char* prefetch;
+    long long prefetch_bytes;
 };
 
 __device__ __forceinline__ void ws_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -137,6 +140,13 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
     };
 
     fetch(0);   // weights do not depend on the previous kernel
+    if (a.prefetch != nullptr) {
+        // While this kernel waits for its predecessor and works, the weights of a kernel further down
+        // the stream travel from HBM to L2: each block asks for its share, one 128-byte line per thread.
+        const long long lines = (a.prefetch_bytes + 127) / 128;
+        for (long long i = (long long)blockIdx.x * 128 + tid; i < lines; i += (long long)gridDim.x * 128)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a.prefetch + i * 128));
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");   // everything below reads what it wrote
 
     const bool normalise = a.X == nullptr;
@@ -315,11 +325,12 @@ static int check_common(const char* who, const void* x, const float* xres, const
 
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated (W = [gate rows; up rows],
 // N = number of gate rows, c = bfloat16 [M, N]). With x == nullptr the float32 rows `xres` are
-// RMS-normalised with `gain` and `eps` on the way in. pdl != 0 launches with programmatic stream
+// RMS-normalised with `gain` and `eps` on the way in. `prefetch` (optional) names a region that the
+// kernel asks the memory system to bring into L2 for a later kernel. pdl != 0 launches with programmatic stream
 // serialisation (the kernel waits for its predecessor itself, after prefetching weights).
 GB_EXPORT int gb_gemm_stream(const void* x, long long ldx, const float* xres, long long ldr, const float* gain, float eps,
                              const void* w, long long ldw, void* c, long long ldc, int mode, int M, int N, int K,
-                             int pdl, cudaStream_t stream) {
+                             const void* prefetch, long long prefetch_bytes, int pdl, cudaStream_t stream) {
     if (check_common("gb_gemm_stream", x, xres, w, M, N, K, ldx, ldr, ldw)) return 1;
     GB_REQUIRE(mode >= 0 && mode <= 3, "gb_gemm_stream: unknown mode %d", mode);
     GB_REQUIRE(mode != WS_GLU_BF16 || N % 16 == 0, "gb_gemm_stream: the gated mode needs N to be a multiple of 16");
@@ -329,6 +340,7 @@ GB_EXPORT int gb_gemm_stream(const void* x, long long ldx, const float* xres, lo
     a.X = (const __nv_bfloat16*)x; a.ldx = ldx; a.xres = xres; a.ldr = ldr; a.gain = gain; a.eps = eps;
     a.W = (const __nv_bfloat16*)w; a.ldw = ldw; a.C = c; a.ldc = ldc; a.mode = mode; a.M = M; a.N = N; a.K = K;
     a.pair_offset = mode == WS_GLU_BF16 ? N : 0;
+    a.prefetch = (const unsigned char*)prefetch; a.prefetch_bytes = prefetch ? prefetch_bytes : 0;
     return dispatch_stream(a, (N + 15) / 16, mode == WS_GLU_BF16, pdl, stream);
 }
 
@@ -340,7 +352,8 @@ GB_EXPORT int gb_gemm_stream_qkv(const void* x, long long ldx, const float* xres
                                  float eps, const void* w, long long ldw, void* q_out, long long ldq, int M, int K,
                                  const float* rope, int max_pos, const int* positions, const int* slots, void* kcache,
                                  void* vcache, int nh, int nkv, int hd, int page_size, long long num_pages, int write_kv,
-                                 int* status, int pdl, cudaStream_t stream) {
+                                 int* status, const void* prefetch, long long prefetch_bytes, int pdl,
+                                 cudaStream_t stream) {
     const int N = (nh + 2 * nkv) * hd;
     if (check_common("gb_gemm_stream_qkv", x, xres, w, M, N, K, ldx, ldr, ldw)) return 1;
     GB_REQUIRE(hd > 0 && hd % 32 == 0 && nh > 0 && nkv > 0, "gb_gemm_stream_qkv: head size %d must be a multiple of 32", hd);
@@ -355,5 +368,6 @@ GB_EXPORT int gb_gemm_stream_qkv(const void* x, long long ldx, const float* xres
     a.kcache = (__nv_bfloat16*)kcache; a.vcache = (__nv_bfloat16*)vcache;
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.page_size = page_size; a.max_pos = max_pos; a.write_kv = write_kv;
     a.num_slots = num_pages * page_size; a.status = status;
+    a.prefetch = (const unsigned char*)prefetch; a.prefetch_bytes = prefetch ? prefetch_bytes : 0;
     return dispatch_stream(a, (nh + 2 * nkv) * (hd / 32), true, pdl, stream);
 }

@@ -65,6 +65,32 @@ class Scratch:
         return buf
 
 
+class WeightOrder:
+    """Learns the order in which weight matrices are used in a step (it is the same in every step of
+    one model) from the calls themselves, so that a product can ask the memory system for the weights
+    of the product two calls further on while it works: parts do not know their neighbours, the
+    sequence of calls does."""
+
+    def __init__(self):
+        self.following = {}     # data_ptr -> the weight used next
+        self._prev = None
+
+    def start_step(self) -> None:
+        self._prev = None
+
+    def ahead(self, w: torch.Tensor, distance: int = 2) -> Optional[torch.Tensor]:
+        """Record that ``w`` is used now; return the weight expected ``distance`` uses later."""
+        if self._prev is not None:
+            self.following[self._prev.data_ptr()] = w
+        self._prev = w
+        t = w
+        for _ in range(distance):
+            t = self.following.get(t.data_ptr())
+            if t is None:
+                return None
+        return t
+
+
 class StepContext:
     def __init__(self, *, scratch: Scratch, cache: DeviceCache, status: torch.Tensor, dtype: torch.dtype,
                  grow_scratch: Optional[Scratch] = None):
@@ -89,6 +115,7 @@ class StepContext:
         self.num_seqs = 0
         self.decode_only = False          # every sequence of the step brings exactly one row
         self.temperature = self.uniform = None
+        self.weight_order: Optional[WeightOrder] = None
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)

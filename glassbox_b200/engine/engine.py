@@ -21,7 +21,7 @@ from ..cache.manager import CacheManager, GroupSpec, OutOfPages
 from ..config.registry import get_architecture, load_config
 from ..config.specs import ModelConfig
 from ..weights.loader import load_parameters, open_model_weights
-from .context import Scratch, SeqInfo, StepContext
+from .context import Scratch, SeqInfo, StepContext, WeightOrder
 from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -82,6 +82,8 @@ class Engine:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.scratch = Scratch(self.max_batch_tokens, self.dtype, self.device)
         self.ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype)
+        self.weight_order = WeightOrder()
+        self.ctx.weight_order = self.weight_order
         self._meta_dev = torch.empty(1 << 16, dtype=torch.int32, device=self.device)
         self._stage = [torch.empty(1 << 16, dtype=torch.int32).pin_memory() for _ in range(4)]
         self._stage_events = [None] * len(self._stage)
@@ -94,6 +96,7 @@ class Engine:
         self.max_graphs = 48
         self.graph_replays = 0
         self.sampled: Optional[torch.Tensor] = None
+        self._sampled_host: Optional[torch.Tensor] = None
         self.h2d_bytes_last = 0
 
     # ---------------------------------------------------------------------------- requests
@@ -208,6 +211,45 @@ class Engine:
             host[off["temperature"]:off["temperature"] + k] = np.asarray(temps, dtype=np.float32).view(np.int32)
             host[off["uniform"]:off["uniform"] + k] = np.asarray(unif, dtype=np.float32).view(np.int32)
         self._seqs, self._max_ctx = seqs, max_ctx
+        return host
+
+    def _fill_decode(self, entries, off, Sb: int, Pb: int, sampling) -> np.ndarray:
+        """``_fill`` for a step of single decoded tokens padded to ``Sb`` rows: the same block, built
+        with whole-array operations (this runs once per generated token of every request)."""
+        ps = self.page_size
+        cache = self.cache
+        S = len(entries)
+        host = np.zeros(off["_size"], dtype=np.int32)
+        lengths = np.fromiter((cache.requests[e.request].length for e in entries), dtype=np.int32, count=S)
+        host[off["tokens"]:off["tokens"] + S] = [e.tokens[0] for e in entries]
+        pos = host[off["positions"]:off["positions"] + Sb]
+        pos[:] = -1
+        pos[:S] = lengths
+        ar = np.arange(Sb + 1, dtype=np.int32)
+        host[off["row_seq"]:off["row_seq"] + Sb] = ar[:Sb]
+        host[off["want"]:off["want"] + Sb] = ar[:Sb]
+        host[off["seq_first_row"]:off["seq_first_row"] + Sb + 1] = ar
+        host[off["seq_start_pos"]:off["seq_start_pos"] + S] = lengths
+        host[off["seq_slots"]:off["seq_slots"] + S] = [cache.requests[e.request].slot for e in entries]
+        page_index = lengths // ps
+        in_page = lengths % ps
+        for g, group in enumerate(cache.groups):
+            tables = host[off[f"tables{g}"]:off[f"tables{g}"] + Sb * Pb].reshape(Sb, Pb)
+            tables[:] = -1
+            slots = host[off[f"slots{g}"]:off[f"slots{g}"] + Sb]
+            slots[:] = -1
+            for i, e in enumerate(entries):
+                t = group.tables[e.request]
+                tables[i, :len(t)] = t
+            slots[:S] = tables[ar[:S], page_index] * ps + in_page
+        if sampling is not None:
+            temps, unif = sampling
+            k = len(temps)
+            host[off["temperature"]:off["temperature"] + k] = np.asarray(temps, dtype=np.float32).view(np.int32)
+            host[off["uniform"]:off["uniform"] + k] = np.asarray(unif, dtype=np.float32).view(np.int32)
+        self._seqs = [SeqInfo(request=e.request, slot=int(host[off["seq_slots"] + i]), start_pos=int(lengths[i]),
+                              n_rows=1, first_row=i) for i, e in enumerate(entries)]
+        self._max_ctx = int(lengths.max()) + 1 if S else 0
         return host
 
     def _bind(self, ctx: StepContext, dev: torch.Tensor, off, n, S, n_want, max_pages) -> None:
@@ -336,7 +378,7 @@ class Engine:
         off = self._layout(Sb, Sb, Sb, Pb)
         if sampling is None:
             sampling = ([0.0] * S, [0.0] * S)
-        host = self._fill(entries, off, Sb, Sb, Pb, sampling)
+        host = self._fill_decode(entries, off, Sb, Pb, sampling)
         g = self._graphs.get(key)
         if g is None:
             blank = np.zeros(off["_size"], dtype=np.int32)      # an all-padding batch: every row skipped
@@ -364,6 +406,7 @@ class Engine:
         ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype,
                           grow_scratch=Scratch(self.max_batch_tokens, self.dtype, self.device))
         self._bind(ctx, meta, off, n, S, n_want, Pb)
+        ctx.weight_order = self.weight_order
         ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(S)]
         ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, max_rows, decode_only
         meta.copy_(torch.from_numpy(host))
@@ -415,7 +458,11 @@ class Engine:
             params = torch.from_numpy(np.stack([temps, unif])).to(self.device, non_blocking=True)
             self.sampled = self.scratch.get("sampled", (w, 1), torch.int32, grow=True).view(-1)
             kernels.sample(logits, self.sampled, params[0], params[1])
-        picked = self.sampled.cpu().numpy()
+        if self._sampled_host is None or self._sampled_host.numel() < w:
+            self._sampled_host = torch.empty(max(w, 64), dtype=torch.int32).pin_memory()
+        self._sampled_host[:w].copy_(self.sampled, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        picked = self._sampled_host.numpy()
         self.sampled = None
         result = []
         for r, s, ctx_tokens in zip(rows, samplers, contexts):

@@ -81,6 +81,8 @@ class DecoderModel:
     def forward(self, ctx) -> torch.Tensor:
         """Run the rows of ``ctx`` through the model; returns float32 logits [wanted rows, vocab]."""
         n, d = ctx.n, self.config.hidden_size
+        if getattr(ctx, "weight_order", None) is not None:
+            ctx.weight_order.start_step()
         x = ctx.scratch("x", (n, d), torch.float32)
         self.embed.forward(ctx, ctx.tokens, x)
         for run in self.config.schedule:

@@ -43,9 +43,9 @@ _SIGNATURES = {
     "gb_attention_decode": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                             _P, _P, _P],
     "gb_attention_decode_counters": [_I, _I, _I],
-    "gb_gemm_stream": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _I, _I, _P],
+    "gb_gemm_stream": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _LL, _I, _P],
     "gb_gemm_stream_qkv": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                           _LL, _I, _P, _I, _P],
+                           _LL, _I, _P, _P, _LL, _I, _P],
     "gb_attention_decode_mma_pdl": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                                     _P, _P, _I, _P],
     "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
@@ -224,11 +224,16 @@ def _stream_input(a: torch.Tensor, norm):
     return 0, 0, _ptr(a), a.stride(0), _ptr(gain), float(eps)
 
 
+def _prefetch_args(t: Optional[torch.Tensor]):
+    return (0, 0) if t is None else (t.data_ptr(), t.numel() * t.element_size())
+
+
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, gated: bool = False,
-                norm=None) -> None:
+                norm=None, prefetch: Optional[torch.Tensor] = None) -> None:
     """c[M, N] (+)= a[M, K] @ w[N, K]^T for M <= 64 on the tensor cores, streaming w once. With
     ``gated``, w is [2I, K] (gate rows, then up rows) and c[M, I] = silu(a gate^T) * (a up^T). With
-    ``norm`` = (gain, eps), ``a`` is the float32 residual and is RMS-normalised on the way in."""
+    ``norm`` = (gain, eps), ``a`` is the float32 residual and is RMS-normalised on the way in.
+    ``prefetch`` names a tensor (a later kernel's weights) to pull into L2 meanwhile."""
     _cuda(a, w, c)
     M, K = a.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
@@ -244,7 +249,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
         assert c.dtype in (torch.bfloat16, torch.float32)
     x, ldx, xres, ldr, gain, eps = _stream_input(a, norm)
     _call("gb_gemm_stream", x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(c), c.stride(0), mode, M, N, K,
-          1 if USE_PDL else 0, _stream())
+          *_prefetch_args(prefetch), 1 if USE_PDL else 0, _stream())
 
 
 def gemm_stream_qkv_supported(a, w: torch.Tensor, hd: int, q_out: torch.Tensor) -> bool:
@@ -254,7 +259,8 @@ def gemm_stream_qkv_supported(a, w: torch.Tensor, hd: int, q_out: torch.Tensor) 
 
 def gemm_stream_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[torch.Tensor],
                     positions: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nh: int,
-                    nkv: int, hd: int, page_size: int, write_kv: bool, status: torch.Tensor, norm=None) -> None:
+                    nkv: int, hd: int, page_size: int, write_kv: bool, status: torch.Tensor, norm=None,
+                    prefetch: Optional[torch.Tensor] = None) -> None:
     """Stacked QKV projection for M <= 64 with rotary encoding and the cache write in its epilogue:
     q_out[:, :nh*hd] receives the rotated queries, rotated keys and values go to each row's cache slot.
     Full rotary (table [max_pos, hd/2, 2]) or none (cos_sin None)."""
@@ -268,7 +274,7 @@ def gemm_stream_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_s
     _call("gb_gemm_stream_qkv", x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(q_out), q_out.stride(0), M, K,
           _ptr(cos_sin), cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slots), _ptr(kcache),
           _ptr(vcache), nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status),
-          1 if USE_PDL else 0, _stream())
+          *_prefetch_args(prefetch), 1 if USE_PDL else 0, _stream())
 
 
 def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:

@@ -14,7 +14,7 @@ import torch
 from .. import kernels
 from ..weights.binding import ParamSpec
 from .base import Mixer, PagedKvSpec, Position, build_part, register_part
-from .linear import _resolve, linear
+from .linear import _resolve, linear, weights_ahead
 
 
 class GqaAttention(Mixer):
@@ -56,7 +56,8 @@ class GqaAttention(Mixer):
                 and kernels.gemm_stream_qkv_supported(x, self.params["wqkv"], self.hd, qkv)):
             # few rows: one kernel normalises, projects, rotates and writes the cache
             kernels.gemm_stream_qkv(x, self.params["wqkv"], qkv, table, ctx.positions, cache.slots, cache.k, cache.v,
-                                    self.nh, self.nkv, self.hd, cache.page_size, writes_cache, ctx.status, norm=norm)
+                                    self.nh, self.nkv, self.hd, cache.page_size, writes_cache, ctx.status, norm=norm,
+                                    prefetch=weights_ahead(ctx, self.params["wqkv"]))
         else:
             linear(ctx, h, self.params["wqkv"], qkv)
             if table is None:

@@ -14,6 +14,12 @@ from .. import kernels
 from .base import DeferredNorm
 
 
+def weights_ahead(ctx, w: torch.Tensor):
+    """The weight matrix that the step will use two products from now (or None while unknown)."""
+    order = getattr(ctx, "weight_order", None)
+    return order.ahead(w) if order is not None else None
+
+
 def _resolve(a):
     """(tensor the stream kernel can take, norm or None, deferred or None) for an input that may be a
     ``DeferredNorm``."""
@@ -30,7 +36,7 @@ def linear(ctx, a, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False)
     when that kernel runs, and computed first otherwise."""
     x, norm, deferred = _resolve(a)
     if kernels.gemm_stream_supported(x, w) and (norm is not None or x.dtype == torch.bfloat16):
-        kernels.gemm_stream(x, w, out, accumulate, norm=norm)
+        kernels.gemm_stream(x, w, out, accumulate, norm=norm, prefetch=weights_ahead(ctx, w))
         return
     if deferred is not None:
         x = deferred.tensor()
@@ -47,6 +53,6 @@ def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
     x, norm, _ = _resolve(a)
     if (kernels.gemm_stream_supported(x, w_gate_up) and (norm is not None or x.dtype == torch.bfloat16)
             and inter % 16 == 0 and act.dtype == torch.bfloat16):
-        kernels.gemm_stream(x, w_gate_up, act, gated=True, norm=norm)
+        kernels.gemm_stream(x, w_gate_up, act, gated=True, norm=norm, prefetch=weights_ahead(ctx, w_gate_up))
         return True
     return False
