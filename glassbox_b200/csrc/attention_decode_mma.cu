@@ -370,13 +370,15 @@ GB_EXPORT int gb_attention_decode_mma_supported(int nh, int nkv, int hd) {
 
 // As gb_attention_decode_mma, with the choice of launching under programmatic stream serialisation
 // (pdl != 0): the kernel then starts while its predecessor in the stream still runs, reads only step
-// metadata until the predecessor has finished, and releases its own successor at once.
+// metadata until the predecessor has finished, and releases its own successor at once. block_keys
+// (0 = default) picks the variant that takes 16 keys per warp iteration where one is built (head
+// size 64): fewer registers, more blocks per SM, which pays when the batch alone fills the GPU.
 GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, void* out, long long out_stride,
                                           const void* kcache, const void* vcache, const int* block_tables,
                                           int max_pages, const int* row_seq, const int* positions, int n, int nh,
                                           int nkv, int hd, int page_size, long long num_pages, float scale, int window,
                                           int splits, float* part_acc, float* part_ml, int* counters, int* status,
-                                          int pdl, cudaStream_t stream) {
+                                          int pdl, int block_keys, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_decode_mma_supported(nh, nkv, hd),
                "gb_attention_decode_mma: head size %d with %d heads per kv head is not built (16/32/64/128, <= 16)", hd,
                nkv > 0 ? nh / nkv : 0);
@@ -394,7 +396,10 @@ GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, voi
                               status, pdl, stream);
     if (hd == 16) { GB_MMA(16, 32) }
     if (hd == 32) { GB_MMA(32, 32) }
-    if (hd == 64) { GB_MMA(64, 32) }
+    if (hd == 64) {
+        if (block_keys == 16) { GB_MMA(64, 16) }   // fewer registers, three blocks per SM: better for large batches
+        GB_MMA(64, 32)
+    }
     GB_MMA(128, 16)
 #undef GB_MMA
 }
@@ -407,5 +412,5 @@ GB_EXPORT int gb_attention_decode_mma(const void* q, long long q_stride, void* o
                                       cudaStream_t stream) {
     return gb_attention_decode_mma_pdl(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, row_seq,
                                        positions, n, nh, nkv, hd, page_size, num_pages, scale, window, splits, part_acc,
-                                       part_ml, counters, status, 0, stream);
+                                       part_ml, counters, status, 0, 0, stream);
 }

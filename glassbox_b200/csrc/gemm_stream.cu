@@ -165,17 +165,31 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
         }
     }
 
+    // bfloat16 activations are fetched one chunk ahead into registers, so that their latency hides
+    // behind the arithmetic of the chunk before (with 64 rows a chunk is 32 KB per block)
+    constexpr int XPT = ROWS * (WS_KC / 8) / 128;   // 16-byte pieces per thread per chunk
+    uint4 xr[XPT];
+    auto xload = [&](int chunk) {
+#pragma unroll
+        for (int i = 0; i < XPT; ++i) {
+            const int c = tid + i * 128;
+            const int row = c / (WS_KC / 8), k = chunk * WS_KC + (c % (WS_KC / 8)) * 8;
+            xr[i] = (row < M && k < K) ? *reinterpret_cast<const uint4*>(a.X + (size_t)row * a.ldx + k) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    if (!normalise) xload(0);
+
     for (int chunk = 0; chunk < nchunks; ++chunk) {
-        // stage the activations of this chunk: ROWS x 256, 8 values per thread and copy
+        // stage the activations of this chunk: ROWS x 256
         __syncthreads();
-        for (int c = tid; c < ROWS * (WS_KC / 8); c += 128) {
-            const int row = c / (WS_KC / 8), col = (c % (WS_KC / 8)) * 8;
-            const int k = chunk * WS_KC + col;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row < M && k < K) {
-                if (normalise) {
-                    const float* xr = a.xres + (size_t)row * a.ldr + k;
-                    const float4 x0 = *reinterpret_cast<const float4*>(xr), x1 = *reinterpret_cast<const float4*>(xr + 4);
+        if (normalise) {
+            for (int c = tid; c < ROWS * (WS_KC / 8); c += 128) {
+                const int row = c / (WS_KC / 8), col = (c % (WS_KC / 8)) * 8;
+                const int k = chunk * WS_KC + col;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (row < M && k < K) {
+                    const float* xrow = a.xres + (size_t)row * a.ldr + k;
+                    const float4 x0 = *reinterpret_cast<const float4*>(xrow), x1 = *reinterpret_cast<const float4*>(xrow + 4);
                     const float4 g0 = *reinterpret_cast<const float4*>(a.gain + k);
                     const float4 g1 = *reinterpret_cast<const float4*>(a.gain + k + 4);
                     const float s = srow[row];
@@ -183,13 +197,18 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
                     v.y = ws_pack(g0.z * (x0.z * s), g0.w * (x0.w * s));
                     v.z = ws_pack(g1.x * (x1.x * s), g1.y * (x1.y * s));
                     v.w = ws_pack(g1.z * (x1.z * s), g1.w * (x1.w * s));
-                } else {
-                    v = *reinterpret_cast<const uint4*>(a.X + (size_t)row * a.ldx + k);
                 }
+                *reinterpret_cast<uint4*>(&xs[row][col]) = v;
             }
-            *reinterpret_cast<uint4*>(&xs[row][col]) = v;
+        } else {
+#pragma unroll
+            for (int i = 0; i < XPT; ++i) {
+                const int c = tid + i * 128;
+                *reinterpret_cast<uint4*>(&xs[c / (WS_KC / 8)][(c % (WS_KC / 8)) * 8]) = xr[i];
+            }
         }
         __syncthreads();
+        if (!normalise && chunk + 1 < nchunks) xload(chunk + 1);
         uint4 ca[SETS][WS_BPW], cb[SETS][WS_BPW];
 #pragma unroll
         for (int s = 0; s < SETS; ++s)

@@ -116,6 +116,7 @@ class StepContext:
         self.decode_only = False          # every sequence of the step brings exactly one row
         self.temperature = self.uniform = None
         self.weight_order: Optional[WeightOrder] = None
+        self.side_stream = None           # a second CUDA stream for work beside the main chain (prefetch)
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)

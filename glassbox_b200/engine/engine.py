@@ -84,6 +84,8 @@ class Engine:
         self.ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype)
         self.weight_order = WeightOrder()
         self.ctx.weight_order = self.weight_order
+        self.side_stream = torch.cuda.Stream(device=self.device)
+        self.ctx.side_stream = self.side_stream
         self._meta_dev = torch.empty(1 << 16, dtype=torch.int32, device=self.device)
         self._stage = [torch.empty(1 << 16, dtype=torch.int32).pin_memory() for _ in range(4)]
         self._stage_events = [None] * len(self._stage)
@@ -407,6 +409,7 @@ class Engine:
                           grow_scratch=Scratch(self.max_batch_tokens, self.dtype, self.device))
         self._bind(ctx, meta, off, n, S, n_want, Pb)
         ctx.weight_order = self.weight_order
+        ctx.side_stream = self.side_stream
         ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(S)]
         ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, max_rows, decode_only
         meta.copy_(torch.from_numpy(host))

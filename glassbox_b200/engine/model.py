@@ -12,7 +12,7 @@ import torch
 
 from ..config.specs import ModelConfig
 from ..parts import Embedding, LmHead, build_block, build_part
-from ..parts.base import Part
+from ..parts.base import Mixer, Part
 from ..weights.binding import ParamSpec
 
 
@@ -85,8 +85,29 @@ class DecoderModel:
             ctx.weight_order.start_step()
         x = ctx.scratch("x", (n, d), torch.float32)
         self.embed.forward(ctx, ctx.tokens, x)
-        for run in self.config.schedule:
-            self.layers[run.layer].forward(ctx, x, ctx.cache_view(run.cache), run.writes_cache)
+        schedule = self.config.schedule
+        side = ctx.side_stream if ctx.decode_only else None
+        pending = False
+        for i, run in enumerate(schedule):
+            hook = None
+            if side is not None and i + 1 < len(schedule):
+                nxt = schedule[i + 1]
+                mixer = getattr(self.layers[nxt.layer], "mixer", None)
+                if mixer is not None and type(mixer).prefetch is not Mixer.prefetch:
+                    def hook(mixer=mixer, cache_layer=nxt.cache):
+                        # beside this layer's feed-forward, on a second stream: the next mixer's prefetch
+                        main = torch.cuda.current_stream()
+                        side.wait_stream(main)
+                        with torch.cuda.stream(side):
+                            mixer.prefetch(ctx, ctx.cache_view(cache_layer))
+            if pending:
+                torch.cuda.current_stream().wait_stream(side)   # the prefetch kernel must not outlive the step
+                pending = False
+            self.layers[run.layer].forward(ctx, x, ctx.cache_view(run.cache), run.writes_cache, after_mixer=hook) \
+                if hook is not None else self.layers[run.layer].forward(ctx, x, ctx.cache_view(run.cache), run.writes_cache)
+            pending = hook is not None
+        if pending:
+            torch.cuda.current_stream().wait_stream(side)
         w = ctx.num_wanted
         logits = ctx.scratch("logits", (w, self.config.vocab_size), torch.float32, grow=True)
         if w:

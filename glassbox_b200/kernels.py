@@ -47,10 +47,11 @@ _SIGNATURES = {
     "gb_gemm_stream_qkv": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                            _LL, _I, _P, _P, _LL, _I, _P],
     "gb_attention_decode_mma_pdl": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
-                                    _P, _P, _I, _P],
+                                    _P, _P, _I, _I, _P],
     "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
                                 _P, _P],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
+    "gb_kv_prefetch": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _LL, _LL, _I, _I, _P],
     "gb_attention_prefill": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_attention_prefill_supported": [_I, _I, _I, _I],
     "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P],
@@ -359,20 +360,29 @@ def attention_decode_mma_supported(dtype: torch.dtype, nh: int, nkv: int, hd: in
             and bool(lib().gb_attention_decode_mma_supported(nh, nkv, hd)))
 
 
-def decode_mma_splits(n: int, nkv: int, hd: int, max_context: int) -> int:
-    """Blocks per (row, kv head) for the tensor-core decode kernel: enough to give every SM a block,
-    but each block keeps at least 512 keys (128 per warp), below which the fixed cost of a block
-    and of the merge outweighs the extra parallelism. Depends on the batch shape and the longest
-    context the step allows, never on the data, so a captured graph can fix it."""
+def decode_mma_plan(n: int, nkv: int, hd: int, max_context: int):
+    """(splits, keys per warp iteration) for the tensor-core decode kernel. A small batch needs many
+    blocks per (row, kv head) to fill the GPU, but each block keeps at least 512 keys, below which the
+    fixed cost of a block and of the merge outweighs the parallelism; a batch that fills the GPU by
+    itself takes the 16-key variant (three blocks per SM instead of two) and few splits. Depends on
+    the batch shape and the longest context the step allows, never on the data, so a captured graph
+    can fix it."""
+    pairs = max(n * nkv, 1)
     most = max(1, -(-max_context // 512))
-    return max(1, min(-(-148 // max(n * nkv, 1)), most))
+    if hd == 64 and pairs >= 96:
+        return max(1, min(-(-296 // pairs), most)), 16
+    return max(1, min(-(-148 // pairs), most)), 0
+
+
+def decode_mma_splits(n: int, nkv: int, hd: int, max_context: int) -> int:
+    return decode_mma_plan(n, nkv, hd, max_context)[0]
 
 
 def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                          block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int,
                          hd: int, page_size: int, scale: float, window: Optional[int], splits: int,
                          part_acc: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
-                         status: torch.Tensor) -> None:
+                         status: torch.Tensor, block_keys: int = 0) -> None:
     """bfloat16 split-key decode attention on the tensor cores. Scratch: part_acc float32
     [n, nh, 4*splits, hd], part_ml float32 [n, nh, 4*splits, 2], counters int32 [n*nkv], zero on entry
     and left zero."""
@@ -385,7 +395,7 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     _call("gb_attention_decode_mma_pdl", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
           _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
           kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml), _ptr(counters),
-          _ptr(status), 1 if USE_PDL else 0, _stream())
+          _ptr(status), 1 if USE_PDL else 0, int(block_keys), _stream())
 
 
 def attention_prefill_supported(dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:
@@ -406,6 +416,19 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
     _call("gb_attention_prefill", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
           _ptr(block_tables), block_tables.shape[1], _ptr(seq_first_row), _ptr(seq_start_pos), S, int(max_rows_per_seq),
           nh, nkv, hd, page_size, kcache.shape[0], float(scale), int(window or 0), _ptr(status), _stream())
+
+
+def kv_prefetch(kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor, row_seq: torch.Tensor,
+                positions: torch.Tensor, nkv: int, hd: int, page_size: int, window: Optional[int],
+                blocks_per_row: int) -> None:
+    """Ask the memory system to bring the pages that each row's attention will read into L2."""
+    _cuda(kcache, vcache, block_tables, row_seq, positions)
+    tile_bytes = page_size * hd * kcache.element_size()
+    if tile_bytes % 128:
+        return
+    _call("gb_kv_prefetch", _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1], _ptr(row_seq),
+          _ptr(positions), positions.shape[0], nkv, page_size, kcache.shape[0], tile_bytes, int(window or 0),
+          int(blocks_per_row), _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

@@ -69,6 +69,19 @@ class GqaAttention(Mixer):
         linear(ctx, att, self.params["wo"], residual, accumulate=True)
 
 
+    #: prefetch the cache into L2 only when a step's share of it fits there comfortably
+    PREFETCH_MAX_BYTES = 48 << 20
+
+    def prefetch(self, ctx, cache) -> None:
+        if not ctx.decode_only or cache is None:
+            return
+        n = ctx.n
+        step_bytes = 2 * n * min(ctx.max_context, self.spec.window or ctx.max_context) * self.kvd * cache.k.element_size()
+        if step_bytes > self.PREFETCH_MAX_BYTES:
+            return
+        kernels.kv_prefetch(cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.nkv, self.hd,
+                            cache.page_size, self.spec.window, blocks_per_row=max(1, 148 // max(n, 1)))
+
     def attend(self, ctx, q, att, cache) -> None:
         """att[row, head, :] = softmax over the row's visible keys; the kernel is picked by the shape
         of the batch: rows that are single decoded tokens share the keys of a request between
@@ -77,13 +90,13 @@ class GqaAttention(Mixer):
         is built for; anything else takes the one-warp-per-(row, head) kernel."""
         n = q.shape[0]
         if ctx.decode_only and kernels.attention_decode_mma_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size):
-            splits = kernels.decode_mma_splits(n, self.nkv, self.hd, ctx.max_context)
+            splits, block_keys = kernels.decode_mma_plan(n, self.nkv, self.hd, ctx.max_context)
             part_acc = ctx.scratch("decode_part_acc", (n, self.nh * 4 * splits * self.hd), torch.float32, grow=True)
             part_ml = ctx.scratch("decode_part_ml", (n, self.nh * 4 * splits * 2), torch.float32, grow=True)
             counters = ctx.zeros_once("decode_counters", ctx.max_rows * self.nh, torch.int32)
             kernels.attention_decode_mma(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
                                          self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale,
-                                         self.spec.window, splits, part_acc, part_ml, counters, ctx.status)
+                                         self.spec.window, splits, part_acc, part_ml, counters, ctx.status, block_keys)
             return
         if ctx.decode_only and self.hd % 16 == 0 and self.hd >= 16:
             splits = kernels.decode_splits(n, self.nh, self.nkv, ctx.max_context)

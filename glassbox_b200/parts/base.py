@@ -114,6 +114,11 @@ class Mixer(Part):
     def forward(self, ctx, h, residual, cache, writes_cache: bool) -> None:
         raise NotImplementedError
 
+    def prefetch(self, ctx, cache) -> None:
+        """A hint, given while an earlier layer still runs (on another stream): this mixer will soon
+        read ``cache``. It may start moving data towards the chip; it must not write anything."""
+        return None
+
 
 class FeedForward(Part):
     accepts_deferred_input = False

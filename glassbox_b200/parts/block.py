@@ -21,9 +21,13 @@ class PreNormBlock(Part):
     def sub_parts(self):
         return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn}
 
-    def forward(self, ctx, x, cache, writes_cache: bool) -> None:
+    def forward(self, ctx, x, cache, writes_cache: bool, after_mixer=None) -> None:
+        """``after_mixer`` (optional) is called once the mixer's kernels are launched: the model uses it
+        to let the next layer's mixer start its prefetch beside this layer's feed-forward."""
         h = DeferredNorm(ctx, self.mixer_norm, x)
         self.mixer.forward(ctx, h if self.mixer.accepts_deferred_input else h.tensor(), x, cache, writes_cache)
+        if after_mixer is not None:
+            after_mixer()
         h = DeferredNorm(ctx, self.ffn_norm, x)
         self.ffn.forward(ctx, h if self.ffn.accepts_deferred_input else h.tensor(), x)
 

@@ -35,7 +35,11 @@ def linear(ctx, a, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False)
     """``a`` is a tensor or a ``DeferredNorm``; the latter is folded into the weight-streaming kernel
     when that kernel runs, and computed first otherwise."""
     x, norm, deferred = _resolve(a)
-    if kernels.gemm_stream_supported(x, w) and (norm is not None or x.dtype == torch.bfloat16):
+    # Few rows: the weight-streaming kernel. Except for a very wide matrix (the head) with more than
+    # 16 rows, where one strip of 16 outputs per block makes thousands of blocks that each repeat the
+    # staging of all rows: there the tile kernel is faster (measured: 28 us against 80 us at 64 rows).
+    wide = x.shape[0] > 16 and w.shape[0] >= 16384 and norm is None and kernels.gemm_tc_supported(x, w, out)
+    if not wide and kernels.gemm_stream_supported(x, w) and (norm is not None or x.dtype == torch.bfloat16):
         kernels.gemm_stream(x, w, out, accumulate, norm=norm, prefetch=weights_ahead(ctx, w))
         return
     if deferred is not None:
