@@ -2,7 +2,7 @@
 // operands staged in shared memory by TMA, tcgen05.mma issued by one thread, the float32
 // accumulator in tensor memory (TMEM), read back with tcgen05.ld for the epilogue.
 //
-// One block computes one 128 x BN tile of C (BN = 64 or 128).
+// A persistent block (one per SM) computes 128 x BN tiles of C one after another (BN = 64, 128 or 256).
 //   warp 0, one lane: producer. For each 64-wide k-block it waits until the stage is free, arms the
 //       stage's "full" mbarrier with the bytes to come and issues two TMA loads (A box 128 x 64,
 //       W box BN x 64, 128-byte swizzle; rows or columns outside the matrices are zero-filled by
@@ -10,8 +10,10 @@
 //   warp 1, one lane: issues 4 tcgen05.mma (M 128, N BN, K 16) per k-block from shared-memory matrix
 //       descriptors, then tcgen05.commit to the stage's "empty" mbarrier (the stage is free once the
 //       tensor core has read it) and, after the last k-block, to the "accumulator ready" mbarrier.
-//   warps 0-3: epilogue. Warp w reads TMEM lanes 32w..32w+31 (rows of the tile), 32 columns at a
-//       time, and stores bfloat16 / float32 or adds into float32 (the residual stream).
+//   warps 2-5: epilogue. Each reads its quarter of the TMEM lanes (rows of the tile), 32 columns at a
+//       time, and stores bfloat16 / float32, adds into float32 (the residual stream) or applies the
+//       gated activation. Two accumulators alternate, so the epilogue of a tile overlaps the main loop
+//       of the next.
 // Both operands are K-major ([rows, K] with K contiguous), exactly as activations and [out, in]
 // weights are stored (crates/glassbox-core/src/kernels.rs:381), so nothing is transposed.
 //
@@ -24,7 +26,6 @@
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;        // 64 bfloat16 = 128 bytes = one swizzle row
-constexpr int TC_STAGES = 4;
 constexpr long long TC_WAIT_CYCLES = 400ll * 1000 * 1000;   // about 0.2 s: far beyond any real wait
 
 enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2 };
@@ -107,36 +108,68 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+constexpr int TC_MAX_STAGES = 8;
+
 struct __align__(8) TcShared {
-    uint64_t full[TC_STAGES];
-    uint64_t empty[TC_STAGES];
-    uint64_t accum;
+    uint64_t full[TC_MAX_STAGES];    // TMA -> MMA: a stage's operands have landed
+    uint64_t empty[TC_MAX_STAGES];   // MMA -> TMA: the tensor core has read the stage
+    uint64_t tfull[2];               // MMA -> epilogue: an accumulator is complete
+    uint64_t tempty[2];              // epilogue -> MMA: an accumulator has been read out
     uint32_t tmem_base;
     int abort_flag;
     int issued;      // k-blocks whose TMA loads were issued
     int consumed;    // k-blocks whose full barrier the MMA thread has passed
 };
 
-template <int BN>
-__global__ void __launch_bounds__(128) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, bool GATED> struct TcGeometry {
+    static constexpr int BNO = GATED ? BN / 2 : BN;                 // output columns per tile
+    static constexpr int A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    static constexpr int STAGES = (192 * 1024 / STAGE_BYTES) < TC_MAX_STAGES ? (192 * 1024 / STAGE_BYTES) : TC_MAX_STAGES;
+    static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;               // per-warp transposition tiles
+    static constexpr int SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024;
+};
+
+// A persistent block walks over output tiles (tile = blockIdx.x, + gridDim.x, ...). Six warps:
+//   warp 0 (one lane)  producer: TMA loads of A and W k-blocks into the stage ring, across tiles;
+//   warp 1 (one lane)  MMA issuer: per tile, tcgen05.mma over the k-blocks into one of two TMEM
+//                      accumulators, so that the next tile's main loop runs while the epilogue
+//                      warps read the previous accumulator out;
+//   warps 2-5          epilogue: warp w reads TMEM lanes 32*(w%4).. (rows of the tile), 32 columns at
+//                      a time, and stores bfloat16 / float32, adds into float32 (the residual
+//                      stream), or, GATED, stores silu(gate)*up: the tile's accumulator then holds the
+//                      gate columns in its first half and the matching up columns (weight rows
+//                      gate_rows further down, loaded by a second TMA box) in its second half
+//                      (crates/glassbox-core/src/model.rs:335-340).
+template <int BN, bool GATED>
+__global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_w, void* __restrict__ C,
-                                                           int mode, int M, int N, int K, long long ldc,
+                                                           int mode, int M, int N, int K, long long ldc, int gate_rows,
                                                            int* __restrict__ status) {
+    using G = TcGeometry<BN, GATED>;
+    constexpr int STAGES = G::STAGES, BNO = G::BNO;
     extern __shared__ unsigned char smem_dyn[];
     // 128-byte-swizzled tiles want 1024-byte alignment
     unsigned char* tiles = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-    constexpr int A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    float* epi = reinterpret_cast<float*>(tiles + STAGES * G::STAGE_BYTES);
     __shared__ TcShared sh;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
     const int kblocks = (K + TC_BK - 1) / TC_BK;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BNO - 1) / BNO;
+    const int ntiles = tiles_m * tiles_n;
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(&sh.full[s], 1);
             mbar_init(&sh.empty[s], 1);
         }
-        mbar_init(&sh.accum, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sh.tfull[b], 1);
+            mbar_init(&sh.tempty[b], 4);   // one arrival per epilogue warp
+        }
         sh.abort_flag = 0;
         sh.issued = 0;
         sh.consumed = 0;
@@ -144,8 +177,8 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(const __grid_constant
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     }
-    if (warp == 0) {   // one warp allocates BN columns of tensor memory for the accumulator
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(BN) : "memory");
+    if (warp == 0) {   // one warp allocates the two accumulators in tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -154,102 +187,141 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(const __grid_constant
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_flag = &sh.abort_flag;
 
-    if (warp == 0 && lane == 0) {
-        // ------------------------------------------------------------------------- producer
-        for (int kb = 0; kb < kblocks; ++kb) {
-            const int s = kb % TC_STAGES;
-            if (kb >= TC_STAGES && !mbar_wait(&sh.empty[s], ((kb / TC_STAGES) - 1) & 1, abort_flag, status)) break;
-            unsigned char* a_dst = tiles + s * STAGE_BYTES;
-            mbar_expect_tx(&sh.full[s], STAGE_BYTES);
-            tma_load_2d(a_dst, &map_a, &sh.full[s], kb * TC_BK, m0);
-            tma_load_2d(a_dst + A_BYTES, &map_w, &sh.full[s], kb * TC_BK, n0);
-            sh.issued = kb + 1;
-        }
-    } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------------------- MMA issuer
-        const uint32_t idesc = umma_idesc(TC_BM, BN);
-        bool ok = true;
-        for (int kb = 0; kb < kblocks; ++kb) {
-            const int s = kb % TC_STAGES;
-            if (!mbar_wait(&sh.full[s], (kb / TC_STAGES) & 1, abort_flag, status)) { ok = false; break; }
-            sh.consumed = kb + 1;
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
-            const uint32_t w_addr = a_addr + A_BYTES;
-#pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k) {
-                // 16 bfloat16 = 32 bytes further along K inside the swizzled row
-                umma_bf16(tmem, umma_desc(a_addr + k * 32), umma_desc(w_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
-            }
-            umma_commit(&sh.empty[s]);       // arrives when the MMAs above have read the stage
-        }
-        if (ok) umma_commit(&sh.accum);      // arrives when every MMA has finished
-    }
-    __syncwarp();
-
-    // ------------------------------------------------------------------------------- epilogue
-    bool ready = true;
-    if (kblocks > 0) ready = mbar_wait(&sh.accum, 0, abort_flag, status);
-    tc_fence_after();
-    if (ready) {
-        // Each thread holds one row of 32 columns after tcgen05.ld. Writing rows per thread would touch
-        // 32 rows with 16 bytes each per instruction, so the chunk goes through shared memory (the
-        // pipeline stages are free by now) and comes back transposed: one row per instruction, lanes
-        // across 32 consecutive columns, 128 contiguous bytes.
-        float* stage = reinterpret_cast<float*>(tiles) + warp * (32 * 33);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t r[32];
-            if (kblocks > 0) {
-                tmem_load32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0u;
-            }
-            if (mode == TC_STORE_BF16) {
-                // a thread's 32 columns are 64 contiguous bytes: store them directly, 16 bytes at a time
-                const int row = m0 + warp * 32 + lane;
-                const int col0 = n0 + c0;
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + col0;
-                if (row < M) {
-                    if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 v;
-                            v.x = pack2(r[j], r[j + 1]); v.y = pack2(r[j + 2], r[j + 3]);
-                            v.z = pack2(r[j + 4], r[j + 5]); v.w = pack2(r[j + 6], r[j + 7]);
-                            *reinterpret_cast<uint4*>(dst + j) = v;
-                        }
+    if (warp == 0) {
+        if (lane == 0 && kblocks > 0) {
+            // --------------------------------------------------------------------- producer
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BNO;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&sh.empty[s], ((it / STAGES) - 1) & 1, abort_flag, status)) { ok = false; break; }
+                    unsigned char* a_dst = tiles + s * G::STAGE_BYTES;
+                    mbar_expect_tx(&sh.full[s], G::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, &sh.full[s], kb * TC_BK, m0);
+                    if (GATED) {
+                        tma_load_2d(a_dst + G::A_BYTES, &map_w, &sh.full[s], kb * TC_BK, n0);
+                        tma_load_2d(a_dst + G::A_BYTES + G::W_BYTES / 2, &map_w, &sh.full[s], kb * TC_BK, gate_rows + n0);
                     } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        tma_load_2d(a_dst + G::A_BYTES, &map_w, &sh.full[s], kb * TC_BK, n0);
                     }
+                    sh.issued = it + 1;
                 }
-                continue;
             }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && kblocks > 0) {
+            // --------------------------------------------------------------------- MMA issuer
+            const uint32_t idesc = umma_idesc(TC_BM, BN);
+            int it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+                const int acc = tcount & 1;
+                if (tcount >= 2 && !mbar_wait(&sh.tempty[acc], ((tcount >> 1) - 1) & 1, abort_flag, status)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&sh.full[s], (it / STAGES) & 1, abort_flag, status)) { ok = false; break; }
+                    sh.consumed = it + 1;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + s * G::STAGE_BYTES);
+                    const uint32_t w_addr = a_addr + G::A_BYTES;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
-            __syncwarp();
-            const int col = n0 + c0 + lane;
-            if (col < N) {
-                float* base = reinterpret_cast<float*>(C) + (size_t)(m0 + warp * 32) * ldc + col;
-                const int rows = min(32, M - (m0 + warp * 32));
-                if (mode == TC_ADD_F32) {
-                    // read the 32 residual values first (independent loads), then add and write
-                    float old[32];
-#pragma unroll
-                    for (int rr = 0; rr < 32; ++rr) old[rr] = rr < rows ? base[(size_t)rr * ldc] : 0.f;
-#pragma unroll
-                    for (int rr = 0; rr < 32; ++rr)
-                        if (rr < rows) base[(size_t)rr * ldc] = old[rr] + stage[rr * 33 + lane];
+                    for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along K inside the swizzled row
+                        umma_bf16(d_tmem, umma_desc(a_addr + k * 32), umma_desc(w_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(&sh.empty[s]);       // arrives when the MMAs above have read the stage
+                }
+                if (ok) umma_commit(&sh.tfull[acc]);   // arrives when the tile's MMAs have finished
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------------- epilogue
+        const int q = warp & 3;                       // the quarter of TMEM lanes this warp may read
+        float* stage = epi + q * (32 * 33);
+        int tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BNO;
+            const int acc = tcount & 1;
+            if (kblocks > 0) {
+                if (!mbar_wait(&sh.tfull[acc], (tcount >> 1) & 1, abort_flag, status)) { ok = false; break; }
+                tc_fence_after();
+            }
+            const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BNO; c0 += 32) {
+                uint32_t r[32];
+                if (kblocks > 0) {
+                    tmem_load32(t_base + (uint32_t)c0, r);
                 } else {
 #pragma unroll
-                    for (int rr = 0; rr < 32; ++rr)
-                        if (rr < rows) base[(size_t)rr * ldc] = stage[rr * 33 + lane];
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
                 }
+                const int col0 = n0 + c0;
+                if (GATED) {
+                    uint32_t u[32];
+                    if (kblocks > 0) {
+                        tmem_load32(t_base + (uint32_t)(BN / 2 + c0), u);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) u[j] = 0u;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float g = __uint_as_float(r[j]);
+                        r[j] = __float_as_uint(g / (1.0f + __expf(-g)) * __uint_as_float(u[j]));
+                    }
+                }
+                if (GATED || mode == TC_STORE_BF16) {
+                    // a thread's 32 columns are 64 contiguous bytes: store them directly, 16 bytes at a time
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + col0;
+                    if (row < M) {
+                        if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 v;
+                                v.x = pack2(r[j], r[j + 1]); v.y = pack2(r[j + 2], r[j + 3]);
+                                v.z = pack2(r[j + 4], r[j + 5]); v.w = pack2(r[j + 6], r[j + 7]);
+                                *reinterpret_cast<uint4*>(dst + j) = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        }
+                    }
+                    continue;
+                }
+                // float32: through shared memory, so that one instruction writes one row (128 contiguous bytes)
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
+                __syncwarp();
+                const int col = col0 + lane;
+                if (col < N) {
+                    float* base = reinterpret_cast<float*>(C) + (size_t)(m0 + q * 32) * ldc + col;
+                    const int rows = min(32, M - (m0 + q * 32));
+                    if (mode == TC_ADD_F32) {
+                        float old[32];   // read the 32 residual values first (independent loads), then add and write
+#pragma unroll
+                        for (int rr = 0; rr < 32; ++rr) old[rr] = rr < rows ? base[(size_t)rr * ldc] : 0.f;
+#pragma unroll
+                        for (int rr = 0; rr < 32; ++rr)
+                            if (rr < rows) base[(size_t)rr * ldc] = old[rr] + stage[rr * 33 + lane];
+                    } else {
+#pragma unroll
+                        for (int rr = 0; rr < 32; ++rr)
+                            if (rr < rows) base[(size_t)rr * ldc] = stage[rr * 33 + lane];
+                    }
+                }
+                __syncwarp();
             }
+            // this warp is done with the accumulator: hand it back to the MMA issuer
+            tc_fence_before();
             __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.tempty[acc]);
         }
     }
 
@@ -259,13 +331,13 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(const __grid_constant
     if (warp == 0) {
         if (lane == 0 && sh.abort_flag) {
             // copies that were issued but never consumed may still be in flight: wait for them (bounded)
-            for (int kb = sh.consumed; kb < sh.issued; ++kb) {
+            for (int it = sh.consumed; it < sh.issued; ++it) {
                 const long long t0 = clock64();
-                while (!mbar_try_wait(&sh.full[kb % TC_STAGES], (kb / TC_STAGES) & 1) && clock64() - t0 < TC_WAIT_CYCLES) {}
+                while (!mbar_try_wait(&sh.full[it % STAGES], (it / STAGES) & 1) && clock64() - t0 < TC_WAIT_CYCLES) {}
             }
         }
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
     }
 }
 
@@ -301,19 +373,27 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return 0;
 }
 
-template <int BN>
+template <int BN, bool GATED>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int mode, int M, int N, int K,
-                     long long ldc, int* status, cudaStream_t stream) {
-    constexpr int smem = TC_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
-    auto kernel = gemm_tcgen05_kernel<BN>;
+                     long long ldc, int gate_rows, int* status, cudaStream_t stream) {
+    using G = TcGeometry<BN, GATED>;
+    auto kernel = gemm_tcgen05_kernel<BN, GATED>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        GB_REQUIRE(e == cudaSuccess, "gb_gemm_tcgen05: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
+        GB_REQUIRE(e == cudaSuccess, "gb_gemm_tcgen05: %d bytes of shared memory refused: %s", G::SMEM, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(gb_ceil_div(N, BN), gb_ceil_div(M, TC_BM));
-    kernel<<<grid, 128, smem, stream>>>(ma, mw, c, mode, M, N, K, ldc, status);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int ntiles = gb_ceil_div(M, TC_BM) * gb_ceil_div(N, G::BNO);
+    const int grid = ntiles < sms ? ntiles : sms;   // persistent: one block per SM walks the tiles
+    kernel<<<grid, 192, G::SMEM, stream>>>(ma, mw, c, mode, M, N, K, ldc, gate_rows, status);
     return gb_check_launch("gb_gemm_tcgen05");
 }
 
@@ -325,6 +405,15 @@ GB_EXPORT int gb_gemm_tcgen05_supported(const void* a, const void* w, int M, int
            (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0;
 }
 
+// Output tile width: the widest tile that still gives every SM a tile (wide tiles reuse the A operand
+// more and amortise the epilogue; narrow ones keep small problems spread over the GPU).
+static int pick_bn(int M, int N) {
+    const long long tm = gb_ceil_div(M, TC_BM);
+    if (tm * gb_ceil_div(N, 256) >= 120) return 256;
+    if (tm * gb_ceil_div(N, 128) >= 120) return 128;
+    return 64;
+}
+
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32.
 GB_EXPORT int gb_gemm_tcgen05(const void* a, const void* w, void* c, int mode, int M, int N, int K, long long lda,
                               long long ldw, long long ldc, int* status, cudaStream_t stream) {
@@ -332,11 +421,29 @@ GB_EXPORT int gb_gemm_tcgen05(const void* a, const void* w, void* c, int mode, i
                "gb_gemm_tcgen05: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d N=%d K=%d)",
                M, N, K);
     GB_REQUIRE(mode >= 0 && mode <= 2 && ldc >= N && status != nullptr, "gb_gemm_tcgen05: bad mode, ldc or status");
-    // Narrow tiles when wide ones would leave most SMs idle.
-    const bool wide = (long long)gb_ceil_div(N, 128) * gb_ceil_div(M, TC_BM) >= 120;
+    const int bn = pick_bn(M, N);
     CUtensorMap ma, mw;
     if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
-    if (make_map(&mw, w, N, K, ldw, wide ? 128 : 64)) return 1;
-    return wide ? launch_tc<128>(ma, mw, c, mode, M, N, K, ldc, status, stream)
-                : launch_tc<64>(ma, mw, c, mode, M, N, K, ldc, status, stream);
+    if (make_map(&mw, w, N, K, ldw, bn)) return 1;
+    if (bn == 256) return launch_tc<256, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream);
+    if (bn == 128) return launch_tc<128, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream);
+    return launch_tc<64, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream);
+}
+
+// Gated feed-forward input product: w = [gate rows; up rows] (2*inter rows), c bfloat16 [M, inter] =
+// silu(a gate^T) * (a up^T). inter must be a multiple of 8 (TMA row addressing needs nothing more).
+GB_EXPORT int gb_gemm_tcgen05_gated(const void* a, const void* w, void* c, int M, int inter, int K, long long lda,
+                                    long long ldw, long long ldc, int* status, cudaStream_t stream) {
+    GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, 2 * inter, K, lda, ldw),
+               "gb_gemm_tcgen05_gated: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d I=%d K=%d)",
+               M, inter, K);
+    GB_REQUIRE(ldc >= inter && status != nullptr, "gb_gemm_tcgen05_gated: bad ldc or status");
+    CUtensorMap ma, mw;
+    if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
+    const bool wide = (long long)gb_ceil_div(M, TC_BM) * gb_ceil_div(inter, 128) >= 120;
+    // the weight map covers only the rows that exist, so a box that runs past the gate rows of the last
+    // tile reads up rows: those columns are >= inter and are never stored
+    if (make_map(&mw, w, 2LL * inter, K, ldw, wide ? 128 : 64)) return 1;
+    return wide ? launch_tc<256, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream)
+                : launch_tc<128, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream);
 }

@@ -56,6 +56,7 @@ _SIGNATURES = {
     "gb_attention_prefill_supported": [_I, _I, _I, _I],
     "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P],
     "gb_gemm_tcgen05_supported": [_P, _P, _I, _I, _I, _LL, _LL],
+    "gb_gemm_tcgen05_gated": [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P],
 }
 
 
@@ -308,6 +309,23 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool 
         mode = 0 if c.dtype == torch.bfloat16 else 1
     _call("gb_gemm_tcgen05", _ptr(a), _ptr(w), _ptr(c), mode, M, N, K, a.stride(0), w.stride(0), c.stride(0),
           _ptr(status), _stream())
+
+
+def gemm_tc_gated(a: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor,
+                  status: Optional[torch.Tensor] = None) -> None:
+    """act[M, I] = silu(a gate^T) * (a up^T) with w_gate_up = [gate rows; up rows], on the tcgen05
+    kernel: gate and up columns of a tile sit side by side in one TMEM accumulator."""
+    _cuda(a, w_gate_up, act, status)
+    M, K = a.shape
+    inter = w_gate_up.shape[0] // 2
+    assert w_gate_up.shape == (2 * inter, K) and act.shape == (M, inter) and act.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1
+    if status is None:
+        status = _tc_status.get(a.device)
+        if status is None:
+            status = _tc_status[a.device] = torch.zeros(1, dtype=torch.int32, device=a.device)
+    _call("gb_gemm_tcgen05_gated", _ptr(a), _ptr(w_gate_up), _ptr(act), M, inter, K, a.stride(0), w_gate_up.stride(0),
+          act.stride(0), _ptr(status), _stream())
 
 
 def attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,

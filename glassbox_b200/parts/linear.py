@@ -59,4 +59,10 @@ def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
             and inter % 16 == 0 and act.dtype == torch.bfloat16):
         kernels.gemm_stream(x, w_gate_up, act, gated=True, norm=norm, prefetch=weights_ahead(ctx, w_gate_up))
         return True
+    if isinstance(a, DeferredNorm):
+        x = a.tensor()
+    if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and act.dtype == torch.bfloat16
+            and x.shape[0] > kernels.STREAM_MAX_ROWS and kernels.gemm_tc_supported(x, w_gate_up, act)):
+        kernels.gemm_tc_gated(x, w_gate_up, act, ctx.status)
+        return True
     return False

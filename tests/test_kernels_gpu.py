@@ -614,3 +614,38 @@ def test_gemm_stream_qkv_with_norm_rotary_and_cache_write(M, nh, nkv, hd, d, ps,
     kernels.gemm_stream_qkv(x, w, q2, table, positions.to(DEV), slots.to(DEV), kc3, vc3, nh, nkv, hd, ps, False, st,
                             norm=(gain, 1e-6))
     assert float(kc3.abs().max()) == 0.0 and float(vc3.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M, inter, K", [(128, 128, 64), (2048, 1536, 576), (300, 176, 72), (65, 8, 8), (1000, 2560, 960),
+                                         (129, 136, 200)])
+def test_gemm_tcgen05_gated(M, inter, K):
+    from glassbox_b200 import kernels
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, device=DEV) * (1.5 / math.sqrt(K))).to(torch.bfloat16)
+    act = torch.full((M, inter + 3), 9.0, device=DEV, dtype=torch.bfloat16)
+    st = status()
+    kernels.gemm_tc_gated(a, w, act[:, :inter], status=st)
+    assert int(st) == 0, "a bounded wait inside the kernel gave up"
+    gu = a.double() @ w.double().T
+    g, u = gu[:, :inter], gu[:, inter:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert ((act[:, :inter].double() - ref).abs() / (1 + ref.abs())).max() <= tol(torch.bfloat16, 1)
+    assert float((act[:, inter:].float() - 9.0).abs().max()) == 0.0        # nothing written beside the output
+
+
+def test_gemm_tcgen05_many_tiles_per_block():
+    """More tiles than SMs: every persistent block walks several tiles and both accumulators alternate."""
+    from glassbox_b200 import kernels
+    M, N, K = 4096, 4096, 256
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    c = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    st = status()
+    kernels.gemm_tc(a, w, c, status=st)
+    assert int(st) == 0
+    ref = (a.float() @ w.float().T)
+    assert (c.float() - ref).abs().max() <= tol(torch.bfloat16, 2)
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    kernels.gemm_tc(a, w, acc, accumulate=True, status=st)
+    assert (acc - base - ref).abs().max() <= 1e-3 and int(st) == 0
