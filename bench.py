@@ -192,7 +192,7 @@ def main():
         achieved = (weight_bytes + kv_bytes) / (ms_per_step / 1e3) / 1e9
 
         out = {
-            "metric": "decode tok/s at batch 8 (SmolLM2-135M shapes); prefill tok/s at 2,048 tokens",
+            "metric": f"decode tok/s at batch {args.batch} (SmolLM2-{args.model.upper()} shapes); prefill tok/s at 2,048 tokens",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic", "impl": "ours",

@@ -8,8 +8,8 @@
 // accumulate); the few activation rows sit in shared memory as the other operand; the four
 // partial sums are added through shared memory. Inside each block of 32 k-values a thread's 16
 // bytes are 8 consecutive k; the instruction's k index is a fixed permutation of them, applied to
-// both operands, so every dot product still sums the same products, in an order that depends only
-// on K, never on M or on a row's place in the batch.
+// both operands, so every dot product still sums the same products, in an order that depends on the
+// matrix and on the bucket of the row count (8, 16, 32, 64), never on a row's place in the batch.
 //
 // Folded in:
 //  * prologue: RMSNorm. Instead of bfloat16 activations the kernel can take the float32 residual
@@ -24,15 +24,21 @@
 //  * programmatic dependent launch: the first weights are requested before the kernel waits for
 //    its predecessor in the stream (they do not depend on it), and the successor is released at
 //    once, so consecutive small kernels overlap their start-up with each other's tails.
+//  * split K over a thread-block cluster: when the matrix has few strips and a long K (a 2048 x 8192
+//    down projection has 128 strips), one block per strip leaves most of the memory system idle. The
+//    strip is then given to a cluster of 2, 4 or 8 blocks, each with a contiguous slice of K; their sums
+//    travel through distributed shared memory to the cluster's first block, which adds them in rank
+//    order (a fixed order: the result does not depend on timing) and runs the epilogue.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 enum { WS_STORE_BF16 = 0, WS_STORE_F32 = 1, WS_ADD_F32 = 2, WS_GLU_BF16 = 3, WS_ROPE_QKV = 4 };
 
-constexpr int WS_KC = 256;             // k per shared-memory chunk
 constexpr int WS_PAD = 32;             // padding per activation row: row stride = 16 banks mod 32, so the
                                        // 16-byte operand loads of a quarter-warp never collide
-constexpr int WS_BLOCKS = WS_KC / 32;  // k32 blocks per chunk
-constexpr int WS_BPW = WS_BLOCKS / 4;  // k32 blocks per warp per chunk
 
 struct StreamArgs {
     const __nv_bfloat16* X;   // [M, K] bfloat16 activations, or nullptr when `xres` is normalised instead
@@ -56,6 +62,7 @@ struct StreamArgs {
     int nh, nkv, hd, page_size, max_pos, write_kv;
     long long num_slots;
     int* status;
+    int kslice;               // k per block of a cluster (a multiple of the chunk); K without a cluster
     // a region to pull into L2 for a later kernel (its weights), or nullptr
     const unsigned char* prefetch;
     long long prefetch_bytes;
@@ -81,10 +88,13 @@ __device__ __forceinline__ uint32_t ws_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int NT, bool PAIR>
+// KC: k per shared-memory chunk (256 or 512); each warp has KC/128 blocks of 32 k in flight per strip row
+template <int NT, bool PAIR, int KC>
 __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
     constexpr int ROWS = NT * 8;   // activation rows held
     constexpr int SETS = PAIR ? 2 : 1;
+    constexpr int WS_KC = KC;
+    constexpr int WS_BPW = KC / 32 / 4;   // k32 blocks per warp per chunk
     __shared__ __align__(16) __nv_bfloat16 xs[ROWS][WS_KC + WS_PAD];
     __shared__ float srow[ROWS];
     // the partial sums of the four warps reuse the activation tile once the k loop is over
@@ -97,13 +107,19 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
     // let the next kernel in the stream start its own prologue
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+    // a cluster shares one strip: block `crank` of `csize` takes k in [kbeg, kend)
+    cg::cluster_group cluster = cg::this_cluster();
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int strip = blockIdx.x / csize;
+    const int kbeg = min(K, crank * a.kslice), kend = min(K, kbeg + a.kslice);
+
     // first weight row of this block's strip (of its first strip, for a pair)
     int n0;
     if (a.mode == WS_ROPE_QKV) {
         const int per_head = a.hd / 32;   // strip pairs per head
-        n0 = (blockIdx.x / per_head) * a.hd + (blockIdx.x % per_head) * 16;
+        n0 = (strip / per_head) * a.hd + (strip % per_head) * 16;
     } else {
-        n0 = blockIdx.x * 16;
+        n0 = strip * 16;
     }
 
     float acc[SETS][NT][4];
@@ -124,13 +140,13 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
         wb[s] = a.W + (size_t)(row_b + s * a.pair_offset) * a.ldw;
     }
 
-    const int nchunks = (K + WS_KC - 1) / WS_KC;
+    const int nchunks = (kend - kbeg + WS_KC - 1) / WS_KC;
     uint4 fa[SETS][WS_BPW], fb[SETS][WS_BPW];
     auto fetch = [&](int chunk) {
 #pragma unroll
         for (int j = 0; j < WS_BPW; ++j) {
-            const int k = chunk * WS_KC + (j * 4 + warp) * 32 + 8 * t;
-            const bool in = k < K;
+            const int k = kbeg + chunk * WS_KC + (j * 4 + warp) * 32 + 8 * t;
+            const bool in = k < kend;
 #pragma unroll
             for (int s = 0; s < SETS; ++s) {
                 fa[s][j] = (in && live_a) ? ldg_stream(wa[s] + k) : make_uint4(0, 0, 0, 0);
@@ -139,7 +155,7 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
         }
     };
 
-    fetch(0);   // weights do not depend on the previous kernel
+    if (nchunks > 0) fetch(0);   // weights do not depend on the previous kernel
     if (a.prefetch != nullptr) {
         // While this kernel waits for its predecessor and works, the weights of a kernel further down
         // the stream travel from HBM to L2: each block asks for its share, one 128-byte line per thread.
@@ -173,11 +189,11 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
 #pragma unroll
         for (int i = 0; i < XPT; ++i) {
             const int c = tid + i * 128;
-            const int row = c / (WS_KC / 8), k = chunk * WS_KC + (c % (WS_KC / 8)) * 8;
-            xr[i] = (row < M && k < K) ? *reinterpret_cast<const uint4*>(a.X + (size_t)row * a.ldx + k) : make_uint4(0, 0, 0, 0);
+            const int row = c / (WS_KC / 8), k = kbeg + chunk * WS_KC + (c % (WS_KC / 8)) * 8;
+            xr[i] = (row < M && k < kend) ? *reinterpret_cast<const uint4*>(a.X + (size_t)row * a.ldx + k) : make_uint4(0, 0, 0, 0);
         }
     };
-    if (!normalise) xload(0);
+    if (!normalise && nchunks > 0) xload(0);
 
     for (int chunk = 0; chunk < nchunks; ++chunk) {
         // stage the activations of this chunk: ROWS x 256
@@ -185,9 +201,9 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
         if (normalise) {
             for (int c = tid; c < ROWS * (WS_KC / 8); c += 128) {
                 const int row = c / (WS_KC / 8), col = (c % (WS_KC / 8)) * 8;
-                const int k = chunk * WS_KC + col;
+                const int k = kbeg + chunk * WS_KC + col;
                 uint4 v = make_uint4(0, 0, 0, 0);
-                if (row < M && k < K) {
+                if (row < M && k < kend) {
                     const float* xrow = a.xres + (size_t)row * a.ldr + k;
                     const float4 x0 = *reinterpret_cast<const float4*>(xrow), x1 = *reinterpret_cast<const float4*>(xrow + 4);
                     const float4 g0 = *reinterpret_cast<const float4*>(a.gain + k);
@@ -246,15 +262,45 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
                 red[((warp * SETS + s) * 16 + row) * ROWS + tok] = acc[s][i][j];
             }
     __syncthreads();
-    for (int e = tid; e < 16 * ROWS; e += 128) {
+    // each thread owns NT elements (strip row, token) of the block's tile and sums the four warps' parts
+    float sum[NT][SETS];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        const int e = tid + i * 128, row = e % 16, tok = e / 16;
+#pragma unroll
+        for (int s = 0; s < SETS; ++s) {
+            sum[i][s] = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) sum[i][s] += red[((w * SETS + s) * 16 + row) * ROWS + tok];
+        }
+    }
+    if (csize > 1) {
+        // the first block's tile is free once every block of the cluster has passed this point; the others
+        // write their sums into it, one plane per rank, and it adds them in rank order
+        constexpr int PLANE = SETS * 16 * ROWS;
+        cluster.sync();
+        if (crank > 0) {
+            float* dst = cluster.map_shared_rank(red, 0) + (size_t)(crank - 1) * PLANE;
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int s = 0; s < SETS; ++s) dst[s * 16 * ROWS + tid + i * 128] = sum[i][s];
+        }
+        cluster.sync();
+        if (crank > 0) return;
+        for (int rk = 1; rk < csize; ++rk)
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int s = 0; s < SETS; ++s) sum[i][s] += red[(rk - 1) * PLANE + s * 16 * ROWS + tid + i * 128];
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        const int e = tid + i * 128;
         const int row = e % 16, tok = e / 16;   // consecutive threads -> consecutive n
         const int n = n0 + row;
         if (n >= N || tok >= M) continue;
-        float v[2] = {0.f, 0.f};
-#pragma unroll
-        for (int s = 0; s < SETS; ++s)
-#pragma unroll
-            for (int w = 0; w < 4; ++w) v[s] += red[((w * SETS + s) * 16 + row) * ROWS + tok];
+        float v[2] = {sum[i][0], SETS > 1 ? sum[i][SETS - 1] : 0.f};
         if (a.mode == WS_ROPE_QKV) {
             const int pos = a.positions[tok];
             if (pos < 0) continue;               // padding row
@@ -301,19 +347,30 @@ __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
     }
 }
 
-template <int NT, bool PAIR>
-static int launch_stream(const StreamArgs& a, int blocks, int pdl, cudaStream_t stream) {
+template <int NT, bool PAIR, int KC>
+static int launch_stream(const StreamArgs& a, int strips, int split, int pdl, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(blocks);
+    cfg.gridDim = dim3(strips * split);
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (split > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = split;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, PAIR>, a);
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, PAIR, KC>, a);
     if (e != cudaSuccess) {
         gb_set_error("gb_gemm_stream: launch failed: %s", cudaGetErrorString(e));
         return 2;
@@ -321,14 +378,72 @@ static int launch_stream(const StreamArgs& a, int blocks, int pdl, cudaStream_t 
     return gb_check_launch("gb_gemm_stream");
 }
 
-static int dispatch_stream(const StreamArgs& a, int blocks, bool pair, int pdl, cudaStream_t stream) {
+// Overrides for measurements: chunk (0 = choose, 256, 512) and cluster size (0 = choose, 1, 2, 4, 8).
+static int g_tune_chunk = 0, g_tune_split = 0;
+GB_EXPORT void gb_gemm_stream_tune(int chunk, int split) {
+    g_tune_chunk = chunk;
+    g_tune_split = split;
+}
+
+static int stream_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+// blocks of one instantiation that the chip holds at a time
+template <int NT, bool PAIR, int KC>
+static int stream_slots() {
+    static int slots = 0;
+    if (slots == 0) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_stream_kernel<NT, PAIR, KC>, 128, 0) != cudaSuccess || per_sm <= 0)
+            per_sm = 1;
+        slots = per_sm * stream_sm_count();
+    }
+    return slots;
+}
+
+static int slots_of(int nt, bool pair, int kc) {
+#define GB_SL(NTT) return pair ? (kc == 512 ? stream_slots<NTT, true, 512>() : stream_slots<NTT, true, 256>()) \
+                               : (kc == 512 ? stream_slots<NTT, false, 512>() : stream_slots<NTT, false, 256>());
+    if (nt == 1) { GB_SL(1) }
+    if (nt == 2) { GB_SL(2) }
+    if (nt == 4) { GB_SL(4) }
+    return pair ? stream_slots<8, true, 256>() : stream_slots<8, false, 256>();
+#undef GB_SL
+}
+
+static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStream_t stream) {
     const int nt = a.M <= 8 ? 1 : a.M <= 16 ? 2 : a.M <= 32 ? 4 : 8;
-#define GB_WS(NTT) return pair ? launch_stream<NTT, true>(a, blocks, pdl, stream) : launch_stream<NTT, false>(a, blocks, pdl, stream);
+    // The wide chunk keeps twice the loads in flight per thread, at twice the registers: it is taken
+    // where its blocks still fit the chip in one wave (and never by the variants with many rows, which
+    // have neither the registers nor the shared memory for it).
+    const bool wide_fits = nt <= (pair ? 2 : 4);
+    int kc = (wide_fits && strips <= slots_of(nt, pair, 512)) ? 512 : 256;
+    if (g_tune_chunk == 256 || (g_tune_chunk == 512 && wide_fits)) kc = g_tune_chunk;
+    // Cluster size: one block per 512 k, rounded up to a power of two, as long as all blocks are on the
+    // chip at once and the other ranks' sums fit the first block's activation tile. Chunk and cluster
+    // size depend on the matrix and on the row bucket (8, 16, 32, 64), not on which rows are in the batch.
+    const int max_split = (kc + 32) / 32 / (pair ? 2 : 1) + 1;   // (split - 1) * sets * 32 <= kc + 32
+    const int slots = slots_of(nt, pair, kc);
+    int split = 1;
+    while (split < 8 && split < a.K / 512) split *= 2;
+    while (split > 1 && (split > max_split || strips * split > slots)) split /= 2;
+    if (g_tune_split >= 1 && g_tune_split <= 8 && g_tune_split <= max_split) split = g_tune_split;
+    a.kslice = split == 1 ? a.K : ((a.K + split - 1) / split + kc - 1) / kc * kc;
+#define GB_WS2(NTT, KCC) return pair ? launch_stream<NTT, true, KCC>(a, strips, split, pdl, stream) : launch_stream<NTT, false, KCC>(a, strips, split, pdl, stream);
+#define GB_WS(NTT) if (kc == 512) { GB_WS2(NTT, 512) } else { GB_WS2(NTT, 256) }
     if (nt == 1) { GB_WS(1) }
     if (nt == 2) { GB_WS(2) }
     if (nt == 4) { GB_WS(4) }
-    GB_WS(8)
+    GB_WS2(8, 256)
 #undef GB_WS
+#undef GB_WS2
 }
 
 static int check_common(const char* who, const void* x, const float* xres, const void* w, int M, int N, int K,

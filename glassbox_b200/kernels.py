@@ -254,6 +254,15 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
           *_prefetch_args(prefetch), 1 if USE_PDL else 0, _stream())
 
 
+def gemm_stream_tune(chunk: int = 0, split: int = 0) -> None:
+    """For measurements: force the weight-streaming kernel's k chunk (256, 512) and cluster size (1, 2, 4,
+    8); 0 gives the choice back to the kernel's own rule."""
+    handle = lib()
+    handle.gb_gemm_stream_tune.argtypes = [ctypes.c_int, ctypes.c_int]
+    handle.gb_gemm_stream_tune.restype = None
+    handle.gb_gemm_stream_tune(int(chunk), int(split))
+
+
 def gemm_stream_qkv_supported(a, w: torch.Tensor, hd: int, q_out: torch.Tensor) -> bool:
     return (gemm_stream_supported(a, w) and a.shape[0] <= STREAM_FUSE_MAX_ROWS and hd % 32 == 0
             and q_out.dtype == torch.bfloat16)

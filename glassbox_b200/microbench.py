@@ -1,0 +1,164 @@
+"""Times single kernels on SmolLM2 shapes with CUDA events, inside a CUDA graph (no launch overhead),
+over operands that rotate through more memory than L2 holds.
+
+    python -m glassbox_b200.microbench gemm_stream [135m|360m|1.7b ...]   weight-streaming GEMM, 1..64 rows
+    python -m glassbox_b200.microbench gemm_tc                           tcgen05 GEMM against torch.matmul
+    python -m glassbox_b200.microbench attention_decode [batch ...]      paged decode attention at context 4096
+    python -m glassbox_b200.microbench attention_prefill                 flash attention, one 2048-token prompt
+
+Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import kernels
+
+DEV = "cuda:0"
+L2_BYTES = 126e6
+
+#: (name, output rows N, K, gated) of the per-layer matrices and the head
+FAMILIES = {
+    "135m": [("qkv", 960, 576, False), ("o", 576, 576, False), ("gate_up", 1536, 576, True), ("down", 576, 1536, False),
+             ("head", 49152, 576, False)],
+    "360m": [("qkv", 1600, 960, False), ("o", 960, 960, False), ("gate_up", 2560, 960, True), ("down", 960, 2560, False),
+             ("head", 49152, 960, False)],
+    "1.7b": [("qkv", 6144, 2048, False), ("o", 2048, 2048, False), ("gate_up", 8192, 2048, True),
+             ("down", 2048, 8192, False), ("head", 49152, 2048, False)],
+}
+
+
+def graph_time(fn, reps: int = 12, outer: int = 5) -> float:
+    """Mean microseconds of one ``fn()`` among ``reps`` captured in a graph that is replayed ``outer`` times."""
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(reps):
+            fn()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(outer):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * outer)
+
+
+def _rotating(rows: int, k: int):
+    """Enough copies of a [rows, k] bfloat16 matrix that consecutive calls never find theirs in L2."""
+    n = max(2, min(12, int(3 * L2_BYTES / (rows * k * 2)) + 1))
+    return [(torch.randn(rows, k, device=DEV) * 0.05).bfloat16() for _ in range(n)]
+
+
+def bench_gemm_stream(families) -> None:
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for fam in families or list(FAMILIES):
+        for name, n, k, gated in FAMILIES[fam]:
+            rows = 2 * n if gated else n
+            ws = _rotating(rows, k)
+            for m in (1, 8, 16, 32, 64):
+                a = torch.randn(m, k, device=DEV).bfloat16()
+                c = torch.empty(m, n, device=DEV, dtype=torch.bfloat16 if gated else torch.float32)
+                turn = [0]
+
+                def stream():
+                    kernels.gemm_stream(a, ws[turn[0] % len(ws)], c, gated=gated)
+                    turn[0] += 1
+
+                def tiles():
+                    w = ws[turn[0] % len(ws)]
+                    kernels.gemm_tc_gated(a, w, c, status) if gated else kernels.gemm_tc(a, w, c, False, status)
+                    turn[0] += 1
+
+                t = graph_time(stream)
+                line = f"{fam} {name:8s} {rows:6d} x {k:5d} rows {m:3d}: stream {t:7.1f} us {rows * k * 2 / t / 1e3:6.0f} GB/s"
+                if m >= 16 and kernels.gemm_tc_supported(a, ws[0], c):
+                    line += f" | tcgen05 {graph_time(tiles):7.1f} us"
+                print(line, flush=True)
+    kernels.check_status(status)
+
+
+def bench_gemm_tc() -> None:
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for name, m, n, k in [("135m qkv", 2048, 960, 576), ("135m o", 2048, 576, 576), ("135m down", 2048, 576, 1536),
+                          ("1.7b qkv", 2048, 6144, 2048), ("1.7b gate_up", 2048, 16384, 2048),
+                          ("1.7b down", 2048, 2048, 8192), ("square", 8192, 8192, 8192)]:
+        a = torch.randn(m, k, device=DEV).bfloat16()
+        w = torch.randn(n, k, device=DEV).bfloat16()
+        c = torch.empty(m, n, device=DEV).bfloat16()
+        t = graph_time(lambda: kernels.gemm_tc(a, w, c, False, status), reps=6)
+        t2 = graph_time(lambda: torch.matmul(a, w.T, out=c), reps=6)
+        fl = 2.0 * m * n * k
+        print(f"{name:13s} {m} x {n} x {k}: tcgen05 {t:8.1f} us {fl / t / 1e6:7.1f} TFLOP/s | torch.matmul {t2:8.1f} us "
+              f"{fl / t2 / 1e6:7.1f} TFLOP/s", flush=True)
+    kernels.check_status(status)
+
+
+def bench_attention_decode(batches) -> None:
+    nh, nkv, hd, ps, ctx = 9, 3, 64, 16, 4096
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for m in batches or (1, 8, 64):
+        per = ctx // ps
+        kc = torch.randn(m * per + 4, nkv, ps, hd, device=DEV).bfloat16()
+        vc = torch.randn_like(kc)
+        tables = torch.arange(m * per, dtype=torch.int32, device=DEV).view(m, per).contiguous()
+        row_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+        pos = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
+        q = torch.randn(m, nh * hd, device=DEV).bfloat16()
+        o = torch.empty_like(q)
+        splits, block_keys = kernels.decode_mma_plan(m, nkv, hd, ctx)
+        pa = torch.empty(m * nh * 4 * splits * hd, device=DEV)
+        pm = torch.empty(m * nh * 4 * splits * 2, device=DEV)
+        cn = torch.zeros(m * nkv, dtype=torch.int32, device=DEV)
+        t = graph_time(lambda: kernels.attention_decode_mma(q, o, kc, vc, tables, row_seq, pos, nh, nkv, hd, ps, hd ** -0.5,
+                                                            None, splits, pa, pm, cn, status, block_keys))
+        nbytes = m * ctx * nkv * hd * 2 * 2
+        print(f"attention_decode_mma batch {m:3d} ctx {ctx} splits {splits} keys/iteration {block_keys or 32}: {t:7.1f} us "
+              f"{nbytes / t / 1e3:6.0f} GB/s", flush=True)
+    kernels.check_status(status)
+
+
+def bench_attention_prefill() -> None:
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for nh, nkv, hd, t_len in [(9, 3, 64, 2048), (15, 5, 64, 2048), (32, 32, 64, 2048)]:
+        ps = 16
+        per = t_len // ps
+        kc = torch.randn(per + 2, nkv, ps, hd, device=DEV).bfloat16()
+        vc = torch.randn_like(kc)
+        tables = torch.arange(per, dtype=torch.int32, device=DEV).view(1, per).contiguous()
+        first = torch.tensor([0, t_len], dtype=torch.int32, device=DEV)
+        start = torch.zeros(1, dtype=torch.int32, device=DEV)
+        q = torch.randn(t_len, nh * hd, device=DEV).bfloat16()
+        o = torch.empty_like(q)
+        t = graph_time(lambda: kernels.attention_prefill(q, o, kc, vc, tables, first, start, t_len, nh, nkv, hd, ps,
+                                                         hd ** -0.5, None, status), reps=6)
+        fl = 2.0 * t_len * t_len * nh * hd   # QK^T and PV over the causal half
+        print(f"attention_prefill heads {nh}/{nkv} x {hd}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+    kernels.check_status(status)
+
+
+def main(argv) -> int:
+    if not argv or argv[0] not in ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill"):
+        print(__doc__)
+        return 2
+    torch.cuda.set_device(0)
+    kernels.lib()
+    if argv[0] == "gemm_stream":
+        bench_gemm_stream(argv[1:])
+    elif argv[0] == "gemm_tc":
+        bench_gemm_tc()
+    elif argv[0] == "attention_decode":
+        bench_attention_decode([int(x) for x in argv[1:]])
+    else:
+        bench_attention_prefill()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))

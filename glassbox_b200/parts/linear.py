@@ -31,14 +31,21 @@ def _resolve(a):
     return a, None, None
 
 
+def _tile_kernel_wins(rows: int, w: torch.Tensor) -> bool:
+    """With few rows the weight-streaming kernel is the fast one, except where one strip of 16 outputs
+    per block makes thousands of blocks that each stage all rows again: a very wide matrix (the head)
+    with more than 16 rows, or a large one with more than 32. Measured at 64 rows: 49152 x 576, 28 us
+    against 93 us; 6144 x 2048, 16 us against 33 us; but 2048 x 8192, 43 us against 33 us (few tiles,
+    long k) and everything smaller stays with the streaming kernel."""
+    n, k = w.shape
+    return (rows > 16 and n >= 16384) or (rows > 32 and n >= 4096 and k >= 1024)
+
+
 def linear(ctx, a, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """``a`` is a tensor or a ``DeferredNorm``; the latter is folded into the weight-streaming kernel
     when that kernel runs, and computed first otherwise."""
     x, norm, deferred = _resolve(a)
-    # Few rows: the weight-streaming kernel. Except for a very wide matrix (the head) with more than
-    # 16 rows, where one strip of 16 outputs per block makes thousands of blocks that each repeat the
-    # staging of all rows: there the tile kernel is faster (measured: 28 us against 80 us at 64 rows).
-    wide = x.shape[0] > 16 and w.shape[0] >= 16384 and norm is None and kernels.gemm_tc_supported(x, w, out)
+    wide = norm is None and _tile_kernel_wins(x.shape[0], w) and kernels.gemm_tc_supported(x, w, out)
     if not wide and kernels.gemm_stream_supported(x, w) and (norm is not None or x.dtype == torch.bfloat16):
         kernels.gemm_stream(x, w, out, accumulate, norm=norm, prefetch=weights_ahead(ctx, w))
         return
@@ -55,14 +62,16 @@ def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
     does nothing) otherwise, and the caller runs the product and the activation separately."""
     inter = w_gate_up.shape[0] // 2
     x, norm, _ = _resolve(a)
-    if (kernels.gemm_stream_supported(x, w_gate_up) and (norm is not None or x.dtype == torch.bfloat16)
+    tiles = (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and act.dtype == torch.bfloat16
+             and kernels.gemm_tc_supported(x, w_gate_up, act))
+    wide = norm is None and tiles and _tile_kernel_wins(x.shape[0], w_gate_up)
+    if (not wide and kernels.gemm_stream_supported(x, w_gate_up) and (norm is not None or x.dtype == torch.bfloat16)
             and inter % 16 == 0 and act.dtype == torch.bfloat16):
         kernels.gemm_stream(x, w_gate_up, act, gated=True, norm=norm, prefetch=weights_ahead(ctx, w_gate_up))
         return True
     if isinstance(a, DeferredNorm):
         x = a.tensor()
-    if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and act.dtype == torch.bfloat16
-            and x.shape[0] > kernels.STREAM_MAX_ROWS and kernels.gemm_tc_supported(x, w_gate_up, act)):
+    if wide or (tiles and x.shape[0] > kernels.STREAM_MAX_ROWS):
         kernels.gemm_tc_gated(x, w_gate_up, act, ctx.status)
         return True
     return False
