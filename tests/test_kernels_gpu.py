@@ -337,7 +337,8 @@ def test_sizes_outside_the_kernels_range_are_refused():
 
 
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 31, 33, 64])
-@pytest.mark.parametrize("N, K", [(16, 8), (100, 40), (576, 576), (960, 264), (49, 1544), (3072, 576)])
+@pytest.mark.parametrize("N, K", [(16, 8), (100, 40), (576, 576), (960, 264), (49, 1544), (3072, 576),
+                                  (576, 1536), (960, 2560), (2048, 2048), (40, 8200)])   # the last four: K split over a cluster
 def test_gemm_stream(M, N, K):
     from glassbox_b200 import kernels
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -354,14 +355,17 @@ def test_gemm_stream(M, N, K):
     acc = base.clone()
     kernels.gemm_stream(a, w, acc, accumulate=True)
     assert (acc.double() - base.double() - ref).abs().max() <= 2e-5 * math.sqrt(K)
-    # the same row gives the same bits whatever else is in the batch
-    one = torch.empty(1, N, device=DEV)
-    kernels.gemm_stream(a[:1], w, one)
-    assert torch.equal(one[0], c32[0])
+    # the same row gives the same bits whatever else is in the batch and wherever it stands in it
+    other = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    place = M // 2
+    other[place] = a[0]
+    moved = torch.empty(M, N, device=DEV)
+    kernels.gemm_stream(other, w, moved)
+    assert torch.equal(moved[place], c32[0])
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 24, 64])
-@pytest.mark.parametrize("inter, K", [(16, 16), (176, 64), (1536, 576), (48, 1000)])
+@pytest.mark.parametrize("inter, K", [(16, 16), (176, 64), (1536, 576), (48, 1000), (256, 2048), (48, 4104)])
 def test_gemm_stream_gated(M, inter, K):
     from glassbox_b200 import kernels
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -451,7 +455,8 @@ def test_attention_decode_mma_one_far_key_stands_out():
 
 
 @pytest.mark.parametrize("M, N, K", [(128, 128, 64), (128, 64, 128), (65, 960, 576), (200, 576, 576), (2048, 3072, 576),
-                                     (300, 100, 72), (129, 49160, 576), (1000, 576, 1536), (77, 8, 8), (256, 200, 1000)])
+                                     (300, 100, 72), (129, 49160, 576), (1000, 576, 1536), (77, 8, 8), (256, 200, 1000),
+                                     (33, 4096, 1024), (17, 16384, 64), (1, 128, 64)])   # few rows: a partly empty tile
 def test_gemm_tcgen05(M, N, K):
     from glassbox_b200 import kernels
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -551,7 +556,7 @@ def test_attention_prefill_each_row_finds_its_own_far_key():
 
 
 @pytest.mark.parametrize("M", [1, 8, 23, 64])
-@pytest.mark.parametrize("N, K", [(576, 576), (100, 264), (3072, 1544)])
+@pytest.mark.parametrize("N, K", [(576, 576), (100, 264), (3072, 1544), (960, 2560)])
 def test_gemm_stream_with_the_norm_folded_in(M, N, K):
     from glassbox_b200 import kernels
     x = torch.randn(M, K, device=DEV) * 3
@@ -571,7 +576,8 @@ def test_gemm_stream_with_the_norm_folded_in(M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 33, 64])
-@pytest.mark.parametrize("nh, nkv, hd, d, ps, rotary", [(9, 3, 64, 576, 16, True), (2, 1, 32, 96, 32, True), (4, 4, 128, 256, 16, False)])
+@pytest.mark.parametrize("nh, nkv, hd, d, ps, rotary", [(9, 3, 64, 576, 16, True), (2, 1, 32, 96, 32, True), (4, 4, 128, 256, 16, False),
+                                                          (3, 1, 64, 2048, 16, True)])
 def test_gemm_stream_qkv_with_norm_rotary_and_cache_write(M, nh, nkv, hd, d, ps, rotary):
     from glassbox_b200 import kernels
     from glassbox_b200.parts.rope import rotary_table
@@ -617,7 +623,7 @@ def test_gemm_stream_qkv_with_norm_rotary_and_cache_write(M, nh, nkv, hd, d, ps,
 
 
 @pytest.mark.parametrize("M, inter, K", [(128, 128, 64), (2048, 1536, 576), (300, 176, 72), (65, 8, 8), (1000, 2560, 960),
-                                         (129, 136, 200)])
+                                         (129, 136, 200), (40, 2048, 1024)])
 def test_gemm_tcgen05_gated(M, inter, K):
     from glassbox_b200 import kernels
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
