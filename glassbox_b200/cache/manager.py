@@ -18,31 +18,25 @@ every group. Beside the pages there are *state slots*: one fixed-size slot per l
 mixers that keep a state instead of keys (and for anything else that is per request and of fixed
 size); a slot is handed out at admission, zeroed before first use, copied on fork, and returned
 when the request ends.
+
+The bookkeeping itself is C++ (``csrc/host/cache_core.cpp``, loaded with ctypes); this module names
+requests by any hashable id, turns return codes into exceptions, and checks the invariants from
+outside, on the state the library reports.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+import threading
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ..csrc import build as _build
 
 
 class OutOfPages(Exception):
     """Not enough free pages (or no free state slot) for what was asked; nothing was changed."""
-
-
-_FNV_OFFSET = 0xCBF29CE484222325
-_FNV_PRIME = 0x100000001B3
-_MASK = (1 << 64) - 1
-
-
-def chain_hash(prev: int, tokens: Sequence[int]) -> int:
-    """FNV-1a over the previous hash and one page of token ids (little-endian u32 bytes),
-    crates/glassbox-core/src/kv.rs:45-55."""
-    h = (prev ^ _FNV_OFFSET) & _MASK
-    for t in tokens:
-        for b in int(t).to_bytes(4, "little"):
-            h ^= b
-            h = (h * _FNV_PRIME) & _MASK
-    return h
 
 
 @dataclass
@@ -54,129 +48,186 @@ class GroupSpec:
     name: str = ""
 
 
-class _Group:
-    def __init__(self, spec: GroupSpec, share_prefixes: bool):
-        if spec.num_pages <= 0 or spec.page_size <= 0:
-            raise ValueError("a cache group needs a positive number of pages and a positive page size")
-        self.spec = spec
-        self.page_size = spec.page_size
-        self.window = spec.window
-        self.refs = [0] * spec.num_pages
-        # Page 0 pops first (kv.rs:67).
-        self.free: List[int] = list(range(spec.num_pages - 1, -1, -1))
-        self.tables: Dict[object, List[int]] = {}
-        self.share = share_prefixes and spec.window is None
-        self.by_hash: Dict[int, int] = {}
-        self.page_hash: List[Optional[int]] = [None] * spec.num_pages
-        self.cached: List[int] = []  # unreferenced pages kept for prefix reuse, oldest first
-
-    # -- pool ------------------------------------------------------------------------------
-    def free_pages(self) -> int:
-        return len(self.free) + len(self.cached)
-
-    def alloc(self) -> int:
-        if self.free:
-            p = self.free.pop()
-        elif self.cached:
-            p = self.cached.pop(0)
-            h = self.page_hash[p]
-            if h is not None:
-                self.page_hash[p] = None
-                self.by_hash.pop(h, None)
-        else:
-            raise OutOfPages()
-        assert self.refs[p] == 0, "allocated a page that is still referenced"
-        self.refs[p] = 1
-        return p
-
-    def release(self, p: int) -> None:
-        assert self.refs[p] > 0, f"page {p} freed twice"
-        self.refs[p] -= 1
-        if self.refs[p] == 0:
-            if self.page_hash[p] is not None:
-                self.cached.append(p)
-            else:
-                self.free.append(p)
-
-    def retain(self, p: int) -> None:
-        if self.refs[p] == 0:
-            self.cached.remove(p)
-        self.refs[p] += 1
-
-    # -- what a reservation needs --------------------------------------------------------------
-    def first_live_page(self, length: int) -> int:
-        """Index of the first page a query at position >= ``length`` can still see."""
-        if self.window is None:
-            return 0
-        return max(0, length - self.window + 1) // self.page_size
-
-    def plan(self, table: List[int], length: int, n: int) -> Tuple[int, bool]:
-        """(new pages, copy-on-write needed) to write positions length .. length+n-1."""
-        need = -(-(length + n) // self.page_size)
-        new = max(0, need - len(table))
-        cow = False
-        if n > 0 and length % self.page_size and length // self.page_size < len(table):
-            last = table[length // self.page_size]
-            cow = last >= 0 and self.refs[last] > 1
-        return new, cow
+_I, _LL, _P = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p
+_SIGNATURES = {
+    "gbh_cache_new": ([_I, _P, _P, _P, _I, _I, _I], _P),
+    "gbh_cache_delete": ([_P], None),
+    "gbh_cache_shares_prefixes": ([_P], _I),
+    "gbh_cache_add": ([_P, _LL, _P, _I, _P], _I),
+    "gbh_cache_reserve": ([_P, _LL, _I, _P, _P], _I),
+    "gbh_cache_commit": ([_P, _LL, _P, _I], _I),
+    "gbh_cache_truncate": ([_P, _LL, _I], _I),
+    "gbh_cache_fork": ([_P, _LL, _LL, _P], _I),
+    "gbh_cache_free": ([_P, _LL], _I),
+    "gbh_cache_has": ([_P, _LL], _I),
+    "gbh_cache_length": ([_P, _LL], _I),
+    "gbh_cache_slot": ([_P, _LL], _I),
+    "gbh_cache_free_pages": ([_P, _I], _I),
+    "gbh_cache_ref_count": ([_P, _I, _I], _I),
+    "gbh_cache_table": ([_P, _I, _LL, _P, _I], _I),
+    "gbh_cache_tokens": ([_P, _LL, _P, _I], _I),
+    "gbh_cache_slots": ([_P, _I, _I, _P, _I], _I),
+    "gbh_cache_pool": ([_P, _I, _I, _P, _I], _I),
+    "gbh_cache_hashes": ([_P, _I, _P, _P, _I, _P], _I),
+    "gbh_cache_ids": ([_P, _I, _P, _I], _I),
+    "gbh_chain_hash": ([ctypes.c_uint64, _P, _I], ctypes.c_uint64),
+    "gbh_fill_step": ([_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _I, _P, _P], _I),
+}
+_lib = None
+_lock = threading.Lock()
 
 
-@dataclass
-class _Request:
-    length: int = 0                      # tokens whose keys/values (or state) are written
-    tokens: List[int] = field(default_factory=list)
-    slot: int = -1
+def host_lib():
+    """The C++ host library; built at first use."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                handle = ctypes.CDLL(_build.ensure_host_built())
+                handle.gbh_last_error.restype = ctypes.c_char_p
+                handle.gbh_last_error.argtypes = []
+                for name, (args, res) in _SIGNATURES.items():
+                    fn = getattr(handle, name)
+                    fn.argtypes, fn.restype = args, res
+                _lib = handle
+    return _lib
+
+
+def _ints(values, dtype=np.int32) -> np.ndarray:
+    return np.ascontiguousarray(values, dtype=dtype)
+
+
+def chain_hash(prev: int, tokens: Sequence[int]) -> int:
+    """FNV-1a over the previous hash and one page of token ids (little-endian u32 bytes),
+    crates/glassbox-core/src/kv.rs:45-55."""
+    toks = _ints(tokens)
+    return int(host_lib().gbh_chain_hash(ctypes.c_uint64(prev), toks.ctypes.data, toks.size))
+
+
+class _GroupView:
+    """What the rest of the engine may know about a group."""
+
+    def __init__(self, spec: GroupSpec):
+        self.spec, self.page_size, self.window = spec, spec.page_size, spec.window
 
 
 class CacheManager:
     def __init__(self, groups: Sequence[GroupSpec], max_requests: int = 64, share_prefixes: bool = False,
                  has_state: bool = False):
-        # Prefix sharing is only sound when what a page holds is a pure function of the token
-        # prefix for every mixer: no windows (pages vanish) and no per-request state.
-        sound = share_prefixes and not has_state and all(g.window is None for g in groups)
-        self.share_prefixes = sound
-        self.groups = [_Group(g, sound) for g in groups]
-        self.requests: Dict[object, _Request] = {}
+        groups = list(groups)
+        for g in groups:
+            if g.num_pages <= 0 or g.page_size <= 0:
+                raise ValueError("a cache group needs a positive number of pages and a positive page size")
+        self._lib = host_lib()
+        self.groups = [_GroupView(g) for g in groups]
         self.max_requests = max_requests
-        self.free_slots: List[int] = list(range(max_requests - 1, -1, -1))
-        self.fresh_slots: List[int] = []  # handed out since the last drain: to be zeroed on the device
+        pages, sizes = _ints([g.num_pages for g in groups]), _ints([g.page_size for g in groups])
+        windows = _ints([-1 if g.window is None else g.window for g in groups])
+        self._h = self._lib.gbh_cache_new(len(groups), pages.ctypes.data, sizes.ctypes.data, windows.ctypes.data,
+                                          max_requests, int(share_prefixes), int(has_state))
+        if not self._h:
+            raise ValueError(self._lib.gbh_last_error().decode())
+        # Prefix sharing is only sound when what a page holds is a pure function of the token prefix
+        # for every mixer: the library switches it off with windows (pages vanish) or per-request state.
+        self.share_prefixes = bool(self._lib.gbh_cache_shares_prefixes(self._h))
+        self._ids: Dict[object, int] = {}     # request id -> the 64-bit name the library knows it by
+        self._next = 1
+        self._scratch = np.empty(3 * max(len(groups), 1) + 2, dtype=np.int32)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h and self._lib is not None:
+            self._lib.gbh_cache_delete(h)
+
+    def _raise(self, code: int, rid=None):
+        msg = self._lib.gbh_last_error().decode()
+        if code == 1:
+            raise OutOfPages(msg)
+        if code == 3:
+            raise KeyError(rid)
+        raise ValueError(f"request {rid!r}: {msg}" if rid is not None else msg)
+
+    def _id(self, rid) -> int:
+        try:
+            return self._ids[rid]
+        except KeyError:
+            raise KeyError(rid) from None
+
+    def native_id(self, rid) -> int:
+        """The name under which the library knows the request (for ``fill_step``)."""
+        return self._id(rid)
 
     # ---------------------------------------------------------------------------------- queries
     def has(self, rid) -> bool:
-        return rid in self.requests
+        return rid in self._ids
 
     def length(self, rid) -> int:
-        return self.requests[rid].length
+        return self._lib.gbh_cache_length(self._h, self._id(rid))
 
     def slot_of(self, rid) -> int:
-        return self.requests[rid].slot
+        return self._lib.gbh_cache_slot(self._h, self._id(rid))
+
+    def request_ids(self) -> List[object]:
+        return list(self._ids)
 
     def table(self, group: int, rid) -> List[int]:
-        return self.groups[group].tables[rid]
+        i = self._id(rid)
+        n = self._lib.gbh_cache_table(self._h, group, i, None, 0)
+        out = np.empty(max(n, 1), dtype=np.int32)
+        self._lib.gbh_cache_table(self._h, group, i, out.ctypes.data, n)
+        return out[:n].tolist()
+
+    def table_len(self, group: int, rid) -> int:
+        return self._lib.gbh_cache_table(self._h, group, self._id(rid), None, 0)
+
+    def tokens(self, rid) -> List[int]:
+        i = self._id(rid)
+        n = self._lib.gbh_cache_tokens(self._h, i, None, 0)
+        out = np.empty(max(n, 1), dtype=np.int32)
+        self._lib.gbh_cache_tokens(self._h, i, out.ctypes.data, n)
+        return out[:n].tolist()
 
     def free_pages(self, group: int = 0) -> int:
-        return self.groups[group].free_pages()
+        return self._lib.gbh_cache_free_pages(self._h, group)
 
     def used_pages(self, group: int = 0) -> int:
-        g = self.groups[group]
-        return g.spec.num_pages - g.free_pages()
+        return self.groups[group].spec.num_pages - self.free_pages(group)
 
     def num_pages(self, group: int = 0) -> int:
         return self.groups[group].spec.num_pages
 
     def ref_count(self, group: int, page: int) -> int:
-        return self.groups[group].refs[page]
+        return self._lib.gbh_cache_ref_count(self._h, group, page)
+
+    def page_hash(self, group: int, page: int) -> Optional[int]:
+        """The chained hash under which a full page can be found again, or None."""
+        pages = self.groups[group].spec.num_pages
+        own = np.empty(pages, dtype=np.uint64)
+        self._lib.gbh_cache_hashes(self._h, group, None, None, 0, own.ctypes.data)
+        return int(own[page]) if self._pool(group, 3)[page] else None
 
     def slot(self, group: int, rid, pos: int) -> int:
         """Row of (request, position) in a cache layer of the group (kv.rs:199-201)."""
-        g = self.groups[group]
-        page = g.tables[rid][pos // g.page_size]
+        ps = self.groups[group].page_size
+        page = self.table(group, rid)[pos // ps]
         assert page >= 0, "position lies on a page that was given back"
-        return page * g.page_size + pos % g.page_size
+        return page * ps + pos % ps
+
+    def _slots(self, which: int, drain: bool) -> List[int]:
+        out = np.empty(max(self.max_requests, 1), dtype=np.int32)
+        n = self._lib.gbh_cache_slots(self._h, which, int(drain), out.ctypes.data, out.size)
+        return out[:n].tolist()
+
+    @property
+    def free_slots(self) -> List[int]:
+        return self._slots(0, False)
+
+    @property
+    def fresh_slots(self) -> List[int]:
+        return self._slots(1, False)
 
     def drain_fresh_slots(self) -> List[int]:
-        out, self.fresh_slots = self.fresh_slots, []
-        return out
+        return self._slots(1, True)
 
     def pages_needed(self, n_tokens: int, group: int = 0) -> int:
         return -(-n_tokens // self.groups[group].page_size)
@@ -186,169 +237,122 @@ class CacheManager:
         """Start a request. With prefix sharing, whole leading pages whose token prefix is already
         cached are shared; never the page that holds the last prompt token, which must still run
         to give logits (kv.rs:135-157). Returns the number of tokens already present."""
-        if rid in self.requests:
+        if rid in self._ids:
             raise ValueError(f"request {rid!r} exists")
-        if not self.free_slots:
-            raise OutOfPages("no free state slot")
-        req = _Request(tokens=list(int(t) for t in prompt))
-        req.slot = self.free_slots.pop()
-        self.fresh_slots.append(req.slot)
-        reused_pages = 0
-        if self.share_prefixes and self.groups:
-            ps = self.groups[0].page_size
-            if all(g.page_size == ps for g in self.groups):
-                found: List[List[int]] = []
-                h = 0
-                for i in range(len(req.tokens) // ps):
-                    if (i + 1) * ps >= len(req.tokens):
-                        break
-                    h = chain_hash(h, req.tokens[i * ps:(i + 1) * ps])
-                    pages = [g.by_hash.get(h) for g in self.groups]
-                    if any(p is None for p in pages):
-                        break
-                    found.append(pages)
-                reused_pages = len(found)
-                for g in self.groups:
-                    g.tables[rid] = []
-                for pages in found:
-                    for g, p in zip(self.groups, pages):
-                        g.retain(p)
-                        g.tables[rid].append(p)
-                req.length = reused_pages * ps
-        for g in self.groups:
-            g.tables.setdefault(rid, [])
-        self.requests[rid] = req
-        return req.length
+        toks = _ints(prompt)
+        present = ctypes.c_int(0)
+        i = self._next
+        code = self._lib.gbh_cache_add(self._h, i, toks.ctypes.data, toks.size, ctypes.byref(present))
+        if code:
+            self._raise(code, rid)
+        self._next += 1
+        self._ids[rid] = i
+        return present.value
 
     def reserve(self, rid, n: int) -> List[Tuple[int, int, int]]:
         """Make room to write positions length .. length+n-1 in every group, all or nothing.
         Returns copy-on-write work as (group, source page, destination page) triples that the
         caller must carry out on the device before the step (kv.rs:161-196)."""
-        req = self.requests[rid]
-        plans = []
-        for g in self.groups:
-            new, cow = g.plan(g.tables[rid], req.length, n)
-            if new + (1 if cow else 0) > g.free_pages():
-                raise OutOfPages()
-            plans.append((new, cow))
-        copies = []
-        for gi, (g, (new, cow)) in enumerate(zip(self.groups, plans)):
-            table = g.tables[rid]
-            if cow:
-                i = req.length // g.page_size
-                old = table[i]
-                fresh = g.alloc()
-                copies.append((gi, old, fresh))
-                g.release(old)
-                table[i] = fresh
-            for _ in range(new):
-                table.append(g.alloc())
-        return copies
+        s = self._scratch
+        code = self._lib.gbh_cache_reserve(self._h, self._id(rid), int(n), s.ctypes.data, s[-1:].ctypes.data)
+        if code:
+            self._raise(code, rid)
+        k = int(s[-1])
+        return [(int(s[3 * j]), int(s[3 * j + 1]), int(s[3 * j + 2])) for j in range(k)] if k else []
 
     def commit(self, rid, tokens: Sequence[int]) -> None:
         """Mark ``len(tokens)`` more positions as written; hash pages that became full
         (kv.rs:205-233); give back pages that a window has passed."""
-        req = self.requests[rid]
-        start = req.length
-        req.length += len(tokens)
-        if len(req.tokens) < req.length:
-            del req.tokens[start:]
-            req.tokens.extend(int(t) for t in tokens)
-        for g in self.groups:
-            table = g.tables[rid]
-            if g.share:
-                for bi in range(start // g.page_size, req.length // g.page_size):
-                    p = table[bi]
-                    if g.page_hash[p] is not None:
-                        continue
-                    h = 0
-                    for c in range(bi + 1):
-                        h = chain_hash(h, req.tokens[c * g.page_size:(c + 1) * g.page_size])
-                    if h not in g.by_hash:
-                        g.by_hash[h] = p
-                        g.page_hash[p] = h
-            if g.window is not None:
-                for bi in range(min(g.first_live_page(req.length), len(table))):
-                    if table[bi] >= 0:
-                        g.release(table[bi])
-                        table[bi] = -1
+        toks = _ints(tokens)
+        code = self._lib.gbh_cache_commit(self._h, self._id(rid), toks.ctypes.data, toks.size)
+        if code:
+            self._raise(code, rid)
 
     def truncate(self, rid, length: int) -> None:
         """Forget everything after the first ``length`` tokens (kv.rs:237-257). Not available
         once a window has given pages back behind ``length``."""
-        req = self.requests[rid]
-        if length > req.length:
-            raise ValueError("cannot truncate to more than is written")
-        for g in self.groups:
-            if g.window is not None and any(p < 0 for p in g.tables[rid][g.first_live_page(length):]):
-                raise ValueError("a windowed group has already released pages that the shorter request would need")
-        req.length = length
-        del req.tokens[length:]
-        for g in self.groups:
-            table = g.tables[rid]
-            keep = -(-length // g.page_size)
-            dropped = table[keep:]
-            del table[keep:]
-            if length % g.page_size:
-                p = table[length // g.page_size]
-                if p >= 0 and g.refs[p] == 1 and g.page_hash[p] is not None:
-                    g.by_hash.pop(g.page_hash[p], None)
-                    g.page_hash[p] = None
-            for p in dropped:
-                if p >= 0:
-                    g.release(p)
+        code = self._lib.gbh_cache_truncate(self._h, self._id(rid), int(length))
+        if code:
+            self._raise(code, rid)
 
     def fork(self, parent, child) -> Tuple[int, int]:
         """New request sharing every page of ``parent`` (kv.rs:260-266). Its state slot is a
         copy, not a share: returns (parent slot, child slot) for the device copy."""
-        if child in self.requests:
+        if child in self._ids:
             raise ValueError(f"request {child!r} exists")
-        if not self.free_slots:
-            raise OutOfPages("no free state slot")
-        src = self.requests[parent]
-        req = _Request(length=src.length, tokens=list(src.tokens), slot=self.free_slots.pop())
-        for g in self.groups:
-            table = list(g.tables[parent])
-            for p in table:
-                if p >= 0:
-                    g.retain(p)
-            g.tables[child] = table
-        self.requests[child] = req
-        return src.slot, req.slot
+        s = self._scratch
+        i = self._next
+        code = self._lib.gbh_cache_fork(self._h, self._id(parent), i, s.ctypes.data)
+        if code:
+            self._raise(code, child)
+        self._next += 1
+        self._ids[child] = i
+        return int(s[0]), int(s[1])
 
     def free_request(self, rid) -> None:
         """Give back everything the request holds (kv.rs:268-274). Unknown ids are ignored."""
-        req = self.requests.pop(rid, None)
-        if req is None:
-            return
-        for g in self.groups:
-            for p in g.tables.pop(rid):
-                if p >= 0:
-                    g.release(p)
-        self.free_slots.append(req.slot)
-        if req.slot in self.fresh_slots:
-            self.fresh_slots.remove(req.slot)
+        i = self._ids.pop(rid, None)
+        if i is not None:
+            self._lib.gbh_cache_free(self._h, i)
+
+    # ------------------------------------------------------------------------------ a step's metadata
+    def fill_step(self, rids, tok_count: np.ndarray, tokens: np.ndarray, want_count: np.ndarray, want: np.ndarray,
+                  n: int, S: int, n_want: int, max_pages: int, offsets: np.ndarray, host: np.ndarray,
+                  temperature: Optional[np.ndarray], uniform: Optional[np.ndarray]):
+        """Write the int32 metadata block of a step into ``host`` (see ``gbh_fill_step``); returns
+        ((start position, slot) per entry as an int32 array [E, 2], longest context)."""
+        E = len(rids)
+        ids = np.fromiter((self._ids[r] for r in rids), dtype=np.int64, count=E)
+        info = np.empty((max(E, 1), 2), dtype=np.int32)
+        longest = ctypes.c_int(0)
+        k = 0 if temperature is None else int(temperature.size)
+        code = self._lib.gbh_fill_step(
+            self._h, E, ids.ctypes.data, tok_count.ctypes.data, tokens.ctypes.data, want_count.ctypes.data,
+            want.ctypes.data, n, S, n_want, max_pages, offsets.ctypes.data, host.size, host.ctypes.data,
+            temperature.ctypes.data if k else None, uniform.ctypes.data if k else None, k, info.ctypes.data,
+            ctypes.byref(longest))
+        if code:
+            self._raise(code)
+        return info[:E], longest.value
 
     # ------------------------------------------------------------------------------ invariants
+    def _pool(self, group: int, which: int) -> List[int]:
+        out = np.empty(self.groups[group].spec.num_pages, dtype=np.int32)
+        n = self._lib.gbh_cache_pool(self._h, group, which, out.ctypes.data, out.size)
+        return out[:n].tolist()
+
     def check_invariants(self) -> None:
         """Every page is referenced exactly as often as block tables name it; pages nobody names
-        are exactly the free and the cached ones, each once; slots likewise (kv.rs:278-288)."""
+        are exactly the free and the cached ones, each once; slots likewise (kv.rs:278-288). Checked
+        here, outside the library, on the state it reports."""
+        names = set(self._ids.values())
+        ids = np.empty(max(len(names), 1) + 8, dtype=np.int64)
+        n = self._lib.gbh_cache_ids(self._h, -1, ids.ctypes.data, ids.size)
+        assert set(ids[:n].tolist()) == names, "the library's requests and the names given out differ"
         for gi, g in enumerate(self.groups):
-            want = [0] * g.spec.num_pages
-            for table in g.tables.values():
-                for p in table:
+            pages = g.spec.num_pages
+            refs, free, cached = self._pool(gi, 0), self._pool(gi, 1), self._pool(gi, 2)
+            hashed = self._pool(gi, 3)
+            want = [0] * pages
+            for rid in self._ids:
+                for p in self.table(gi, rid):
                     if p >= 0:
                         want[p] += 1
-            assert want == g.refs, f"group {gi}: page reference counts drifted"
-            idle = [p for p, r in enumerate(g.refs) if r == 0]
-            pool = g.free + g.cached
+            assert want == refs, f"group {gi}: page reference counts drifted"
+            idle = [p for p, r in enumerate(refs) if r == 0]
+            pool = free + cached
             assert len(pool) == len(set(pool)), f"group {gi}: a page is on the free lists twice"
             assert sorted(pool) == idle, f"group {gi}: free lists drifted from the reference counts"
-            assert all(g.page_hash[p] is not None for p in g.cached), f"group {gi}: cached page without a hash"
-            assert all(g.page_hash[p] is None for p in g.free), f"group {gi}: free page still hashed"
-            for h, p in g.by_hash.items():
-                assert g.page_hash[p] == h, f"group {gi}: hash index drifted"
-            assert set(g.tables) == set(self.requests), f"group {gi}: tables and requests differ"
-        held = sorted(r.slot for r in self.requests.values())
+            assert all(hashed[p] for p in cached), f"group {gi}: cached page without a hash"
+            assert not any(hashed[p] for p in free), f"group {gi}: free page still hashed"
+            hs, ps = np.empty(pages, dtype=np.uint64), np.empty(pages, dtype=np.int32)
+            own = np.empty(pages, dtype=np.uint64)
+            k = self._lib.gbh_cache_hashes(self._h, gi, hs.ctypes.data, ps.ctypes.data, pages, own.ctypes.data)
+            assert k <= pages and k == sum(hashed), f"group {gi}: hash index drifted"
+            for h, p in zip(hs[:k].tolist(), ps[:k].tolist()):
+                assert hashed[p] and int(own[p]) == h, f"group {gi}: hash index drifted"
+            n = self._lib.gbh_cache_ids(self._h, gi, ids.ctypes.data, ids.size)
+            assert set(ids[:n].tolist()) == names, f"group {gi}: tables and requests differ"
+        held = sorted(self.slot_of(r) for r in self._ids)
         assert len(held) == len(set(held)), "a state slot is held twice"
         assert sorted(held + self.free_slots) == list(range(self.max_requests)), "state slots drifted"

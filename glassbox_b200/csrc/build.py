@@ -120,5 +120,65 @@ def ensure_built(force: bool = False, verbose_ptxas: bool = False) -> str:
     return lib
 
 
+HOST_DIR = os.path.join(HERE, "host")
+HOST_LIB_NAME = "libglassbox_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+
+
+def host_library_path() -> str:
+    return os.path.join(BUILD_DIR, HOST_LIB_NAME)
+
+
+def ensure_host_built(force: bool = False) -> str:
+    """Build the C++ host library (``csrc/host/*.cpp``: cache bookkeeping, step layout) with the C++
+    compiler; it has no CUDA in it and is needed on machines without a GPU too."""
+    lib = host_library_path()
+    stamp_file = os.path.join(BUILD_DIR, "host_stamp")
+    srcs = sorted(f for f in os.listdir(HOST_DIR) if f.endswith((".cpp", ".h")))
+    h = hashlib.sha256(" ".join(HOST_FLAGS).encode())
+    for f in srcs:
+        h.update(f.encode())
+        with open(os.path.join(HOST_DIR, f), "rb") as fh:
+            h.update(fh.read())
+    want = h.hexdigest()
+
+    def fresh() -> bool:
+        try:
+            with open(stamp_file) as f:
+                return f.read().strip() == want and os.path.exists(lib)
+        except OSError:
+            return False
+
+    if not force and fresh():
+        return lib
+    try:
+        os.makedirs(BUILD_DIR, exist_ok=True)
+    except OSError as e:
+        raise BuildError(f"cannot create {BUILD_DIR}: {e}") from None
+    with open(os.path.join(BUILD_DIR, "host_lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and fresh():
+                return lib
+            cxx = next((c for c in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++"))
+                        if c), None)
+            if cxx is None:
+                raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++); the host library cannot be built")
+            t0 = time.time()
+            tmp = lib + f".{os.getpid()}.tmp"
+            cmd = [cxx, *HOST_FLAGS, "-o", tmp, *[os.path.join(HOST_DIR, f) for f in srcs if f.endswith(".cpp")]]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise BuildError(f"compiling {HOST_LIB_NAME} failed:\n{proc.stdout}\n{proc.stderr}")
+            os.replace(tmp, lib)
+            with open(stamp_file, "w") as f:
+                f.write(want)
+            _log(f"built {HOST_LIB_NAME} in {time.time() - t0:.1f}s")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return lib
+
+
 if __name__ == "__main__":
+    print(ensure_host_built(force="--force" in sys.argv))
     print(ensure_built(force="--force" in sys.argv, verbose_ptxas="-v" in sys.argv))

@@ -94,6 +94,7 @@ class Engine:
         self.use_graphs = bool(use_graphs)
         self.max_graph_batch = 64
         self._graphs: Dict[tuple, dict] = {}
+        self._layouts: Dict[tuple, dict] = {}
         self._seen: Dict[tuple, int] = {}
         self.max_graphs = 48
         self.graph_replays = 0
@@ -151,6 +152,12 @@ class Engine:
         self.h2d_bytes_last = n * 4
 
     def _layout(self, n: int, S: int, n_want: int, max_pages: int):
+        key = (n, S, n_want, max_pages)
+        off = self._layouts.get(key)
+        if off is not None:
+            return off
+        if len(self._layouts) > 4096:
+            self._layouts.clear()
         off, cur = {}, 0
         for name, size in (("tokens", n), ("positions", n), ("row_seq", n), ("want", n_want),
                            ("seq_first_row", S + 1), ("seq_start_pos", S), ("seq_slots", S),
@@ -163,95 +170,34 @@ class Engine:
             off[f"tables{g}"] = cur
             cur += S * max_pages
         off["_size"] = cur
+        names = ["tokens", "positions", "row_seq", "want", "seq_first_row", "seq_start_pos", "seq_slots", "temperature",
+                 "uniform"] + [f"{kind}{g}" for g in range(len(self.cache.groups)) for kind in ("slots", "tables")]
+        off["_array"] = np.array([off[k] for k in names], dtype=np.int64)   # the order the host library reads
+        self._layouts[key] = off
         return off
 
-    def _fill(self, entries, off, n, S, max_pages, sampling=None) -> np.ndarray:
-        """Host copy of the metadata block. Rows and sequences beyond the entries (a batch padded to
-        a fixed shape) get position -1, slot -1 and empty tables: every kernel skips them."""
-        ps = self.page_size
-        n_groups = len(self.cache.groups)
-        host = np.zeros(off["_size"], dtype=np.int32)
-        host[off["positions"]:off["positions"] + n] = -1
-        for g in range(n_groups):
-            host[off[f"slots{g}"]:off[f"slots{g}"] + n] = -1
-            host[off[f"tables{g}"]:off[f"tables{g}"] + S * max_pages] = -1
-        seqs: List[SeqInfo] = []
-        row, wi, max_ctx = 0, off["want"], 0
-        for si, e in enumerate(entries):
-            k = len(e.tokens)
-            start = self.cache.length(e.request)
-            seqs.append(SeqInfo(request=e.request, slot=self.cache.slot_of(e.request), start_pos=start, n_rows=k,
-                                first_row=row))
-            host[off["tokens"] + row:off["tokens"] + row + k] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
-            pos = np.arange(start, start + k, dtype=np.int32)
-            host[off["positions"] + row:off["positions"] + row + k] = pos
-            host[off["row_seq"] + row:off["row_seq"] + row + k] = si
-            for w in e.want:
-                host[wi] = row + w
-                wi += 1
-            host[off["seq_first_row"] + si] = row
-            host[off["seq_start_pos"] + si] = start
-            host[off["seq_slots"] + si] = seqs[-1].slot
-            for g in range(n_groups):
-                table = np.asarray(self.cache.table(g, e.request), dtype=np.int32)
-                t0 = off[f"tables{g}"] + si * max_pages
-                host[t0:t0 + table.size] = table
-                host[off[f"slots{g}"] + row:off[f"slots{g}"] + row + k] = table[pos // ps] * ps + pos % ps
-            row += k
-            max_ctx = max(max_ctx, start + k)
-        host[off["seq_first_row"] + len(entries):off["seq_first_row"] + S + 1] = row
-        for si in range(len(entries), S):            # padding sequences: one padding row each
-            host[off["row_seq"] + row] = si
-            host[off["seq_first_row"] + si] = row
-            host[wi] = row
-            wi += 1
-            row += 1
-        host[off["seq_first_row"] + S] = row
+    def _fill(self, entries, off, n, S, n_want, max_pages, sampling=None) -> np.ndarray:
+        """Host copy of the metadata block, written by the C++ host library from the cache manager's
+        tables. Rows and sequences beyond the entries (a batch padded to a fixed shape) get position
+        -1, slot -1 and empty tables: every kernel skips them."""
+        E = len(entries)
+        tok_count = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=E)
+        want_count = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=E)
+        if int(tok_count.sum()) == E:
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=E)
+        else:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]).astype(np.int32)
+        want = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(want_count.sum()))
+        host = np.empty(off["_size"], dtype=np.int32)
+        temps = unif = None
         if sampling is not None:
-            temps, unif = sampling
-            k = len(temps)
-            host[off["temperature"]:off["temperature"] + k] = np.asarray(temps, dtype=np.float32).view(np.int32)
-            host[off["uniform"]:off["uniform"] + k] = np.asarray(unif, dtype=np.float32).view(np.int32)
-        self._seqs, self._max_ctx = seqs, max_ctx
-        return host
-
-    def _fill_decode(self, entries, off, Sb: int, Pb: int, sampling) -> np.ndarray:
-        """``_fill`` for a step of single decoded tokens padded to ``Sb`` rows: the same block, built
-        with whole-array operations (this runs once per generated token of every request)."""
-        ps = self.page_size
-        cache = self.cache
-        S = len(entries)
-        host = np.zeros(off["_size"], dtype=np.int32)
-        lengths = np.fromiter((cache.requests[e.request].length for e in entries), dtype=np.int32, count=S)
-        host[off["tokens"]:off["tokens"] + S] = [e.tokens[0] for e in entries]
-        pos = host[off["positions"]:off["positions"] + Sb]
-        pos[:] = -1
-        pos[:S] = lengths
-        ar = np.arange(Sb + 1, dtype=np.int32)
-        host[off["row_seq"]:off["row_seq"] + Sb] = ar[:Sb]
-        host[off["want"]:off["want"] + Sb] = ar[:Sb]
-        host[off["seq_first_row"]:off["seq_first_row"] + Sb + 1] = ar
-        host[off["seq_start_pos"]:off["seq_start_pos"] + S] = lengths
-        host[off["seq_slots"]:off["seq_slots"] + S] = [cache.requests[e.request].slot for e in entries]
-        page_index = lengths // ps
-        in_page = lengths % ps
-        for g, group in enumerate(cache.groups):
-            tables = host[off[f"tables{g}"]:off[f"tables{g}"] + Sb * Pb].reshape(Sb, Pb)
-            tables[:] = -1
-            slots = host[off[f"slots{g}"]:off[f"slots{g}"] + Sb]
-            slots[:] = -1
-            for i, e in enumerate(entries):
-                t = group.tables[e.request]
-                tables[i, :len(t)] = t
-            slots[:S] = tables[ar[:S], page_index] * ps + in_page
-        if sampling is not None:
-            temps, unif = sampling
-            k = len(temps)
-            host[off["temperature"]:off["temperature"] + k] = np.asarray(temps, dtype=np.float32).view(np.int32)
-            host[off["uniform"]:off["uniform"] + k] = np.asarray(unif, dtype=np.float32).view(np.int32)
-        self._seqs = [SeqInfo(request=e.request, slot=int(host[off["seq_slots"] + i]), start_pos=int(lengths[i]),
-                              n_rows=1, first_row=i) for i, e in enumerate(entries)]
-        self._max_ctx = int(lengths.max()) + 1 if S else 0
+            temps = np.ascontiguousarray(sampling[0], dtype=np.float32)
+            unif = np.ascontiguousarray(sampling[1], dtype=np.float32)
+        info, self._max_ctx = self.cache.fill_step([e.request for e in entries], tok_count, tokens, want_count, want,
+                                                   n, S, n_want, max_pages, off["_array"], host, temps, unif)
+        first = np.concatenate(([0], np.cumsum(tok_count)[:-1])) if E else ()
+        self._seqs = [SeqInfo(request=e.request, slot=int(info[i, 1]), start_pos=int(info[i, 0]), n_rows=int(tok_count[i]),
+                              first_row=int(first[i])) for i, e in enumerate(entries)]
         return host
 
     def _bind(self, ctx: StepContext, dev: torch.Tensor, off, n, S, n_want, max_pages) -> None:
@@ -316,7 +262,7 @@ class Engine:
         self.device_cache.zero_slots(self.cache.drain_fresh_slots())
         n_groups = len(self.cache.groups)
         S = len(entries)
-        max_pages = max(max(len(self.cache.table(g, e.request)) for e in entries) for g in range(n_groups)) \
+        max_pages = max(max(self.cache.table_len(g, e.request) for e in entries) for g in range(n_groups)) \
             if n_groups else 1
         n_want = sum(len(e.want) for e in entries)
         decode_only = self.use_graphs and n == S and n_want == S and S <= self.max_graph_batch \
@@ -339,12 +285,12 @@ class Engine:
                         self._seen.clear()
                     self._seen[key] = self._seen.get(key, 0) + 1
                     if self._seen[key] >= 2 and len(self._graphs) < self.max_graphs:
-                        host = self._fill(entries, off, n, S, Pb, sampling)
+                        host = self._fill(entries, off, n, S, n_want, Pb, sampling)
                         g = self._capture(key, off, host, n, S, n_want, Pb, max_rows, decode_only=(n == S))
                         self.sampled = g["sampled"][:n_want] if sampling is not None else None
                         logits = g["logits"][:n_want]       # the warm-up run of the capture computed this step
                 else:
-                    host = self._fill(entries, off, n, S, Pb, sampling)
+                    host = self._fill(entries, off, n, S, n_want, Pb, sampling)
                     self._stage_copy(host, g["meta"])
                     g["graph"].replay()
                     kernels.launch_count += g["nodes"]
@@ -353,7 +299,7 @@ class Engine:
                     logits = g["logits"][:n_want]
             if logits is None:
                 off = self._layout(n, S, n_want, max_pages)
-                host = self._fill(entries, off, n, S, max_pages, sampling)
+                host = self._fill(entries, off, n, S, n_want, max_pages, sampling)
                 if off["_size"] > self._meta_dev.numel():
                     self._meta_dev = torch.empty(1 << int(off["_size"] - 1).bit_length(), dtype=torch.int32,
                                                  device=self.device)
@@ -380,17 +326,12 @@ class Engine:
         off = self._layout(Sb, Sb, Sb, Pb)
         if sampling is None:
             sampling = ([0.0] * S, [0.0] * S)
-        host = self._fill_decode(entries, off, Sb, Pb, sampling)
+        host = self._fill(entries, off, Sb, Sb, Sb, Pb, sampling)
         g = self._graphs.get(key)
         if g is None:
-            blank = np.zeros(off["_size"], dtype=np.int32)      # an all-padding batch: every row skipped
-            blank[off["positions"]:off["positions"] + Sb] = -1
-            for gi in range(len(self.cache.groups)):
-                blank[off[f"slots{gi}"]:off[f"slots{gi}"] + Sb] = -1
-                blank[off[f"tables{gi}"]:off[f"tables{gi}"] + Sb * Pb] = -1
-            blank[off["row_seq"]:off["row_seq"] + Sb] = np.arange(Sb)
-            blank[off["want"]:off["want"] + Sb] = np.arange(Sb)
-            blank[off["seq_first_row"]:off["seq_first_row"] + Sb + 1] = np.arange(Sb + 1)
+            seqs, longest = self._seqs, self._max_ctx
+            blank = self._fill([], off, Sb, Sb, Sb, Pb)          # an all-padding batch: every row skipped
+            self._seqs, self._max_ctx = seqs, longest
             g = self._capture(key, off, blank, Sb, Sb, Sb, Pb, 1, decode_only=True)
         self._stage_copy(host, g["meta"])
         g["graph"].replay()

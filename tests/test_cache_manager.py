@@ -26,6 +26,28 @@ def test_chain_hash_is_fnv1a_over_le_bytes():
     assert chain_hash(chain_hash(0, [1, 2]), [3]) != chain_hash(0, [1, 2, 3])
 
 
+def plain_fnv(prev, tokens):
+    h = (prev ^ 0xCBF29CE484222325) & (2 ** 64 - 1)
+    for t in tokens:
+        for b in int(t).to_bytes(4, "little"):
+            h = ((h ^ b) * 0x100000001B3) & (2 ** 64 - 1)
+    return h
+
+
+def test_full_pages_are_indexed_under_the_chain_of_their_prefix():
+    m = mgr(pages=6, share=True)
+    toks = list(range(100, 100 + 40))
+    m.add_request("a", toks)
+    feed(m, "a", toks[:35])                      # two full pages and a partial one, in one commit
+    t = m.table(0, "a")
+    h0 = plain_fnv(0, toks[:16])
+    assert m.page_hash(0, t[0]) == h0 and m.page_hash(0, t[1]) == plain_fnv(h0, toks[16:32])
+    assert m.page_hash(0, t[2]) is None
+    feed(m, "a", toks[35:40])                    # the third page is still not full
+    assert m.page_hash(0, t[2]) is None
+    m.check_invariants()
+
+
 def test_pages_come_in_order_and_go_back():
     m = mgr(pages=4, share=False)
     m.add_request("a")
