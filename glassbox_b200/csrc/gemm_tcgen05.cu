@@ -20,93 +20,12 @@
 // Every wait is bounded: a wait that exceeds its limit sets GB_STATUS_WAIT_TIMEOUT in the status
 // word and the block winds down (waits, again bounded, for its own TMA copies, frees its TMEM,
 // returns) instead of hanging the GPU. TMA loads use no multicast.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;        // 64 bfloat16 = 128 bytes = one swizzle row
-constexpr long long TC_WAIT_CYCLES = 400ll * 1000 * 1000;   // about 0.2 s: far beyond any real wait
 
 enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2 };
-
-// ------------------------------------------------------------------------------------ PTX helpers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait. Returns false (and records it) if the limit passes or another thread gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (*abort_flag) return false;
-        if (clock64() - t0 > TC_WAIT_CYCLES) {
-            *abort_flag = 1;
-            atomicOr(status, GB_STATUS_WAIT_TIMEOUT);
-            return false;
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, K-major operand in 128-byte-swizzled rows: 8-row groups are 1024
-// bytes apart (stride byte offset); the leading byte offset is unused for this layout (set to 1).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                               // leading byte offset (unused)
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
-    d |= (uint64_t)1 << 46;                               // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: bfloat16 A and B (both K-major), float32 accumulator, M x N tile.
-__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo_bits), __uint_as_float(hi_bits));
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 constexpr int TC_MAX_STAGES = 8;
 
@@ -120,10 +39,6 @@ struct __align__(8) TcShared {
     int issued;      // k-blocks whose TMA loads were issued
     int consumed;    // k-blocks whose full barrier the MMA thread has passed
 };
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 template <int BN, bool GATED> struct TcGeometry {
     static constexpr int BNO = GATED ? BN / 2 : BN;                 // output columns per tile
@@ -246,7 +161,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BNO;
             const int acc = tcount & 1;
             if (kblocks > 0) {
-                if (!mbar_wait(&sh.tfull[acc], (tcount >> 1) & 1, abort_flag, status)) { ok = false; break; }
+                if (!mbar_wait_warp(&sh.tfull[acc], (tcount >> 1) & 1, abort_flag, status)) { ok = false; break; }
                 tc_fence_after();
             }
             const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
@@ -342,35 +257,9 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------------- host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 // [rows, K] bfloat16, K contiguous, `ld` elements between rows; boxes of box_rows x 64, 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    GB_REQUIRE(fn != nullptr, "gb_gemm_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    GB_REQUIRE(r == CUDA_SUCCESS, "gb_gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return 0;
+    return tc_make_map_2d(map, base, rows, K, ld, box_rows, TC_BK, "gb_gemm_tcgen05");
 }
 
 template <int BN, bool GATED>

@@ -54,6 +54,8 @@ _SIGNATURES = {
     "gb_kv_prefetch": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _LL, _LL, _I, _I, _P],
     "gb_attention_prefill": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_attention_prefill_supported": [_I, _I, _I, _I],
+    "gb_attention_prefill_tc": [_P, _LL, _I, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_attention_prefill_tc_supported": [_I, _I, _I, _I],
     "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P],
     "gb_gemm_tcgen05_supported": [_P, _P, _I, _I, _I, _LL, _LL],
     "gb_gemm_tcgen05_gated": [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P],
@@ -427,6 +429,31 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
 
 def attention_prefill_supported(dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:
     return dtype == torch.bfloat16 and bool(lib().gb_attention_prefill_supported(nh, nkv, hd, page_size))
+
+
+def attention_prefill_tc_supported(q: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, hd: int, page_size: int) -> bool:
+    """Whether the tcgen05 flash-attention kernel takes these operands (bfloat16, head size 64, rows
+    aligned for TMA)."""
+    return (q.dtype == torch.bfloat16 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and out.data_ptr() % 16 == 0 and bool(lib().gb_attention_prefill_tc_supported(nh, nkv, hd, page_size)))
+
+
+def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                         block_tables: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor,
+                         max_rows_per_seq: int, nh: int, nkv: int, hd: int, page_size: int, scale: float,
+                         window: Optional[int], status: torch.Tensor) -> None:
+    """bfloat16 flash attention on tcgen05 (TMA loads from the paged cache, S and PV in tensor memory) for
+    batches whose requests bring runs of consecutive rows; arguments as ``attention_prefill``."""
+    _cuda(q, out, kcache, vcache, block_tables, seq_first_row, seq_start_pos, status)
+    assert q.dtype == out.dtype == kcache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[1:] == (nkv, page_size, hd)
+    S = block_tables.shape[0]
+    assert seq_first_row.numel() == S + 1 and seq_start_pos.numel() == S
+    _call("gb_attention_prefill_tc", _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache),
+          _ptr(vcache), _ptr(block_tables), block_tables.shape[1], _ptr(seq_first_row), _ptr(seq_start_pos), S,
+          int(max_rows_per_seq), nh, nkv, hd, page_size, kcache.shape[0], float(scale), int(window or 0), _ptr(status),
+          _stream())
 
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,

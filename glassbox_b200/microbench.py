@@ -126,7 +126,7 @@ def bench_attention_decode(batches) -> None:
 
 def bench_attention_prefill() -> None:
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for nh, nkv, hd, t_len in [(9, 3, 64, 2048), (15, 5, 64, 2048), (32, 32, 64, 2048)]:
+    for nh, nkv, hd, t_len in [(9, 3, 64, 2048), (15, 5, 64, 2048), (32, 32, 64, 2048), (32, 32, 64, 8192)]:
         ps = 16
         per = t_len // ps
         kc = torch.randn(per + 2, nkv, ps, hd, device=DEV).bfloat16()
@@ -136,10 +136,12 @@ def bench_attention_prefill() -> None:
         start = torch.zeros(1, dtype=torch.int32, device=DEV)
         q = torch.randn(t_len, nh * hd, device=DEV).bfloat16()
         o = torch.empty_like(q)
-        t = graph_time(lambda: kernels.attention_prefill(q, o, kc, vc, tables, first, start, t_len, nh, nkv, hd, ps,
-                                                         hd ** -0.5, None, status), reps=6)
         fl = 2.0 * t_len * t_len * nh * hd   # QK^T and PV over the causal half
-        print(f"attention_prefill heads {nh}/{nkv} x {hd}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        for name, fn in (("mma.sync", kernels.attention_prefill), ("tcgen05", kernels.attention_prefill_tc)):
+            t = graph_time(lambda: fn(q, o, kc, vc, tables, first, start, t_len, nh, nkv, hd, ps, hd ** -0.5, None, status),
+                           reps=6)
+            print(f"attention_prefill {name:8s} heads {nh}/{nkv} x {hd}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s",
+                  flush=True)
     kernels.check_status(status)
 
 

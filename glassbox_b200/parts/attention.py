@@ -109,6 +109,12 @@ class GqaAttention(Mixer):
                                      self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window,
                                      splits, part_acc, part_ml, counters, ctx.status)
             return
+        if not ctx.decode_only and kernels.attention_prefill_tc_supported(q, att, self.nh, self.nkv, self.hd,
+                                                                          cache.page_size):
+            kernels.attention_prefill_tc(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row,
+                                         ctx.seq_start_pos, ctx.max_rows_per_seq, self.nh, self.nkv, self.hd,
+                                         cache.page_size, self.spec.scale, self.spec.window, ctx.status)
+            return
         if not ctx.decode_only and kernels.attention_prefill_supported(q.dtype, self.nh, self.nkv, self.hd,
                                                                        cache.page_size):
             kernels.attention_prefill(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row,

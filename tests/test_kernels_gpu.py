@@ -502,6 +502,78 @@ PREFILL_CASES = [  # nh, nkv, hd, page_size, window, [(cached tokens, new rows),
 ]
 
 
+PREFILL_TC_CASES = [  # the tcgen05 kernel: 128-row query tiles over 128-key tiles, head size 64
+    (9, 3, 64, 16, None, [(0, 200), (0, 64), (0, 1), (0, 65)]),
+    (9, 3, 64, 16, None, [(100, 31), (640, 2), (63, 130), (1, 1)]),       # portions that continue a cache
+    (4, 4, 64, 32, 100, [(0, 300), (250, 77)]),
+    (3, 1, 64, 8, None, [(0, 700), (300, 513), (127, 129)]),              # many key tiles, every parity of the rings
+    (2, 2, 64, 128, 300, [(0, 1000), (990, 40)]),                         # a page is a whole key tile; a window over tiles
+    (5, 5, 64, 64, 5, [(0, 260), (1000, 7)]),
+]
+
+
+def _run_prefill(fn, case):
+    from glassbox_b200 import kernels  # noqa: F401
+    nh, nkv, hd, ps, window, seqs = case
+    dtype = torch.bfloat16
+    lens = [c + n for c, n in seqs]
+    k, v, tables, dense = make_cache(dtype, len(lens), lens, nkv, hd, ps, seed=4)
+    first, row_seq, positions = [0], [], []
+    for s_i, (c, n) in enumerate(seqs):
+        row_seq += [s_i] * n
+        positions += list(range(c, c + n))
+        first.append(first[-1] + n)
+    n = len(row_seq)
+    q = torch.randn(n, nh, hd).to(dtype)
+    wide = torch.zeros(n, nh * hd + 2 * nkv * hd, dtype=dtype)               # q sits inside a wider qkv buffer
+    wide[:, :nh * hd] = q.reshape(n, -1)
+    wide = wide.to(DEV)
+    out = torch.full((n, nh * hd), 7.0, device=DEV, dtype=dtype)
+    st = status()
+    fn(wide[:, :nh * hd], out, k, v, tables, torch.tensor(first, dtype=torch.int32, device=DEV),
+       torch.tensor([c for c, _ in seqs], dtype=torch.int32, device=DEV), max(nn for _, nn in seqs),
+       nh, nkv, hd, ps, hd ** -0.5, window, st)
+    ref = ref_attention(q, dense, row_seq, positions, nh, nkv, hd ** -0.5, window)
+    assert int(st) == 0
+    diff = (out.cpu().double().reshape(n, nh, hd) - ref).abs()
+    worst = int(diff.amax(dim=(1, 2)).argmax())
+    assert diff.max() <= tol(dtype, 2), f"row {worst} (sequence, position) = {row_seq[worst], positions[worst]}"
+
+
+@pytest.mark.parametrize("case", PREFILL_TC_CASES)
+def test_attention_prefill_tcgen05(case):
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps = case[:4]
+    probe = torch.empty(1, nh * hd, device=DEV, dtype=torch.bfloat16)
+    assert kernels.attention_prefill_tc_supported(probe, probe, nh, nkv, hd, ps)
+    _run_prefill(kernels.attention_prefill_tc, case)
+
+
+def test_attention_prefill_tcgen05_each_row_finds_its_own_far_key():
+    """As the test of the same name below, for the tcgen05 kernel: every query row matches exactly one key
+    somewhere before it, on every side of the 128-key tile and page edges."""
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps, dtype, L = 2, 1, 64, 16, torch.bfloat16, 530
+    k, v, tables, dense = make_cache(dtype, 1, [L], nkv, hd, ps, seed=8)
+    kk, vv = dense[0]
+    gen = torch.Generator().manual_seed(0)
+    targets = [[int(torch.randint(0, p + 1, (1,), generator=gen)) for _ in range(nh)] for p in range(L)]
+    q = torch.zeros(L, nh, hd)
+    for p in range(L):
+        for h in range(nh):
+            key = kk[0, targets[p][h]]
+            q[p, h] = (key / key.norm() ** 2 * 60.0 * 8.0).float()
+    q = q.to(dtype)
+    out = torch.empty(L, nh * hd, device=DEV, dtype=dtype)
+    st = status()
+    kernels.attention_prefill_tc(q.to(DEV).reshape(L, -1), out, k, v, tables, torch.tensor([0, L], dtype=torch.int32, device=DEV),
+                                 torch.zeros(1, dtype=torch.int32, device=DEV), L, nh, nkv, hd, ps, hd ** -0.5, None, st)
+    assert int(st) == 0
+    ref = ref_attention(q, dense, [0] * L, list(range(L)), nh, nkv, hd ** -0.5, None)
+    diff = (out.cpu().double().reshape(L, nh, hd) - ref).abs().amax(dim=(1, 2))
+    assert diff.max() <= tol(dtype, 2), f"position {int(diff.argmax())} (target {targets[int(diff.argmax())]})"
+
+
 @pytest.mark.parametrize("case", PREFILL_CASES)
 def test_attention_prefill(case):
     from glassbox_b200 import kernels
