@@ -126,8 +126,8 @@ def bench_attention_decode(batches) -> None:
 
 def bench_attention_prefill() -> None:
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for nh, nkv, hd, t_len in [(9, 3, 64, 2048), (15, 5, 64, 2048), (32, 32, 64, 2048), (32, 32, 64, 8192)]:
-        ps = 16
+    for nh, nkv, hd, t_len, ps in [(9, 3, 64, 2048, 16), (15, 5, 64, 2048, 16), (32, 32, 64, 2048, 16), (32, 32, 64, 8192, 16),
+                                   (32, 32, 64, 8192, 128)]:
         per = t_len // ps
         kc = torch.randn(per + 2, nkv, ps, hd, device=DEV).bfloat16()
         vc = torch.randn_like(kc)
@@ -140,7 +140,7 @@ def bench_attention_prefill() -> None:
         for name, fn in (("mma.sync", kernels.attention_prefill), ("tcgen05", kernels.attention_prefill_tc)):
             t = graph_time(lambda: fn(q, o, kc, vc, tables, first, start, t_len, nh, nkv, hd, ps, hd ** -0.5, None, status),
                            reps=6)
-            print(f"attention_prefill {name:8s} heads {nh}/{nkv} x {hd}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s",
+            print(f"attention_prefill {name:8s} heads {nh}/{nkv} x {hd}, {t_len} tokens, page {ps}: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s",
                   flush=True)
     kernels.check_status(status)
 
