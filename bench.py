@@ -244,10 +244,14 @@ def main():
             # end to end through the scheduler: host tokens in, sampled tokens out, every step
             sched = Scheduler(eng, SchedulerConfig(token_budget=2048, max_seqs=B))
             e2e_steps = max(32, min(K, 256))
-            start_ctx = max(CTX - e2e_steps - W - 1, 1)
+            # Requests that finish their prompts early decode a few tokens while the others still prefill; leave
+            # room for that, so that every request is still live (and within the context) at the last timed step:
+            # a batch that shrinks changes the step's shape, and recording a new CUDA graph is not a decode step.
+            early = 2 * (-(-B * CTX // 2048))
+            start_ctx = max(CTX - e2e_steps - W - 1 - early, 1)
             for i in range(B):
                 sched.submit(Request(prompt=rng.integers(0, vocab, size=start_ctx).tolist(),
-                                     max_tokens=e2e_steps + W + 1))
+                                     max_tokens=e2e_steps + W + 1 + early))
             while any(s.generated == 0 for s in sched.running) or sched.waiting:
                 sched.step()
             for _ in range(W):
@@ -255,15 +259,24 @@ def main():
             torch.cuda.synchronize()
             gc.collect()
             gc.freeze()      # the model's long-lived objects leave the collector's view: no full collection mid-run
+            made = sum(s.generated for s in sched.running)
             t0 = time.perf_counter()
             h2d = 0
+            step_s = []
             for _ in range(e2e_steps):
+                ts = time.perf_counter()
                 sched.step()
+                step_s.append(time.perf_counter() - ts)
                 h2d += eng.h2d_bytes_last
             torch.cuda.synchronize()
             dt = time.perf_counter() - t0
             gc.unfreeze()
-            out["e2e"] = {"value": round(B * e2e_steps / dt, 1), "unit": "tokens/s", "steps": e2e_steps,
+            made = sum(s.generated for s in sched.running) - made
+            assert len(sched.running) == B and made == B * e2e_steps, "a request ended inside the timed region"
+            slow = sorted(range(e2e_steps), key=lambda i: -step_s[i])[:3]
+            print("e2e: slowest steps (index, ms): " + ", ".join(f"{i}: {step_s[i] * 1e3:.1f}" for i in slow)
+                  + f"; median {sorted(step_s)[e2e_steps // 2] * 1e3:.3f} ms", file=sys.stderr)
+            out["e2e"] = {"value": round(made / dt, 1), "unit": "tokens/s", "steps": e2e_steps,
                           "h2d_bytes_per_step": int(h2d / e2e_steps), "d2h_bytes_per_step": 4 * B,
                           "api": "Scheduler.submit/step (host token ids in, sampled ids out)"}
             sched.run_until_idle()

@@ -172,6 +172,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_flag = &sh.abort_flag;
+    // the set-up above overlapped the tail of the kernel before; from here on its results are read
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
 
     if (warp == 0 || warp == AT_WARPS - 1) {
         // ------------------------------------------------------------------------- producers
@@ -479,8 +482,9 @@ GB_EXPORT int gb_attention_prefill_tc(const void* q, long long q_stride, int n_r
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
     dim3 grid(gb_ceil_div(max_rows_per_seq, AT_BM), nh, num_seqs);
-    kernel<<<grid, AT_WARPS * 32, G::SMEM, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, out_stride, block_tables, max_pages,
-                                           seq_first_row, seq_start_pos, nh, nkv, page_size, page_shift, num_pages, scale,
-                                           window, status);
+    cudaError_t e = gb_launch(GB_PDL_ATTENTION, kernel, grid, dim3(AT_WARPS * 32), G::SMEM, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride,
+                              block_tables, max_pages, seq_first_row, seq_start_pos, nh, nkv, page_size, page_shift, num_pages,
+                              scale, window, status);
+    GB_REQUIRE(e == cudaSuccess, "gb_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return gb_check_launch("gb_attention_prefill_tc");
 }

@@ -55,3 +55,31 @@ __device__ __forceinline__ float gb_warp_max(float v) {
 }
 
 static inline int gb_ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// Programmatic dependent launch. A kernel launched through gb_launch (while the switch is on) may start
+// while its predecessor in the stream is still running: it does its set-up, lets its own successor start
+// (gb_pdl_launch_dependents) and then waits (gb_pdl_wait) until the predecessor has completed and its
+// writes are visible; nothing before the wait may read what earlier kernels wrote, or write anything.
+// Launched any other way, both instructions do nothing.
+int gb_pdl_enabled();
+
+__device__ __forceinline__ void gb_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void gb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+enum { GB_PDL_ELEMENTWISE = 1, GB_PDL_GEMM = 2, GB_PDL_ATTENTION = 4 };   // bits of the switch
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t gb_launch(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (gb_pdl_enabled() & family) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

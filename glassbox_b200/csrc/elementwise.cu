@@ -43,6 +43,8 @@ GB_EXPORT int gb_embed(const void* table, int table_dtype, const int* tokens, fl
 template <typename TO, int THREADS>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ gain, TO* __restrict__ out, int n, int d, float eps) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
     int r = blockIdx.x;
     if (r >= n) return;
     const float* src = x + (size_t)(rows ? rows[r] : r) * d;
@@ -73,9 +75,10 @@ GB_EXPORT int gb_rmsnorm(const float* x, const int* rows, const float* gain, voi
     GB_REQUIRE(n >= 0 && d > 0, "gb_rmsnorm: bad sizes n=%d d=%d", n, d);
     if (n == 0) return 0;
     if (out_dtype == GB_F32)
-        rmsnorm_kernel<float, 128><<<n, 128, 0, stream>>>(x, rows, gain, (float*)out, n, d, eps);
+        gb_launch(GB_PDL_ELEMENTWISE, rmsnorm_kernel<float, 128>, dim3(n), dim3(128), 0, stream, x, rows, gain, (float*)out, n, d, eps);
     else if (out_dtype == GB_BF16)
-        rmsnorm_kernel<__nv_bfloat16, 128><<<n, 128, 0, stream>>>(x, rows, gain, (__nv_bfloat16*)out, n, d, eps);
+        gb_launch(GB_PDL_ELEMENTWISE, rmsnorm_kernel<__nv_bfloat16, 128>, dim3(n), dim3(128), 0, stream, x, rows, gain, (__nv_bfloat16*)out, n, d,
+                  eps);
     else
         GB_REQUIRE(false, "gb_rmsnorm: unsupported output dtype %d", out_dtype);
     return gb_check_launch("gb_rmsnorm");
@@ -95,6 +98,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float2* __restri
                                      T* __restrict__ kcache, T* __restrict__ vcache, int n, int nh, int nkv, int hd,
                                      int rot, int max_pos, int page_size, long long num_slots, int write_kv,
                                      int* __restrict__ status) {
+    // (launched without programmatic serialisation: letting the attention kernel that follows start early
+    // cost 9 % of a decode step at batch 64 with SmolLM2-1.7B shapes and gained 1 % of a prefill step)
     int row = blockIdx.x;
     if (row >= n) return;
     const int qd = nh * hd, kvd = nkv * hd;
@@ -183,13 +188,12 @@ GB_EXPORT int gb_rope_kv_write(void* qkv, int dtype, const float* cos_sin, const
     long long num_slots = num_pages * page_size;
     const float2* table = rot > 0 ? (const float2*)cos_sin : nullptr;
     if (dtype == GB_F32)
-        rope_kv_write_kernel<float><<<n, 128, 0, stream>>>((float*)qkv, table, positions, slots, (float*)kcache,
-                                                           (float*)vcache, n, nh, nkv, hd, rot, max_pos, page_size,
-                                                           num_slots, write_kv, status);
+        gb_launch(0, rope_kv_write_kernel<float>, dim3(n), dim3(128), 0, stream, (float*)qkv, table, positions, slots,
+                  (float*)kcache, (float*)vcache, n, nh, nkv, hd, rot, max_pos, page_size, num_slots, write_kv, status);
     else if (dtype == GB_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<n, 128, 0, stream>>>(
-            (__nv_bfloat16*)qkv, table, positions, slots, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n, nh, nkv,
-            hd, rot, max_pos, page_size, num_slots, write_kv, status);
+        gb_launch(0, rope_kv_write_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, (__nv_bfloat16*)qkv, table, positions,
+                  slots, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n, nh, nkv, hd, rot, max_pos, page_size, num_slots,
+                  write_kv, status);
     else
         GB_REQUIRE(false, "gb_rope_kv_write: unsupported dtype %d", dtype);
     return gb_check_launch("gb_rope_kv_write");

@@ -25,7 +25,20 @@
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;        // 64 bfloat16 = 128 bytes = one swizzle row
 
-enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2 };
+enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_ROPE_QKV = 3 };
+
+// What the epilogue of a stacked QKV product needs to rotate the heads and write the cache: the
+// (cos, sin) table [max_pos, hd/2], each row's position (negative: a padding row) and cache slot
+// (page * page_size + offset), one layer of the paged cache [pages, nkv, page_size, hd].
+struct TcQkv {
+    const float2* rope;       // nullptr: no rotation
+    const int* positions;
+    const int* slots;
+    __nv_bfloat16* kcache;
+    __nv_bfloat16* vcache;
+    int nh, nkv, hd, page_size, max_pos, write_kv;
+    long long num_slots;
+};
 
 constexpr int TC_MAX_STAGES = 8;
 
@@ -63,7 +76,7 @@ template <int BN, bool GATED>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_w, void* __restrict__ C,
                                                            int mode, int M, int N, int K, long long ldc, int gate_rows,
-                                                           int* __restrict__ status) {
+                                                           int* __restrict__ status, const TcQkv qkv) {
     using G = TcGeometry<BN, GATED>;
     constexpr int STAGES = G::STAGES, BNO = G::BNO;
     extern __shared__ unsigned char smem_dyn[];
@@ -101,6 +114,9 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
     volatile int* abort_flag = &sh.abort_flag;
+    // the set-up above overlapped the tail of the kernel before; from here on its results are read
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
 
     if (warp == 0) {
         if (lane == 0 && kblocks > 0) {
@@ -166,6 +182,77 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
             }
             const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             const int row = m0 + q * 32 + lane;
+            if (!GATED && mode == TC_ROPE_QKV) {
+                // Stacked QKV (crates/glassbox-core/src/model.rs:266-276): a tile holds whole heads (BN is a multiple
+                // of the head size). Query and key heads are rotated, channel i with channel i + hd/2, from the
+                // float32 sums; queries go to C, rotated keys and the values to the row's cache slot.
+                const int hd = qkv.hd, half = hd >> 1;
+                const int pos = row < M ? qkv.positions[row] : -1;
+                const long long slot = (row < M && pos >= 0) ? qkv.slots[row] : -1;
+                const bool bad_pos = qkv.rope != nullptr && pos >= qkv.max_pos;
+                const bool bad_slot = qkv.write_kv && pos >= 0 && (slot < 0 || slot >= qkv.num_slots);
+                if (bad_pos) atomicOr(status, GB_STATUS_BAD_POSITION);
+                if (bad_slot) atomicOr(status, GB_STATUS_BAD_SLOT);
+                const int heads_total = qkv.nh + 2 * qkv.nkv;
+#pragma unroll 1
+                for (int c = 0; c < half; c += 32) {
+                    // (cos, sin) of channels c .. c+31 at this row's position: read once, used by every head of the tile
+                    float4 cs[16];
+                    const bool have_cs = qkv.rope != nullptr && !bad_pos && pos >= 0;
+                    if (have_cs) {
+                        const float4* src = reinterpret_cast<const float4*>(qkv.rope + (size_t)pos * half + c);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) cs[j] = src[j];
+                    }
+#pragma unroll 1
+                    for (int h0 = 0; h0 < BN; h0 += hd) {
+                        const int head = (n0 + h0) / hd;
+                        if (head >= heads_total) break;               // columns beyond the matrix (uniform for the block)
+                        const bool is_q = head < qkv.nh, is_k = !is_q && head < qkv.nh + qkv.nkv;
+                        __nv_bfloat16* dst = nullptr;                  // this row's head: hd contiguous bfloat16
+                        if (pos >= 0) {
+                            if (is_q) {
+                                dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + (size_t)head * hd;
+                            } else if (qkv.write_kv && !bad_slot) {
+                                const int kvh = is_k ? head - qkv.nh : head - qkv.nh - qkv.nkv;
+                                dst = (is_k ? qkv.kcache : qkv.vcache) +
+                                      (((slot / qkv.page_size) * qkv.nkv + kvh) * qkv.page_size + slot % qkv.page_size) * hd;
+                            }
+                        }
+                        uint32_t x0[32], x1[32];   // the warp-collective loads run for every row; the stores only for live ones
+                        tmem_load32(t_base + (uint32_t)(h0 + c), x0);
+                        tmem_load32(t_base + (uint32_t)(h0 + half + c), x1);
+                        if ((is_q || is_k) && have_cs) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                const float4 t = cs[j >> 1];   // (cos, sin) of channels c+j and c+j+1
+                                const float a0 = __uint_as_float(x0[j]), b0 = __uint_as_float(x1[j]);
+                                const float a1 = __uint_as_float(x0[j + 1]), b1 = __uint_as_float(x1[j + 1]);
+                                x0[j] = __float_as_uint(a0 * t.x - b0 * t.y);
+                                x1[j] = __float_as_uint(b0 * t.x + a0 * t.y);
+                                x0[j + 1] = __float_as_uint(a1 * t.z - b1 * t.w);
+                                x1[j + 1] = __float_as_uint(b1 * t.z + a1 * t.w);
+                            }
+                        }
+                        if (dst != nullptr) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 v0, v1;
+                                v0.x = pack2(x0[j], x0[j + 1]); v0.y = pack2(x0[j + 2], x0[j + 3]);
+                                v0.z = pack2(x0[j + 4], x0[j + 5]); v0.w = pack2(x0[j + 6], x0[j + 7]);
+                                v1.x = pack2(x1[j], x1[j + 1]); v1.y = pack2(x1[j + 2], x1[j + 3]);
+                                v1.z = pack2(x1[j + 4], x1[j + 5]); v1.w = pack2(x1[j + 6], x1[j + 7]);
+                                *reinterpret_cast<uint4*>(dst + c + j) = v0;
+                                *reinterpret_cast<uint4*>(dst + half + c + j) = v1;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh.tempty[acc]);
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BNO; c0 += 32) {
                 uint32_t r[32];
@@ -264,7 +351,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 
 template <int BN, bool GATED>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int mode, int M, int N, int K,
-                     long long ldc, int gate_rows, int* status, cudaStream_t stream) {
+                     long long ldc, int gate_rows, int* status, cudaStream_t stream, const TcQkv& qkv = TcQkv()) {
     using G = TcGeometry<BN, GATED>;
     auto kernel = gemm_tcgen05_kernel<BN, GATED>;
     static bool configured = false;
@@ -282,7 +369,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int 
     }
     const int ntiles = gb_ceil_div(M, TC_BM) * gb_ceil_div(N, G::BNO);
     const int grid = ntiles < sms ? ntiles : sms;   // persistent: one block per SM walks the tiles
-    kernel<<<grid, 192, G::SMEM, stream>>>(ma, mw, c, mode, M, N, K, ldc, gate_rows, status);
+    cudaError_t e = gb_launch(GB_PDL_GEMM, kernel, dim3(grid), dim3(192), G::SMEM, stream, ma, mw, c, mode, M, N, K, ldc, gate_rows, status, qkv);
+    GB_REQUIRE(e == cudaSuccess, "gb_gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return gb_check_launch("gb_gemm_tcgen05");
 }
 
@@ -335,4 +423,37 @@ GB_EXPORT int gb_gemm_tcgen05_gated(const void* a, const void* w, void* c, int M
     if (make_map(&mw, w, 2LL * inter, K, ldw, wide ? 128 : 64)) return 1;
     return wide ? launch_tc<256, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream)
                 : launch_tc<128, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream);
+}
+
+// 1 if gb_gemm_tcgen05_qkv takes this head size: whole heads must tile the 128 columns of an output tile and half
+// a head must be a multiple of the 32 columns an epilogue thread reads at a time.
+GB_EXPORT int gb_gemm_tcgen05_qkv_supported(int hd) { return hd == 64 || hd == 128; }
+
+// Stacked QKV projection with rotary encoding and cache write in the epilogue: w = [q rows; k rows; v rows]
+// ((nh + 2 nkv) * hd rows); q_out bfloat16 [M, >= nh*hd] receives the rotated queries; rotated keys and the
+// values go to the cache slot of each row (unless write_kv == 0). rope == nullptr stores without rotation.
+GB_EXPORT int gb_gemm_tcgen05_qkv(const void* a, const void* w, void* q_out, int M, int K, long long lda, long long ldw,
+                                  long long ldq, const float* rope, int max_pos, const int* positions, const int* slots,
+                                  void* kcache, void* vcache, int nh, int nkv, int hd, int page_size, long long num_pages,
+                                  int write_kv, int* status, cudaStream_t stream) {
+    const int N = (nh + 2 * nkv) * hd;
+    GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, N, K, lda, ldw),
+               "gb_gemm_tcgen05_qkv: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d N=%d K=%d)",
+               M, N, K);
+    GB_REQUIRE(gb_gemm_tcgen05_qkv_supported(hd) && nh > 0 && nkv > 0, "gb_gemm_tcgen05_qkv: head size %d is not built (64, 128)", hd);
+    GB_REQUIRE(ldq >= (long long)nh * hd && ldq % 8 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)kcache % 16 == 0 &&
+                   (uintptr_t)vcache % 16 == 0,
+               "gb_gemm_tcgen05_qkv: q_out and the cache must be 16-byte aligned");
+    GB_REQUIRE(page_size > 0 && positions && slots && status, "gb_gemm_tcgen05_qkv: bad arguments");
+    CUtensorMap ma, mw;
+    if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
+    const int bn = pick_bn(M, N) == 256 ? 256 : 128;   // whole heads per tile
+    if (make_map(&mw, w, N, K, ldw, bn)) return 1;
+    TcQkv q = {};
+    q.rope = (const float2*)rope; q.positions = positions; q.slots = slots;
+    q.kcache = (__nv_bfloat16*)kcache; q.vcache = (__nv_bfloat16*)vcache;
+    q.nh = nh; q.nkv = nkv; q.hd = hd; q.page_size = page_size; q.max_pos = max_pos; q.write_kv = write_kv;
+    q.num_slots = num_pages * page_size;
+    if (bn == 256) return launch_tc<256, false>(ma, mw, q_out, TC_ROPE_QKV, M, N, K, ldq, 0, status, stream, q);
+    return launch_tc<128, false>(ma, mw, q_out, TC_ROPE_QKV, M, N, K, ldq, 0, status, stream, q);
 }

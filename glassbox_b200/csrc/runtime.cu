@@ -24,6 +24,11 @@ int gb_check_launch(const char* what) {
 
 GB_EXPORT const char* gb_last_error() { return g_error; }
 
+// Which kernel families are launched with programmatic stream serialisation (bits GB_PDL_*; all by default).
+static int g_pdl = 7;
+int gb_pdl_enabled() { return g_pdl; }
+GB_EXPORT void gb_set_pdl(int families) { g_pdl = families; }
+
 // Compute capability of the current device as major*10+minor, or a negative CUDA error code.
 GB_EXPORT int gb_device_arch() {
     int dev = 0, major = 0, minor = 0;

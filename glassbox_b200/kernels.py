@@ -8,6 +8,7 @@ no library stand-in: if the shared library cannot be built or loaded, the first 
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Optional
 
@@ -54,6 +55,8 @@ _SIGNATURES = {
     "gb_kv_prefetch": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _LL, _LL, _I, _I, _P],
     "gb_attention_prefill": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_attention_prefill_supported": [_I, _I, _I, _I],
+    "gb_gemm_tcgen05_qkv": [_P, _P, _P, _I, _I, _LL, _LL, _LL, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _I, _P, _P],
+    "gb_gemm_tcgen05_qkv_supported": [_I],
     "gb_attention_prefill_tc": [_P, _LL, _I, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_attention_prefill_tc_supported": [_I, _I, _I, _I],
     "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P],
@@ -82,6 +85,9 @@ def lib():
                     raise KernelError(f"{path} does not export {name}; rebuild it (csrc/build.py --force)")
                 fn.argtypes = args
                 fn.restype = ctypes.c_int
+            handle.gb_set_pdl.argtypes = [ctypes.c_int]
+            handle.gb_set_pdl.restype = None
+            handle.gb_set_pdl(int(os.environ.get("GLASSBOX_B200_PDL", "7")) if USE_PDL else 0)
             _lib = handle
     return _lib
 
@@ -320,6 +326,28 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool 
         mode = 0 if c.dtype == torch.bfloat16 else 1
     _call("gb_gemm_tcgen05", _ptr(a), _ptr(w), _ptr(c), mode, M, N, K, a.stride(0), w.stride(0), c.stride(0),
           _ptr(status), _stream())
+
+
+def gemm_tc_qkv_supported(a: torch.Tensor, w: torch.Tensor, hd: int, q_out: torch.Tensor, kcache: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel can project, rotate and write the cache in one go for these operands."""
+    return (q_out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and q_out.stride(0) % 8 == 0
+            and q_out.data_ptr() % 16 == 0 and bool(lib().gb_gemm_tcgen05_qkv_supported(hd)) and gemm_tc_supported(a, w, q_out))
+
+
+def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[torch.Tensor],
+                positions: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nh: int, nkv: int,
+                hd: int, page_size: int, write_kv: bool, status: torch.Tensor) -> None:
+    """Stacked QKV projection on the tcgen05 kernel with the rotation and the cache write in its epilogue:
+    q_out[:, :nh*hd] receives the rotated queries, the cache slots of the rows the rotated keys and the
+    values. ``cos_sin`` is float32 [max_pos, hd/2, 2] or None (no rotation)."""
+    _cuda(a, w, q_out, cos_sin, positions, slots, kcache, vcache, status)
+    M, K = a.shape
+    assert w.shape == ((nh + 2 * nkv) * hd, K) and a.stride(1) == 1 and w.stride(1) == 1 and q_out.stride(1) == 1
+    assert q_out.shape[0] == M and q_out.shape[1] >= nh * hd and kcache.is_contiguous() and vcache.is_contiguous()
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape[1:] == (hd // 2, 2) and cos_sin.is_contiguous())
+    _call("gb_gemm_tcgen05_qkv", _ptr(a), _ptr(w), _ptr(q_out), M, K, a.stride(0), w.stride(0), q_out.stride(0),
+          _ptr(cos_sin), cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slots), _ptr(kcache),
+          _ptr(vcache), nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status), _stream())
 
 
 def gemm_tc_gated(a: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor,

@@ -58,6 +58,11 @@ class GqaAttention(Mixer):
             kernels.gemm_stream_qkv(x, self.params["wqkv"], qkv, table, ctx.positions, cache.slots, cache.k, cache.v,
                                     self.nh, self.nkv, self.hd, cache.page_size, writes_cache, ctx.status, norm=norm,
                                     prefetch=weights_ahead(ctx, self.params["wqkv"]))
+        elif (plain_rotary and norm is None and n > kernels.STREAM_MAX_ROWS
+              and kernels.gemm_tc_qkv_supported(x, self.params["wqkv"], self.hd, qkv, cache.k)):
+            # many rows: the tile kernel projects; its epilogue rotates from the float32 sums and writes the cache
+            kernels.gemm_tc_qkv(x, self.params["wqkv"], qkv, table, ctx.positions, cache.slots, cache.k, cache.v,
+                                self.nh, self.nkv, self.hd, cache.page_size, writes_cache, ctx.status)
         else:
             linear(ctx, h, self.params["wqkv"], qkv)
             if table is None:

@@ -694,6 +694,58 @@ def test_gemm_stream_qkv_with_norm_rotary_and_cache_write(M, nh, nkv, hd, d, ps,
     assert float(kc3.abs().max()) == 0.0 and float(vc3.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("M", [65, 128, 300, 2048])
+@pytest.mark.parametrize("nh, nkv, hd, d, ps, rotary", [(9, 3, 64, 576, 16, True), (3, 1, 128, 264, 32, True), (4, 4, 64, 256, 16, False),
+                                                          (1, 1, 64, 64, 8, True)])
+def test_gemm_tcgen05_qkv_with_rotary_and_cache_write(M, nh, nkv, hd, d, ps, rotary):
+    """The tile kernel's QKV epilogue against the separate kernels (product, then rotation and cache write)."""
+    from glassbox_b200 import kernels
+    from glassbox_b200.parts.rope import rotary_table
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(M + hd)
+    h = torch.randn(M, d, generator=g).to(dtype).to(DEV)
+    w = (torch.randn((nh + 2 * nkv) * hd, d, generator=g) / math.sqrt(d)).to(dtype).to(DEV)
+    table = rotary_table(1e5, hd, 3000).to(DEV) if rotary else None
+    positions = torch.randint(0, 3000, (M,), generator=g).to(torch.int32)
+    pages = -(-M // ps) + 3
+    slots = torch.randperm(pages * ps, generator=g)[:M].to(torch.int32)
+    positions[1] = -1                                      # a padding row: nothing may be stored for it
+    qkv = torch.empty(M, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
+    st = status()
+    kernels.gemm_tc(h, w, qkv, status=st)
+    kc = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    kernels.rope_kv_write(qkv, table, positions.to(DEV), slots.to(DEV), kc, vc, nh, nkv, hd, hd, ps, True, st)
+    q2 = torch.zeros(M, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    assert kernels.gemm_tc_qkv_supported(h, w, hd, q2, kc2)
+    kernels.gemm_tc_qkv(h, w, q2, table, positions.to(DEV), slots.to(DEV), kc2, vc2, nh, nkv, hd, ps, True, st)
+    assert int(st) == 0
+    live = (positions >= 0).to(DEV)
+    t = tol(dtype, 2)
+    assert (q2[live, :nh * hd].float() - qkv[live, :nh * hd].float()).abs().max() <= t
+    assert (kc2.float() - kc.float()).abs().max() <= t and (vc2.float() - vc.float()).abs().max() <= t
+    assert float(q2[~live].abs().max()) == 0.0 and float(q2[:, nh * hd:].abs().max()) == 0.0   # nothing beside the queries
+    written = kc2.abs().sum(dim=(1, 3)).flatten().nonzero().numel()     # (page, offset) rows touched
+    assert written == int(live.sum())
+    # and against float64: the rotation of the float32 sums
+    ref = h.double() @ w.double().T
+    if rotary:
+        half = hd // 2
+        cs = table.double().cpu()[positions.clamp(min=0).long()]        # [M, half, 2]
+        r = ref.cpu().reshape(M, nh + 2 * nkv, hd).clone()
+        a, b = r[:, :nh + nkv, :half].clone(), r[:, :nh + nkv, half:].clone()
+        r[:, :nh + nkv, :half] = a * cs[:, None, :, 0] - b * cs[:, None, :, 1]
+        r[:, :nh + nkv, half:] = b * cs[:, None, :, 0] + a * cs[:, None, :, 1]
+        ref = r.reshape(M, -1)
+    else:
+        ref = ref.cpu()
+    assert (q2.cpu().double()[live.cpu(), :nh * hd] - ref[live.cpu(), :nh * hd]).abs().max() <= tol(dtype, 2)
+    kernels.gemm_tc_qkv(h, w, q2, table, positions.to(DEV), slots.to(DEV), torch.zeros_like(kc), vc3 := torch.zeros_like(vc),
+                        nh, nkv, hd, ps, False, st)
+    assert float(vc3.abs().max()) == 0.0                                   # write_kv off: queries only
+
+
 @pytest.mark.parametrize("M, inter, K", [(128, 128, 64), (2048, 1536, 576), (300, 176, 72), (65, 8, 8), (1000, 2560, 960),
                                          (129, 136, 200), (40, 2048, 1024)])
 def test_gemm_tcgen05_gated(M, inter, K):
