@@ -34,6 +34,15 @@ class LLM:
     def config(self):
         return self.engine.config
 
+    def warm_up(self, max_batch: Optional[int] = None, max_context: Optional[int] = None) -> int:
+        """Record the CUDA graphs of decode steps up to ``max_batch`` requests and ``max_context`` tokens now,
+        instead of inside the first step of each shape (a few tens of milliseconds each). Defaults: the
+        scheduler's ``max_seqs`` and what the cache holds. Returns the number of graphs recorded."""
+        mb = self.scheduler_config.max_seqs if max_batch is None else max_batch
+        mc = min(self.engine.num_pages * self.engine.page_size, self.engine.config.max_position) if max_context is None \
+            else max_context
+        return self.engine.warm_up(mb, mc)
+
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], max_tokens: int = 128, *,
                  temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
                  repetition_penalty: float = 1.0, seed: int = 0, stop: Sequence[int] = (),

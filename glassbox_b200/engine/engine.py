@@ -319,20 +319,51 @@ class Engine:
         self.steps += 1
         return logits
 
+    def _decode_graph(self, Sb: int, Pb: int):
+        """The CUDA graph of a decode step of ``Sb`` rows with block tables ``Pb`` wide, recorded if new."""
+        key = (Sb, Pb)
+        g = self._graphs.get(key)
+        if g is None:
+            off = self._layout(Sb, Sb, Sb, Pb)
+            seqs, longest = getattr(self, "_seqs", None), getattr(self, "_max_ctx", 0)
+            blank = self._fill([], off, Sb, Sb, Sb, Pb)          # an all-padding batch: every row skipped
+            self._seqs, self._max_ctx = seqs, longest
+            g = self._capture(key, off, blank, Sb, Sb, Sb, Pb, 1, decode_only=True)
+        return g
+
+    def warm_up(self, max_batch: int, max_context: int) -> int:
+        """Record the decode graphs a service will need before it needs them: every batch bucket (powers of
+        two up to ``max_batch``) at every table width (powers of two up to ``max_context`` tokens). Recording
+        a graph takes tens of milliseconds; without this it happens inside the first step of each new shape,
+        also when a batch shrinks because requests end. Returns the number of graphs recorded."""
+        if not self.use_graphs or self.device_cache.has_state:
+            return 0
+        before = len(self._graphs)
+        max_pages = -(-min(int(max_context), self.config.max_position) // self.page_size)
+        Pb = 8
+        widths = []
+        while True:
+            widths.append(Pb)
+            if Pb >= max_pages:
+                break
+            Pb *= 2
+        Sb = 1
+        while Sb <= min(int(max_batch), self.max_graph_batch):
+            for Pb in widths:
+                if len(self._graphs) >= self.max_graphs:
+                    return len(self._graphs) - before
+                self._decode_graph(Sb, Pb)
+            Sb *= 2
+        return len(self._graphs) - before
+
     def _step_graph(self, entries, S: int, max_pages: int, sampling) -> torch.Tensor:
         Sb = 1 << max(S - 1, 0).bit_length()
         Pb = max(8, 1 << max(max_pages - 1, 0).bit_length())
-        key = (Sb, Pb)
         off = self._layout(Sb, Sb, Sb, Pb)
         if sampling is None:
             sampling = ([0.0] * S, [0.0] * S)
         host = self._fill(entries, off, Sb, Sb, Sb, Pb, sampling)
-        g = self._graphs.get(key)
-        if g is None:
-            seqs, longest = self._seqs, self._max_ctx
-            blank = self._fill([], off, Sb, Sb, Sb, Pb)          # an all-padding batch: every row skipped
-            self._seqs, self._max_ctx = seqs, longest
-            g = self._capture(key, off, blank, Sb, Sb, Sb, Pb, 1, decode_only=True)
+        g = self._decode_graph(Sb, Pb)
         self._stage_copy(host, g["meta"])
         g["graph"].replay()
         kernels.launch_count += g["nodes"]

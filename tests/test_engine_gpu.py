@@ -40,6 +40,29 @@ def test_first_tokens_and_long_decoding(model_dirs, name, dtype):
         eng.step([StepEntry("a", [1], [0])])
 
 
+def test_warm_up_records_the_decode_graphs_before_they_are_needed(model_dirs):
+    from glassbox_b200.engine.engine import StepEntry
+    folder = model_dirs("A", "bfloat16")
+    toks = [random.Random(3).randrange(TINY["A"]["vocab_size"]) for _ in range(40)]
+    ref = forward_logits(folder, toks)
+    eng = make_engine(folder, "bfloat16")
+    made = eng.warm_up(max_batch=4, max_context=TINY["A"]["max_position_embeddings"])
+    assert made == len(eng._graphs) and made >= 3 * 1          # batch buckets 1, 2, 4 at every table width
+    assert eng.warm_up(max_batch=4, max_context=TINY["A"]["max_position_embeddings"]) == 0
+    for r in ("a", "b", "c"):
+        eng.add_request(r)
+        eng.step([StepEntry(r, toks[:20], [])])
+    rows = []
+    for i in range(20, 40):                                      # three requests, then two, then one: the batch shrinks
+        live = ["a", "b", "c"][:3 if i < 28 else 2 if i < 34 else 1]
+        out = eng.step([StepEntry(r, [toks[i]], [0]) for r in live])
+        rows.append(out[0].cpu().numpy())
+    eng.check()
+    decode_graphs = [k for k in eng._graphs if len(k) == 2]     # (batch bucket, table width); prompt shapes have longer keys
+    assert len(decode_graphs) == made, "a decode step recorded a graph although its shape was warmed up"
+    assert_logits_close(np.stack(rows), ref[20:40], "bfloat16", "decoding on warmed-up graphs")
+
+
 @pytest.mark.parametrize("name, dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("D", "float32")])
 def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
     import glassbox_b200
