@@ -7,6 +7,9 @@ the same public calls a user would make, without touching the framework's files:
 * ``ToyStateForCausalLM``: layer 0 mixes with a decaying running sum kept in a per-request state
   slot (no keys, no pages); layer 1 is ordinary attention. Its schedule may run a layer twice or
   let a run read another run's cache.
+* ``ToyRoutedForCausalLM``: layer 0 is attention whose position encoding is a learned table added to
+  queries and keys (not a rotation) followed by a feed-forward that routes each token to its top-k of a
+  few small experts; layer 1 is rotary attention with the dense gated feed-forward.
 
 These are test fixtures for the framework's interfaces, not models of anything.
 """
@@ -19,7 +22,7 @@ import torch
 from glassbox_b200.config import (GqaAttentionSpec, LayerSpec, ModelConfig, NoPositionSpec, RmsNormSpec, RopeSpec,
                                   RunSpec, SwiGluSpec)
 from glassbox_b200.config.registry import Architecture, register_architecture
-from glassbox_b200.parts import FeedForward, Mixer, Norm, StateSpec, register_part
+from glassbox_b200.parts import FeedForward, Mixer, Norm, Position, StateSpec, register_part
 from glassbox_b200.weights.binding import ParamSpec, Stacked
 
 
@@ -92,6 +95,63 @@ class ZeroMixer(Mixer):
         return None
 
 
+@dataclass(frozen=True)
+class RoutedFfnSpec:
+    """Each token goes to the ``top_k`` experts with the largest router logits; their outputs are mixed
+    with the softmax of those logits. Every expert is a small gated feed-forward."""
+    num_experts: int
+    top_k: int
+    intermediate_size: int
+    kind: str = "test_routed_ffn"
+
+
+class RoutedFfn(FeedForward):
+    def __init__(self, spec, *, hidden_size):
+        super().__init__(spec)
+        self.d = hidden_size
+
+    def param_specs(self):
+        e, i = self.spec.num_experts, self.spec.intermediate_size
+        return {"router": ParamSpec((e, self.d)), "w_gate_up": ParamSpec((e, 2 * i, self.d)),
+                "w_down": ParamSpec((e, self.d, i))}
+
+    def forward(self, ctx, h, residual):
+        # router logits and mixing weights in float32; every expert runs on every row and rows it was
+        # not chosen for get weight zero (static shapes: the step can be recorded as a CUDA graph)
+        x = h.float()
+        logits = x @ self.params["router"].float().T
+        top = logits.topk(self.spec.top_k, dim=-1)
+        mix = torch.zeros_like(logits).scatter_(1, top.indices, torch.softmax(top.values, dim=-1))
+        i = self.spec.intermediate_size
+        for e in range(self.spec.num_experts):
+            gu = x @ self.params["w_gate_up"][e].float().T
+            act = torch.nn.functional.silu(gu[:, :i]) * gu[:, i:]
+            residual += mix[:, e:e + 1] * (act @ self.params["w_down"][e].float().T)
+
+
+@dataclass(frozen=True)
+class LearnedOffsetPositionSpec:
+    """q and k of the token at position p get a learned vector table[p] added, per head."""
+    head_dim: int
+    max_position: int
+    kind: str = "test_learned_offset"
+
+
+class LearnedOffsetPosition(Position):
+    rotary_dim = 0
+
+    def param_specs(self):
+        return {"table": ParamSpec((self.spec.max_position, self.spec.head_dim))}
+
+    def apply_qk(self, ctx, qkv, num_heads, num_kv_heads, head_dim):
+        live = (ctx.positions >= 0).unsqueeze(-1).unsqueeze(-1)            # padding rows carry position -1
+        add = self.params["table"][ctx.positions.clamp(min=0).long()].to(qkv.dtype).unsqueeze(1) * live
+        heads = qkv[:, :(num_heads + num_kv_heads) * head_dim].unflatten(1, (num_heads + num_kv_heads, head_dim))
+        heads += add
+
+
+register_part("ffn", "test_routed_ffn", RoutedFfn, replace=True)
+register_part("position", "test_learned_offset", LearnedOffsetPosition, replace=True)
 register_part("mixer", "test_zero_mixer", ZeroMixer, replace=True)
 register_part("norm", "test_identity_norm", IdentityNorm, replace=True)
 register_part("ffn", "test_zero_ffn", ZeroFfn, replace=True)
@@ -147,6 +207,40 @@ def _bind_toy_state(config):
 
 
 register_architecture(Architecture("ToyStateForCausalLM", _parse_toy_state, _bind_toy_state), replace=True)
+
+
+def _parse_toy_routed(raw):
+    d, hd = raw["hidden_size"], raw["head_dim"]
+    norm = RmsNormSpec(eps=raw["eps"])
+    learned = LearnedOffsetPositionSpec(head_dim=hd, max_position=raw["max_position"])
+    rope = RopeSpec(theta=raw["rope_theta"], rotary_dim=hd, max_position=raw["max_position"])
+    attn = lambda position: GqaAttentionSpec(num_heads=raw["num_heads"], num_kv_heads=raw["num_kv_heads"], head_dim=hd,
+                                             scale=hd ** -0.5, position=position)
+    routed = RoutedFfnSpec(num_experts=raw["num_experts"], top_k=raw["top_k"], intermediate_size=raw["expert_size"])
+    layers = (LayerSpec(attn(learned), routed, norm, norm),
+              LayerSpec(attn(rope), SwiGluSpec(intermediate_size=raw["intermediate_size"]), norm, norm))
+    return ModelConfig(architecture="ToyRoutedForCausalLM", vocab_size=raw["vocab_size"], hidden_size=d,
+                       max_position=raw["max_position"], tie_word_embeddings=True, layers=layers,
+                       schedule=(RunSpec(0, 0), RunSpec(1, 1)), final_norm=norm, raw=dict(raw))
+
+
+def _bind_toy_routed(config):
+    from glassbox_b200.weights.binding import Tied
+    b = {"embed.weight": Stacked(("embed",)), "head.weight": Tied("embed.weight"),
+         "final_norm.weight": Stacked(("final_norm",)),
+         "layers.0.mixer.position.table": Stacked(("offsets",)),
+         "layers.0.ffn.router": Stacked(("router",)), "layers.0.ffn.w_gate_up": Stacked(("experts_gate_up",)),
+         "layers.0.ffn.w_down": Stacked(("experts_down",)),
+         "layers.1.ffn.w_gate_up": Stacked(("gate", "up")), "layers.1.ffn.w_down": Stacked(("down",))}
+    for i in (0, 1):
+        b[f"layers.{i}.mixer.wqkv"] = Stacked((f"wq{i}", f"wk{i}", f"wv{i}"))
+        b[f"layers.{i}.mixer.wo"] = Stacked((f"wo{i}",))
+        b[f"layers.{i}.mixer_norm.weight"] = Stacked((f"norm{i}a",))
+        b[f"layers.{i}.ffn_norm.weight"] = Stacked((f"norm{i}b",))
+    return b
+
+
+register_architecture(Architecture("ToyRoutedForCausalLM", _parse_toy_routed, _bind_toy_routed), replace=True)
 
 
 def _parse_one_part(raw):
