@@ -97,6 +97,72 @@ def prefill_flops(c, T):
     return L * (2.0 * matrix_params_per_layer(c) * T + 2.0 * T * T * qd) + 2.0 * c["vocab_size"] * c["hidden_size"]
 
 
+def serving_workload(args):
+    """Continuous batching on a mixed workload, after the reference's serving benchmark
+    (crates/glassbox-bench/src/main.rs:296-318: random tokens, a spread of prompt and output lengths, a shared
+    prefix for some), all requests submitted at once. Wall-clock, host tokens in and sampled tokens out."""
+    import numpy as np
+    import torch
+    import glassbox_b200
+    from glassbox_b200 import kernels
+    from glassbox_b200.engine.engine import Engine
+    from glassbox_b200.engine.scheduler import Request, Scheduler, SchedulerConfig
+    from glassbox_b200.models.llama import make_llama_raw_config
+    from glassbox_b200.sampling.sampler import SamplerConfig
+
+    model = args.model if args.model != "135m" else "360m"
+    shape = dict(SHAPES[model])
+    if args.layers:
+        shape["num_hidden_layers"] = min(args.layers, shape["num_hidden_layers"])
+    n_req, chunk, max_seqs = 64, 512, 64
+    rng = np.random.default_rng(1)
+
+    def draw():
+        """One workload: fresh tokens every time, so that nothing of an earlier pass is found in the prefix cache."""
+        shared = rng.integers(0, shape["vocab_size"], size=384).tolist()
+        prompts, outs = [], []
+        for i in range(n_req):
+            n = int(rng.integers(32, 2049))
+            body = rng.integers(0, shape["vocab_size"], size=n).tolist()
+            prompts.append(shared + body[384:] if i % 4 == 0 and n > 384 else body)
+            outs.append(int(rng.integers(32, 513)))
+        return prompts, outs
+
+    tmp = tempfile.mkdtemp(prefix="glassbox_b200_bench_")
+    try:
+        glassbox_b200.write_random_model(tmp, make_llama_raw_config(**shape), seed=0, store_dtype=torch.bfloat16)
+        eng = Engine(tmp, "bfloat16", cache_tokens=n_req * 2600, page_size=16, max_batch_tokens=chunk + max_seqs,
+                     max_requests=max_seqs + 2, share_prefixes=True)
+        results = {}
+        for rep in range(3):          # two passes record graphs; the third, on new tokens, is reported
+            prompts, outs = draw()
+            sched = Scheduler(eng, SchedulerConfig(token_budget=chunk + max_seqs, max_seqs=max_seqs))
+            torch.cuda.synchronize()
+            launches0, replays0 = kernels.launch_count, eng.graph_replays
+            t0 = time.perf_counter()
+            for p, n in zip(prompts, outs):
+                sched.submit(Request(prompt=p, max_tokens=n, sampler=SamplerConfig(temperature=0.8, seed=len(p))))
+            sched.run_until_idle()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            eng.check()
+            m = sched.metrics
+            results = {"metric": f"serving tok/s, mixed workload (SmolLM2-{model.upper()} shapes)",
+                       "value": round(m.generated_tokens / dt, 1), "unit": "generated tokens/s", "n_gpus": 1,
+                       "seconds": round(dt, 3), "requests": n_req, "prompt_tokens": m.prompt_tokens,
+                       "generated_tokens": m.generated_tokens, "total_tokens_per_s": round((m.prompt_tokens + m.generated_tokens) / dt, 1),
+                       "steps": m.steps, "prefix_hit_tokens": m.prefix_hit_tokens, "preemptions": m.preemptions,
+                       "graph_replays": eng.graph_replays - replays0, "gpu_launches": kernels.launch_count - launches0,
+                       "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                       "config": {"model": f"SmolLM2-{model} shapes, random weights", "layers": shape["num_hidden_layers"],
+                                  "requests": n_req, "prompt_len": "U(32,2048)", "output_len": "U(32,512)",
+                                  "portion": chunk, "max_seqs": max_seqs, "shared_prefix": 384, "page_size": 16}}
+        print(json.dumps(results))
+        return 0
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -109,6 +175,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip batch-1/64 decode, prefill and e2e")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="serving: the mixed workload of the 360M configuration (64 requests, prompts 32-2048, outputs "
+                         "32-512, prompt portions of 512, a quarter of the requests sharing a 384-token prefix) through "
+                         "the scheduler; prints its own JSON line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -128,6 +198,8 @@ def main():
     from glassbox_b200.engine.scheduler import Request, Scheduler, SchedulerConfig
     from glassbox_b200.models.llama import make_llama_raw_config
 
+    if args.workload == "serving":
+        return serving_workload(args)
     K, W, B, CTX = args.steps, max(args.warmup, 3), args.batch, args.context
     shape = dict(SHAPES[args.model])
     full_layers = shape["num_hidden_layers"]

@@ -65,6 +65,11 @@ __global__ void __launch_bounds__(256) attention_prefill_kernel(
     const int nrows = seq_first_row[seq + 1] - row0;
     if (qt * PF_BM >= nrows) return;
     const int start_pos = seq_start_pos[seq];
+    if (start_pos < 0) {                          // a padding sequence of a fixed-shape batch (uniform for the block):
+        for (int i = threadIdx.x; i < nrows * (HD / 2); i += blockDim.x)   // its rows read as zeros downstream
+            *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + i / (HD / 2)) * out_stride + (size_t)head * HD + (i % (HD / 2)) * 2) = 0u;
+        return;
+    }
     const int kvh = head / (nh / nkv);
     const int q_lo = qt * PF_BM;
     const int pos_lo = start_pos + q_lo, pos_hi = start_pos + min(nrows, q_lo + PF_BM) - 1;

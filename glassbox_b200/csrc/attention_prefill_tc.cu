@@ -133,6 +133,12 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
         return;
     }
     const int start_pos = seq_start_pos[seq];
+    if (start_pos < 0) {                          // a padding sequence of a fixed-shape batch (uniform for the block):
+        for (int i = tid; i < nrows * (HD / 8); i += blockDim.x)   // its rows read as zeros downstream
+            *reinterpret_cast<uint4*>(out + (size_t)(row0 + i / (HD / 8)) * out_stride + (size_t)head * HD + (i % (HD / 8)) * 8) =
+                make_uint4(0, 0, 0, 0);
+        return;
+    }
     const int kvh = head / (nh / nkv);
     const int q_lo = qt * AT_BM;
     const int pos_lo = start_pos + q_lo, pos_hi = start_pos + min(nrows, q_lo + AT_BM) - 1;

@@ -483,23 +483,29 @@ GBH_EXPORT int gbh_cache_ids(void* h, int group, int64_t* out, int cap) {
 //   seq_slots [S], temperature [n_want], uniform [n_want] (float bits); then per group g: off[9+2g] slots [n],
 //   off[10+2g] tables [S, max_pages].
 // The E entries bring tok_count[e] tokens each (flat in tokens) and ask for want_count[e] of their rows
-// (indices within the entry, flat in want). Rows and sequences beyond the entries (a batch padded to a fixed
-// shape: S >= E, one padding row and one wanted row per padding sequence) get position -1, slot -1 and empty
-// tables: every kernel skips them. seq_info receives (start position, slot) per entry, *max_ctx the
-// longest context of the step.
+// (indices within the entry, flat in want). The step has a fixed shape of S >= E sequences and n rows:
+// pad_after padding sequences follow the first `lead` entries (so that a batch whose leading single-token
+// requests are counted in round numbers keeps its shape while their number changes), the rest follow the last
+// entry; a padding sequence has one padding row. Padding rows, the rows behind the last sequence and the
+// padding sequences get position -1 (the sequences: start position -1), slot -1 and empty tables: every kernel
+// skips them. The wanted rows of the
+// entries come first, in entry order; the remaining want slots name padding rows (row 0 when there are none
+// left), whose logits nobody reads. seq_info receives (start position, slot, first row) per entry, *max_ctx
+// the longest context of the step.
 GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok_count, const int32_t* tokens,
-                             const int* want_count, const int* want, int n, int S, int n_want, int max_pages,
-                             const long long* off, long long size, int32_t* host, const float* temperature,
-                             const float* uniform, int n_sampling, int* seq_info, int* max_ctx) {
+                             const int* want_count, const int* want, int lead, int pad_after, int n, int S, int n_want,
+                             int max_pages, const long long* off, long long size, int32_t* host,
+                             const float* temperature, const float* uniform, int n_sampling, int* seq_info,
+                             int* max_ctx) {
     Cache* c = static_cast<Cache*>(h);
     const int G = (int)c->groups.size();
-    if (S < E) return fail(BAD_VALUE, "fewer sequences than entries");
+    if (S < E + pad_after || lead < 0 || lead > E || pad_after < 0) return fail(BAD_VALUE, "fewer sequences than entries");
     long long rows = 0, wanted = 0;
     for (int e = 0; e < E; ++e) {
         rows += tok_count[e];
         wanted += want_count[e];
     }
-    if (rows + (S - E) > n || wanted + (S - E) > n_want) return fail(BAD_VALUE, "the entries do not fit the step's shape");
+    if (rows + (S - E) > n || wanted > n_want) return fail(BAD_VALUE, "the entries do not fit the step's shape");
     std::memset(host, 0, sizeof(int32_t) * (size_t)size);
     int32_t* h_tokens = host + off[0];
     int32_t* h_pos = host + off[1];
@@ -513,29 +519,41 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
         std::fill(host + off[9 + 2 * g], host + off[9 + 2 * g] + n, -1);
         std::fill(host + off[10 + 2 * g], host + off[10 + 2 * g] + (long long)S * max_pages, -1);
     }
-    int row = 0, wi = 0, longest = 0, tcur = 0, wcur = 0;
+    std::vector<int> pad_rows;
+    int row = 0, wi = 0, longest = 0, tcur = 0, wcur = 0, seq = 0;
+    auto pad_seq = [&]() {   // a padding sequence: one padding row, start position -1
+        h_row_seq[row] = seq;
+        h_first[seq] = row;
+        h_start[seq] = -1;
+        pad_rows.push_back(row);
+        ++row;
+        ++seq;
+    };
     for (int e = 0; e < E; ++e) {
+        if (e == lead)
+            for (int p = 0; p < pad_after; ++p) pad_seq();
         Request* req = find(c, rids[e]);
         if (!req) return fail(UNKNOWN_REQUEST, "unknown request");
         const int k = tok_count[e], start = req->length;
-        seq_info[2 * e] = start;
-        seq_info[2 * e + 1] = req->slot;
+        seq_info[3 * e] = start;
+        seq_info[3 * e + 1] = req->slot;
+        seq_info[3 * e + 2] = row;
         for (int i = 0; i < k; ++i) {
             h_tokens[row + i] = tokens[tcur + i];
             h_pos[row + i] = start + i;
-            h_row_seq[row + i] = e;
+            h_row_seq[row + i] = seq;
         }
         for (int i = 0; i < want_count[e]; ++i) h_want[wi++] = row + want[wcur + i];
-        h_first[e] = row;
-        h_start[e] = start;
-        h_slots[e] = req->slot;
+        h_first[seq] = row;
+        h_start[seq] = start;
+        h_slots[seq] = req->slot;
         for (int g = 0; g < G; ++g) {
             const Group& gr = c->groups[g];
             const std::vector<int>& table = gr.tables.find(rids[e])->second;
             if ((int)table.size() > max_pages) return fail(BAD_VALUE, "a block table is wider than the step's tables");
             if ((start + k + gr.page_size - 1) / gr.page_size > (int)table.size())
                 return fail(BAD_VALUE, "a request brings tokens for which no page was reserved");
-            std::memcpy(host + off[10 + 2 * g] + (long long)e * max_pages, table.data(), sizeof(int) * table.size());
+            std::memcpy(host + off[10 + 2 * g] + (long long)seq * max_pages, table.data(), sizeof(int) * table.size());
             int32_t* sl = host + off[9 + 2 * g] + row;
             for (int i = 0; i < k; ++i) {
                 const int pos = start + i;
@@ -546,14 +564,14 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
         tcur += k;
         wcur += want_count[e];
         longest = std::max(longest, start + k);
+        ++seq;
     }
-    for (int s = E; s < S; ++s) {   // padding sequences: one padding row each
-        h_row_seq[row] = s;
-        h_first[s] = row;
-        h_want[wi++] = row;
-        ++row;
-    }
+    if (lead == E)
+        for (int p = 0; p < pad_after; ++p) pad_seq();
+    while (seq < S) pad_seq();
     h_first[S] = row;
+    for (int r = row; r < n; ++r) h_row_seq[r] = S - 1;   // rows behind the last sequence: skipped by their position
+    for (size_t p = 0; wi < n_want; ++p) h_want[wi++] = p < pad_rows.size() ? pad_rows[p] : 0;
     if (temperature && uniform && n_sampling > 0) {
         std::memcpy(host + off[7], temperature, sizeof(float) * std::min(n_sampling, n_want));
         std::memcpy(host + off[8], uniform, sizeof(float) * std::min(n_sampling, n_want));

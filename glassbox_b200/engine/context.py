@@ -114,6 +114,7 @@ class StepContext:
         self.max_context = 0
         self.num_seqs = 0
         self.decode_only = False          # every sequence of the step brings exactly one row
+        self.leading_single = 0           # the first this many sequences bring one row each (rows 0 .. this - 1)
         self.temperature = self.uniform = None
         self.weight_order: Optional[WeightOrder] = None
         self.side_stream = None           # a second CUDA stream for work beside the main chain (prefetch)

@@ -80,7 +80,9 @@ class Engine:
         self.cache = CacheManager(groups, max_requests=self.max_requests, share_prefixes=share_prefixes,
                                   has_state=self.device_cache.has_state)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.scratch = Scratch(self.max_batch_tokens, self.dtype, self.device)
+        # a step recorded as a graph runs at a rounded shape: a few rows more than the tokens it brings
+        self._scratch_rows = self.max_batch_tokens + self.max_requests + 128
+        self.scratch = Scratch(self._scratch_rows, self.dtype, self.device)
         self.ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype)
         self.weight_order = WeightOrder()
         self.ctx.weight_order = self.weight_order
@@ -96,7 +98,7 @@ class Engine:
         self._graphs: Dict[tuple, dict] = {}
         self._layouts: Dict[tuple, dict] = {}
         self._seen: Dict[tuple, int] = {}
-        self.max_graphs = 48
+        self.max_graphs = 128
         self.graph_replays = 0
         self.sampled: Optional[torch.Tensor] = None
         self._sampled_host: Optional[torch.Tensor] = None
@@ -176,7 +178,7 @@ class Engine:
         self._layouts[key] = off
         return off
 
-    def _fill(self, entries, off, n, S, n_want, max_pages, sampling=None) -> np.ndarray:
+    def _fill(self, entries, off, n, S, n_want, max_pages, sampling=None, lead=0, pad_after=0) -> np.ndarray:
         """Host copy of the metadata block, written by the C++ host library from the cache manager's
         tables. Rows and sequences beyond the entries (a batch padded to a fixed shape) get position
         -1, slot -1 and empty tables: every kernel skips them."""
@@ -194,10 +196,9 @@ class Engine:
             temps = np.ascontiguousarray(sampling[0], dtype=np.float32)
             unif = np.ascontiguousarray(sampling[1], dtype=np.float32)
         info, self._max_ctx = self.cache.fill_step([e.request for e in entries], tok_count, tokens, want_count, want,
-                                                   n, S, n_want, max_pages, off["_array"], host, temps, unif)
-        first = np.concatenate(([0], np.cumsum(tok_count)[:-1])) if E else ()
+                                                   n, S, n_want, max_pages, off["_array"], host, temps, unif, lead, pad_after)
         self._seqs = [SeqInfo(request=e.request, slot=int(info[i, 1]), start_pos=int(info[i, 0]), n_rows=int(tok_count[i]),
-                              first_row=int(first[i])) for i, e in enumerate(entries)]
+                              first_row=int(info[i, 2])) for i, e in enumerate(entries)]
         return host
 
     def _bind(self, ctx: StepContext, dev: torch.Tensor, off, n, S, n_want, max_pages) -> None:
@@ -272,25 +273,39 @@ class Engine:
         else:
             logits = None
             max_rows = max(len(e.tokens) for e in entries)
-            small_logits = n_want * self.config.vocab_size * 4 <= (64 << 20)   # each graph owns its logits buffer
+            lead = 0                      # single-token requests at the head of the batch (the scheduler's order)
+            while lead < S and len(entries[lead].tokens) == 1:
+                lead += 1
+            small_logits = (n_want + 8) * self.config.vocab_size * 4 <= (64 << 20)   # each graph owns its logits buffer
             if self.use_graphs and not self.device_cache.has_state and small_logits:
-                # A step whose shape (rows, requests, longest run, wanted rows, table width) has been seen
-                # before is recorded once and replayed from then on: chunked prompts repeat their shape.
+                # A step is replayed as a CUDA graph of a rounded shape, so that batches which differ a little share
+                # one: the single-token requests at its head counted in eights (padding sequences behind them), the
+                # other requests in powers of two, the rows in 64s, the wanted rows in eights, the table width in
+                # powers of two (the flash kernel's grid covers the longest run such a shape can hold). A shape is recorded the second time it is seen: a
+                # portioned prompt repeats its shape, and so does a service that fills its token budget.
                 Pb = max(8, 1 << max(max_pages - 1, 0).bit_length())
-                key = ("step", n, S, max_rows, n_want, Pb)
+                lead_b = -(-lead // 8) * 8
+                rest = S - lead
+                rest_b = 1 << max(rest - 1, 0).bit_length() if rest else 0
+                S_b = lead_b + rest_b
+                n_b = lead_b + -(-(n - lead + rest_b - rest) // 64) * 64
+                want_b = -(-n_want // 8) * 8
+                tiles = -(-(n_b - lead_b) // 128)      # the most row tiles a request of this shape can have
+                key = ("step", n_b, lead_b, rest_b, want_b, Pb)
                 g = self._graphs.get(key)
-                off = self._layout(n, S, n_want, Pb)
+                off = self._layout(n_b, S_b, want_b, Pb)
                 if g is None:
                     if len(self._seen) > 4096:
                         self._seen.clear()
                     self._seen[key] = self._seen.get(key, 0) + 1
                     if self._seen[key] >= 2 and len(self._graphs) < self.max_graphs:
-                        host = self._fill(entries, off, n, S, n_want, Pb, sampling)
-                        g = self._capture(key, off, host, n, S, n_want, Pb, max_rows, decode_only=(n == S))
+                        host = self._fill(entries, off, n_b, S_b, want_b, Pb, sampling, lead, lead_b - lead)
+                        g = self._capture(key, off, host, n_b, S_b, want_b, Pb, tiles * 128, decode_only=(rest == 0),
+                                          lead=lead_b)
                         self.sampled = g["sampled"][:n_want] if sampling is not None else None
                         logits = g["logits"][:n_want]       # the warm-up run of the capture computed this step
                 else:
-                    host = self._fill(entries, off, n, S, n_want, Pb, sampling)
+                    host = self._fill(entries, off, n_b, S_b, want_b, Pb, sampling, lead, lead_b - lead)
                     self._stage_copy(host, g["meta"])
                     g["graph"].replay()
                     kernels.launch_count += g["nodes"]
@@ -309,6 +324,7 @@ class Engine:
                 ctx.seqs, ctx.max_context = self._seqs, self._max_ctx
                 ctx.max_rows_per_seq = max_rows
                 ctx.decode_only = (n == S)
+                ctx.leading_single = lead
                 logits = self.model.forward(ctx)
                 if sampling is not None and n_want:
                     self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
@@ -371,19 +387,20 @@ class Engine:
         self.graph_replays += 1
         return g["logits"][:S]
 
-    def _capture(self, key, off, host, n, S, n_want, Pb, max_rows, decode_only):
+    def _capture(self, key, off, host, n, S, n_want, Pb, max_rows, decode_only, lead=0):
         """Record the kernels of one step shape into a CUDA graph with a metadata block, logits and
         scratch of its own. The kernels run once outside capture first, on the metadata given (for a
         decode shape an all-padding batch; otherwise the real step, which is thereby computed), so
         that every scratch buffer exists; then they are recorded."""
         meta = torch.empty(off["_size"], dtype=torch.int32, device=self.device)
         ctx = StepContext(scratch=self.scratch, cache=self.device_cache, status=self.status, dtype=self.dtype,
-                          grow_scratch=Scratch(self.max_batch_tokens, self.dtype, self.device))
+                          grow_scratch=Scratch(self._scratch_rows, self.dtype, self.device))
         self._bind(ctx, meta, off, n, S, n_want, Pb)
         ctx.weight_order = self.weight_order
         ctx.side_stream = self.side_stream
         ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(S)]
         ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, max_rows, decode_only
+        ctx.leading_single = lead
         meta.copy_(torch.from_numpy(host))
         sampled = torch.zeros(max(n_want, 1), dtype=torch.int32, device=self.device)
 

@@ -91,43 +91,72 @@ class GqaAttention(Mixer):
         """att[row, head, :] = softmax over the row's visible keys; the kernel is picked by the shape
         of the batch: rows that are single decoded tokens share the keys of a request between
         several blocks (on the tensor cores in bfloat16 where the head size is one the kernel is built
-        for, else with float32 FMA); prompt portions take the flash kernel in bfloat16 at head sizes it
-        is built for; anything else takes the one-warp-per-(row, head) kernel."""
+        for, else with float32 FMA); prompt portions take a flash kernel in bfloat16 at head sizes one
+        is built for; anything else takes the one-warp-per-(row, head) kernel. A mixed batch that starts
+        with many single-token requests (the scheduler puts them first) is split: those rows go to the
+        decode kernel, the portions to the flash kernel, which would otherwise spend a 128-row tile per
+        head on each of them."""
         n = q.shape[0]
-        if ctx.decode_only and kernels.attention_decode_mma_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size):
+        if ctx.decode_only:
+            if self._attend_decode(ctx, q, att, cache, n):
+                return
+        else:
+            k = ctx.leading_single if ctx.leading_single * self.nh > SPLIT_MIXED_ABOVE else 0
+            if k and self._has_flash(q, att, cache) and self._attend_decode(ctx, q[:k], att[:k], cache, k):
+                self._attend_flash(ctx, q, att, cache, k)
+                return
+            if self._attend_flash(ctx, q, att, cache, 0):
+                return
+        kernels.attention_rows(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.nh,
+                               self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window, ctx.status)
+
+    def _attend_decode(self, ctx, q, att, cache, n: int) -> bool:
+        """Rows 0 .. n-1, one per request (request i is row i); False if no decode kernel takes the shape."""
+        if kernels.attention_decode_mma_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size):
             splits, block_keys = kernels.decode_mma_plan(n, self.nkv, self.hd, ctx.max_context)
             part_acc = ctx.scratch("decode_part_acc", (n, self.nh * 4 * splits * self.hd), torch.float32, grow=True)
             part_ml = ctx.scratch("decode_part_ml", (n, self.nh * 4 * splits * 2), torch.float32, grow=True)
             counters = ctx.zeros_once("decode_counters", ctx.max_rows * self.nh, torch.int32)
-            kernels.attention_decode_mma(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
+            kernels.attention_decode_mma(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq[:n], ctx.positions[:n],
                                          self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale,
                                          self.spec.window, splits, part_acc, part_ml, counters, ctx.status, block_keys)
-            return
-        if ctx.decode_only and self.hd % 16 == 0 and self.hd >= 16:
+            return True
+        if self.hd % 16 == 0 and self.hd >= 16:
             splits = kernels.decode_splits(n, self.nh, self.nkv, ctx.max_context)
             part_acc = part_ml = counters = None
             if splits > 1:
                 part_acc = ctx.scratch("decode_part_acc", (n, self.nh * splits * self.hd), torch.float32, grow=True)
                 part_ml = ctx.scratch("decode_part_ml", (n, self.nh * splits * 2), torch.float32, grow=True)
                 counters = ctx.zeros_once("decode_counters", ctx.max_rows * self.nh, torch.int32)
-            kernels.attention_decode(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
+            kernels.attention_decode(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq[:n], ctx.positions[:n],
                                      self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window,
                                      splits, part_acc, part_ml, counters, ctx.status)
-            return
-        if not ctx.decode_only and kernels.attention_prefill_tc_supported(q, att, self.nh, self.nkv, self.hd,
-                                                                          cache.page_size):
-            kernels.attention_prefill_tc(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row,
-                                         ctx.seq_start_pos, ctx.max_rows_per_seq, self.nh, self.nkv, self.hd,
-                                         cache.page_size, self.spec.scale, self.spec.window, ctx.status)
-            return
-        if not ctx.decode_only and kernels.attention_prefill_supported(q.dtype, self.nh, self.nkv, self.hd,
-                                                                       cache.page_size):
-            kernels.attention_prefill(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row,
-                                      ctx.seq_start_pos, ctx.max_rows_per_seq, self.nh, self.nkv, self.hd,
-                                      cache.page_size, self.spec.scale, self.spec.window, ctx.status)
-            return
-        kernels.attention_rows(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.nh,
-                               self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window, ctx.status)
+            return True
+        return False
 
+    def _has_flash(self, q, att, cache) -> bool:
+        return (kernels.attention_prefill_tc_supported(q, att, self.nh, self.nkv, self.hd, cache.page_size)
+                or kernels.attention_prefill_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size))
+
+    def _attend_flash(self, ctx, q, att, cache, first_seq: int) -> bool:
+        """The requests from ``first_seq`` on (runs of consecutive rows); False if no flash kernel takes the shape."""
+        tables = cache.block_tables[first_seq:]
+        first_row, start_pos = ctx.seq_first_row[first_seq:], ctx.seq_start_pos[first_seq:]
+        if kernels.attention_prefill_tc_supported(q, att, self.nh, self.nkv, self.hd, cache.page_size):
+            kernels.attention_prefill_tc(q, att, cache.k, cache.v, tables, first_row, start_pos, ctx.max_rows_per_seq,
+                                         self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window,
+                                         ctx.status)
+            return True
+        if kernels.attention_prefill_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size):
+            kernels.attention_prefill(q, att, cache.k, cache.v, tables, first_row, start_pos, ctx.max_rows_per_seq,
+                                      self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale, self.spec.window,
+                                      ctx.status)
+            return True
+        return False
+
+
+#: a mixed batch is split between the decode and the flash kernel when its leading single-token requests would
+#: otherwise add more 128-row tiles (one per request and head) than the GPU has SMs
+SPLIT_MIXED_ABOVE = 148
 
 register_part("mixer", "gqa_attention", GqaAttention, replace=True)

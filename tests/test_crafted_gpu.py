@@ -102,3 +102,30 @@ def test_window_edge_and_page_edges(tmp_path, dtype, page_size):
         for label, steps in (("whole", ru.whole(requests)), ("tail", ru.tail_one_by_one(requests, tail=20)),
                              ("portions", ru.changing_portions(requests))):
             check(info, ru.run_steps_inprocess(eng, steps), requests, dtype, f"query at {t_query} {label}")
+
+
+@pytest.mark.parametrize("window", [None, 37])
+def test_mixed_batches_split_between_the_decode_and_the_flash_kernel(tmp_path, monkeypatch, window):
+    """A batch that starts with single-token requests and goes on with prompt portions is served by two
+    attention kernels (here forced for any such batch; in service only for large ones): every row must still
+    read exactly its keys."""
+    from glassbox_b200.parts import attention
+    monkeypatch.setattr(attention, "SPLIT_MIXED_ABOVE", 0)
+    split_calls = []
+    real = attention.GqaAttention._attend_decode
+
+    def counting(self, ctx, q, att, cache, n):
+        if not ctx.decode_only:
+            split_calls.append((n, ctx.n))
+        return real(self, ctx, q, att, cache, n)
+    monkeypatch.setattr(attention.GqaAttention, "_attend_decode", counting)
+    info = toy_arch.write_probe_model(str(tmp_path / "m"), window=window, store=torch.bfloat16, seed=3, hd=64, nh=2, nkv=1)
+    rng = random.Random(4)
+    requests = {f"r{i}": [rng.randrange(info["vocab"]) for _ in range(n)] for i, n in enumerate([300, 65, 150, 40, 200, 90])}
+    for seed in (1, 2):
+        steps = ru.mixed(requests, random.Random(seed))
+        for st in steps:                                   # the scheduler's order: single tokens first
+            st["entries"].sort(key=lambda e: len(e["tokens"]) > 1)
+        eng = engine_for(str(tmp_path / "m"), "bfloat16", ru.live_tokens_needed(steps))
+        check(info, ru.run_steps_inprocess(eng, steps), requests, "bfloat16", f"window {window} split mixed {seed}")
+    assert any(0 < k < n for k, n in split_calls), "no batch was split: the test did not reach what it is about"
