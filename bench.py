@@ -100,7 +100,7 @@ def prefill_flops(c, T):
 def serving_workload(args):
     """Continuous batching on a mixed workload, after the reference's serving benchmark
     (crates/glassbox-bench/src/main.rs:296-318: random tokens, a spread of prompt and output lengths, a shared
-    prefix for some), all requests submitted at once. Wall-clock, host tokens in and sampled tokens out."""
+    prefix for some), two requests arriving per step. Wall-clock, host tokens in and sampled tokens out."""
     import numpy as np
     import torch
     import glassbox_b200
@@ -140,9 +140,12 @@ def serving_workload(args):
             torch.cuda.synchronize()
             launches0, replays0 = kernels.launch_count, eng.graph_replays
             t0 = time.perf_counter()
-            for p, n in zip(prompts, outs):
-                sched.submit(Request(prompt=p, max_tokens=n, sampler=SamplerConfig(temperature=0.8, seed=len(p))))
-            sched.run_until_idle()
+            todo = list(zip(prompts, outs))
+            while todo or not sched.is_idle():
+                for p, n in todo[:2]:     # two arrivals per step: later requests find the shared prefix cached
+                    sched.submit(Request(prompt=p, max_tokens=n, sampler=SamplerConfig(temperature=0.8, seed=len(p))))
+                del todo[:2]
+                sched.step()
             torch.cuda.synchronize()
             dt = time.perf_counter() - t0
             eng.check()
@@ -156,7 +159,8 @@ def serving_workload(args):
                        "dtype": "bf16", "data": "synthetic", "impl": "ours",
                        "config": {"model": f"SmolLM2-{model} shapes, random weights", "layers": shape["num_hidden_layers"],
                                   "requests": n_req, "prompt_len": "U(32,2048)", "output_len": "U(32,512)",
-                                  "portion": chunk, "max_seqs": max_seqs, "shared_prefix": 384, "page_size": 16}}
+                                  "portion": chunk, "max_seqs": max_seqs, "shared_prefix": 384, "page_size": 16,
+                                  "arrivals_per_step": 2}}
         print(json.dumps(results))
         return 0
     finally:
