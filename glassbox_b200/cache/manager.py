@@ -56,6 +56,8 @@ _SIGNATURES = {
     "gbh_cache_add": ([_P, _LL, _P, _I, _P], _I),
     "gbh_cache_reserve": ([_P, _LL, _I, _P, _P], _I),
     "gbh_cache_commit": ([_P, _LL, _P, _I], _I),
+    "gbh_cache_commit_many": ([_P, _I, _P, _P, _P], _I),
+    "gbh_cache_lengths": ([_P, _I, _P, _P], None),
     "gbh_cache_truncate": ([_P, _LL, _I], _I),
     "gbh_cache_fork": ([_P, _LL, _LL, _P], _I),
     "gbh_cache_free": ([_P, _LL], _I),
@@ -267,6 +269,21 @@ class CacheManager:
         code = self._lib.gbh_cache_commit(self._h, self._id(rid), toks.ctypes.data, toks.size)
         if code:
             self._raise(code, rid)
+
+    def commit_many(self, rids, tok_count: np.ndarray, tokens: np.ndarray) -> None:
+        """``commit`` for several requests in one call: request e brings ``tok_count[e]`` tokens, flat in
+        ``tokens`` (int32)."""
+        ids = np.fromiter((self._id(r) for r in rids), dtype=np.int64, count=len(rids))
+        code = self._lib.gbh_cache_commit_many(self._h, len(rids), ids.ctypes.data, tok_count.ctypes.data, tokens.ctypes.data)
+        if code:
+            self._raise(code)
+
+    def lengths(self, rids) -> np.ndarray:
+        """Lengths of several requests (-1 for one that does not exist)."""
+        ids = np.fromiter((self._ids.get(r, -1) for r in rids), dtype=np.int64, count=len(rids))
+        out = np.empty(max(len(rids), 1), dtype=np.int32)
+        self._lib.gbh_cache_lengths(self._h, len(rids), ids.ctypes.data, out.ctypes.data)
+        return out[:len(rids)]
 
     def truncate(self, rid, length: int) -> None:
         """Forget everything after the first ``length`` tokens (kv.rs:237-257). Not available

@@ -305,6 +305,17 @@ GBH_EXPORT int gbh_cache_commit(void* h, int64_t rid, const int32_t* tokens, int
     return OK;
 }
 
+// commit for several requests in one call: request e brings counts[e] tokens, flat in `tokens`.
+GBH_EXPORT int gbh_cache_commit_many(void* h, int n, const int64_t* rids, const int* counts, const int32_t* tokens) {
+    int at = 0;
+    for (int e = 0; e < n; ++e) {
+        const int code = gbh_cache_commit(h, rids[e], tokens + at, counts[e]);
+        if (code) return code;
+        at += counts[e];
+    }
+    return OK;
+}
+
 // Forget everything after the first `length` tokens (kv.rs:237-257). Not available once a window has
 // given pages back behind `length`.
 GBH_EXPORT int gbh_cache_truncate(void* h, int64_t rid, int length) {
@@ -389,6 +400,11 @@ GBH_EXPORT int gbh_cache_has(void* h, int64_t rid) { return find(static_cast<Cac
 GBH_EXPORT int gbh_cache_length(void* h, int64_t rid) {
     Request* r = find(static_cast<Cache*>(h), rid);
     return r ? r->length : -1;
+}
+
+// Lengths of several requests in one call (-1 for an unknown one).
+GBH_EXPORT void gbh_cache_lengths(void* h, int n, const int64_t* rids, int* out) {
+    for (int e = 0; e < n; ++e) out[e] = gbh_cache_length(h, rids[e]);
 }
 
 GBH_EXPORT int gbh_cache_slot(void* h, int64_t rid) {

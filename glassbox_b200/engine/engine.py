@@ -90,6 +90,7 @@ class Engine:
         self.ctx.side_stream = self.side_stream
         self._meta_dev = torch.empty(1 << 16, dtype=torch.int32, device=self.device)
         self._stage = [torch.empty(1 << 16, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._stage_np = [t.numpy() for t in self._stage]
         self._stage_events = [None] * len(self._stage)
         self._stage_next = 0
         self.steps = 0
@@ -133,24 +134,26 @@ class Engine:
                 kernels.copy_pages(self.device_cache.k[g], self.device_cache.v[g], t)
 
     # ----------------------------------------------------------------------- step metadata
-    def _stage_copy(self, host: np.ndarray, dev: torch.Tensor) -> None:
-        """One host-to-device copy of the step's metadata through pinned staging buffers (a ring,
-        so that a buffer is not rewritten while its copy may still be in flight)."""
-        n = host.size
-        if n > self._stage[0].numel():
-            cap = 1 << int(n - 1).bit_length()
+    def _stage_buffer(self, size: int) -> np.ndarray:
+        """The next pinned staging buffer of the ring as a numpy array of ``size`` int32 (a ring, so that a
+        buffer is not rewritten while its copy may still be in flight)."""
+        if size > self._stage[0].numel():
+            cap = 1 << int(size - 1).bit_length()
             self._stage = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(len(self._stage))]
+            self._stage_np = [t.numpy() for t in self._stage]
             self._stage_events = [None] * len(self._stage)
-        i = self._stage_next
-        self._stage_next = (i + 1) % len(self._stage)
+        i = self._stage_next = (self._stage_next + 1) % len(self._stage)
         if self._stage_events[i] is not None:
             self._stage_events[i].synchronize()
-        stage = self._stage[i]
-        stage.numpy()[:n] = host
-        dev[:n].copy_(stage[:n], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._stage_events[i] = ev
+        return self._stage_np[i][:size]
+
+    def _stage_copy(self, host: np.ndarray, dev: torch.Tensor) -> None:
+        """One host-to-device copy of the step's metadata; ``host`` is the array ``_stage_buffer`` gave last."""
+        i, n = self._stage_next, host.size
+        dev[:n].copy_(self._stage[i][:n], non_blocking=True)
+        if self._stage_events[i] is None:
+            self._stage_events[i] = torch.cuda.Event()
+        self._stage_events[i].record()
         self.h2d_bytes_last = n * 4
 
     def _layout(self, n: int, S: int, n_want: int, max_pages: int):
@@ -190,7 +193,8 @@ class Engine:
         else:
             tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]).astype(np.int32)
         want = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(want_count.sum()))
-        host = np.empty(off["_size"], dtype=np.int32)
+        self._tok_count, self._tokens = tok_count, tokens      # kept for the commit that follows the step
+        host = self._stage_buffer(off["_size"])
         temps = unif = None
         if sampling is not None:
             temps = np.ascontiguousarray(sampling[0], dtype=np.float32)
@@ -225,22 +229,21 @@ class Engine:
             raise ValueError("a step needs at least one token")
         if n > self.max_batch_tokens:
             raise ValueError(f"a step of {n} tokens exceeds max_batch_tokens {self.max_batch_tokens}")
-        seen = set()
-        for e in entries:
-            if not self.cache.has(e.request):
+        if len({e.request for e in entries}) != len(entries):
+            raise ValueError("a request appears twice in one step")
+        lengths = self.cache.lengths([e.request for e in entries])
+        for e, have in zip(entries, lengths):
+            k = len(e.tokens)
+            if have < 0:
                 raise KeyError(f"unknown request {e.request!r}; add_request first")
-            if e.request in seen:
-                raise ValueError(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
-            if not len(e.tokens):
+            if not k:
                 raise ValueError(f"request {e.request!r} brings no tokens")
-            end = self.cache.length(e.request) + len(e.tokens)
-            if end > cfg.max_position:
-                raise ValueError(f"request {e.request!r} would reach {end} tokens, beyond max_position "
+            if have + k > cfg.max_position:
+                raise ValueError(f"request {e.request!r} would reach {have + k} tokens, beyond max_position "
                                  f"{cfg.max_position}")
             for w in e.want:
-                if not 0 <= w < len(e.tokens):
-                    raise ValueError(f"request {e.request!r}: wanted index {w} outside its {len(e.tokens)} tokens")
+                if not 0 <= w < k:
+                    raise ValueError(f"request {e.request!r}: wanted index {w} outside its {k} tokens")
         return n
 
     def step(self, entries: Sequence[StepEntry], reserve: bool = True, commit: bool = True,
@@ -330,8 +333,7 @@ class Engine:
                     self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
                     kernels.sample(logits, self.sampled, ctx.temperature, ctx.uniform)
         if commit:
-            for e in entries:
-                self.cache.commit(e.request, e.tokens)
+            self.cache.commit_many([e.request for e in entries], self._tok_count, self._tokens)
         self.steps += 1
         return logits
 
@@ -378,8 +380,8 @@ class Engine:
         off = self._layout(Sb, Sb, Sb, Pb)
         if sampling is None:
             sampling = ([0.0] * S, [0.0] * S)
+        g = self._decode_graph(Sb, Pb)          # (may fill a blank batch of its own: before this step's metadata)
         host = self._fill(entries, off, Sb, Sb, Sb, Pb, sampling)
-        g = self._decode_graph(Sb, Pb)
         self._stage_copy(host, g["meta"])
         g["graph"].replay()
         kernels.launch_count += g["nodes"]
