@@ -23,7 +23,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-SHAPES = {  # BASELINE.json configs[2..4]
+SHAPES = {  # the three SmolLM2 sizes that Glassbox benchmarks (its README.md:30-34)
     "135m": dict(num_hidden_layers=30, hidden_size=576, num_attention_heads=9, num_key_value_heads=3,
                  intermediate_size=1536, vocab_size=49152, rope_theta=100000.0, rms_norm_eps=1e-5,
                  tie_word_embeddings=True, max_position_embeddings=8192),

@@ -1,5 +1,8 @@
 """glassbox_b200: a small, whole inference engine for one B200, for the Llama-family decoder
-that Glassbox runs (SmolLM2). See DESIGN.md at the repository root."""
+that Glassbox runs (SmolLM2): typed configuration and an architecture registry (``config``, ``models``),
+safetensors weights (``weights``), layers put together from parts (``parts``), a paged cache manager
+(``cache``), one step function, a scheduler and trace replay (``engine``), sampling, and hand-written CUDA
+kernels for sm_100a (``csrc``, called through ``kernels``)."""
 from . import models  # noqa: F401  (registers the architectures)
 from . import parts  # noqa: F401   (registers the parts)
 from .config import ConfigError, load_config, parse_config, register_architecture
