@@ -73,6 +73,7 @@ _SIGNATURES = {
     "gbh_cache_hashes": ([_P, _I, _P, _P, _I, _P], _I),
     "gbh_cache_ids": ([_P, _I, _P, _I], _I),
     "gbh_chain_hash": ([ctypes.c_uint64, _P, _I], ctypes.c_uint64),
+    "gbh_plan_step": ([_P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P], _I),
     "gbh_fill_step": ([_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _I, _P, _P], _I),
 }
 _lib = None
@@ -311,6 +312,29 @@ class CacheManager:
         i = self._ids.pop(rid, None)
         if i is not None:
             self._lib.gbh_cache_free(self._h, i)
+
+    # ------------------------------------------------------------------------------ a scheduler step's plan
+    def plan_step(self, rids, remaining, budget: int):
+        """Plan one step of continuous batching over the running requests (admission order, with the tokens
+        each still has to run) and reserve its pages, in the library (see ``gbh_plan_step``): decoding requests
+        first, then prompt portions, under the token budget; when pages run out the most recently admitted
+        request is preempted and what it holds given back. Returns (plan as [(index, tokens)], copy-on-write
+        triples, number of preempted requests counted from the end of the list, whether a lone request did
+        not fit). The caller forgets the preempted requests with ``free_request`` (their pages are gone already)."""
+        n = len(rids)
+        ids = np.fromiter((self._id(r) for r in rids), dtype=np.int64, count=n)
+        rem = _ints(remaining)
+        out = np.empty(2 * n + 3 * max(len(self.groups), 1) * max(n, 1) + 4, dtype=np.int32)
+        plan_idx, plan_n, copies, tail = out[:n], out[n:2 * n], out[2 * n:-4], out[-4:]
+        code = self._lib.gbh_plan_step(self._h, n, ids.ctypes.data, rem.ctypes.data, int(budget), plan_idx.ctypes.data,
+                                       plan_n.ctypes.data, tail[0:].ctypes.data, copies.ctypes.data, tail[1:].ctypes.data,
+                                       tail[2:].ctypes.data, tail[3:].ctypes.data)
+        if code:
+            self._raise(code)
+        k, nc = int(tail[0]), int(tail[1])
+        plan = list(zip(plan_idx[:k].tolist(), plan_n[:k].tolist()))
+        triples = [(int(copies[3 * j]), int(copies[3 * j + 1]), int(copies[3 * j + 2])) for j in range(nc)]
+        return plan, triples, int(tail[2]), bool(tail[3])
 
     # ------------------------------------------------------------------------------ a step's metadata
     def fill_step(self, rids, tok_count: np.ndarray, tokens: np.ndarray, want_count: np.ndarray, want: np.ndarray,

@@ -493,6 +493,66 @@ GBH_EXPORT int gbh_cache_ids(void* h, int group, int64_t* out, int cap) {
     return i;
 }
 
+// ------------------------------------------------------------------------------ a scheduler step's plan
+// What one step of continuous batching computes, and with which pages (the policy of
+// crates/glassbox-server/src/scheduler.rs:283-330). The running requests are given in admission order with the
+// number of tokens each still has to run. Requests with one token left (decoding) come first, then the others
+// (prompt portions), each taking what is left of the token budget. Room is then reserved entry by entry; when the
+// pages run out, the most recently admitted request is preempted (everything it holds is given back, its plan
+// entry dropped) and the entry tried again; a lone request that does not fit is reported instead.
+// Out: plan_idx / plan_n (index into the running list, tokens), *n_plan; copies (group, source page, destination
+// page triples of copy-on-write work, at most one per group and entry), *n_copies; *n_preempted (the last that
+// many running requests, latest first); *lone_failed.
+GBH_EXPORT int gbh_plan_step(void* h, int n_running, const int64_t* rids, const int* remaining, int budget, int* plan_idx,
+                             int* plan_n, int* n_plan, int* copies, int* n_copies, int* n_preempted, int* lone_failed) {
+    Cache* c = static_cast<Cache*>(h);
+    std::vector<std::pair<int, int>> plan;
+    for (int pass = 0; pass < 2 && budget > 0; ++pass)
+        for (int i = 0; i < n_running && budget > 0; ++i) {
+            if ((remaining[i] > 1) != (pass == 1)) continue;
+            const int n = std::min(remaining[i], budget);
+            plan.emplace_back(i, n);
+            budget -= n;
+        }
+    int live = n_running, nc = 0, pre = 0;
+    *lone_failed = 0;
+    size_t k = 0;
+    std::vector<int> one(3 * std::max<size_t>(c->groups.size(), 1));
+    while (k < plan.size()) {
+        int got = 0;
+        const int code = gbh_cache_reserve(h, rids[plan[k].first], plan[k].second, one.data(), &got);
+        if (code == OK) {
+            std::memcpy(copies + 3 * nc, one.data(), sizeof(int) * 3 * got);
+            nc += got;
+            ++k;
+            continue;
+        }
+        if (code != OUT_OF_PAGES) return code;
+        if (live == 1) {
+            *lone_failed = 1;
+            plan.clear();
+            break;
+        }
+        const int victim = --live;
+        gbh_cache_free(h, rids[victim]);
+        ++pre;
+        for (size_t p = 0; p < plan.size(); ++p)
+            if (plan[p].first == victim) {
+                plan.erase(plan.begin() + p);
+                if (p < k) --k;
+                break;
+            }
+    }
+    for (size_t p = 0; p < plan.size(); ++p) {
+        plan_idx[p] = plan[p].first;
+        plan_n[p] = plan[p].second;
+    }
+    *n_plan = (int)plan.size();
+    *n_copies = nc;
+    *n_preempted = pre;
+    return OK;
+}
+
 // ------------------------------------------------------------------------------ a step's metadata
 // Fills the int32 block that a step copies to the device. Its sections start at the offsets given:
 //   off[0..8]: tokens [n], positions [n], row_seq [n], want [n_want], seq_first_row [S+1], seq_start_pos [S],

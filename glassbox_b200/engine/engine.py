@@ -124,7 +124,10 @@ class Engine:
     def reserve(self, request, n: int) -> None:
         """Make room for ``n`` more tokens of ``request`` (raises ``OutOfPages``; nothing changes
         then) and carry out any copy-on-write on the device."""
-        copies = self.cache.reserve(request, n)
+        self.run_copies(self.cache.reserve(request, n))
+
+    def run_copies(self, copies) -> None:
+        """Carry out copy-on-write work, (group, source page, destination page) triples, on the device."""
         if copies:
             by_group: Dict[int, List[List[int]]] = {}
             for g, src, dst in copies:

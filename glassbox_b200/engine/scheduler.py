@@ -179,39 +179,20 @@ class Scheduler:
         if not self.running:
             return False
 
-        plan: List[List[int]] = []  # [running index, tokens]
-        budget = cfg.token_budget
-        order = sorted(range(len(self.running)),
-                       key=lambda i: len(self.running[i].tokens) - self.running[i].computed > 1)
-        for i in order:
-            if budget == 0:
-                break
-            s = self.running[i]
-            n = min(len(s.tokens) - s.computed, budget)
-            plan.append([i, n])
-            budget -= n
-
-        k = 0
-        while k < len(plan):
-            i, n = plan[k]
-            try:
-                self.backend.reserve(self.running[i].id, n)
-                k += 1
-            except OutOfPages:
-                if len(self.running) == 1:
-                    s = self.running.pop()
-                    finished.append(s.id)
-                    self._finish(s, LENGTH)
-                    plan = []
-                    break
-                preempted.append(self._preempt_last())
-                victim = len(self.running)
-                for p, (j, _) in enumerate(plan):
-                    if j == victim:
-                        del plan[p]
-                        if p < k:
-                            k -= 1
-                        break
+        # Planning under the token budget (decoding requests first, then prompt portions), reserving pages, and
+        # preempting the most recently admitted request when they run out, happen in the cache library in one
+        # call; what is left here is to forget the preempted requests and to end a lone request that did not fit.
+        remaining = [len(s.tokens) - s.computed for s in self.running]
+        plan, copies, n_preempted, lone_failed = cache.plan_step([s.id for s in self.running], remaining, cfg.token_budget)
+        run_copies = getattr(self.backend, "run_copies", None)
+        if copies and run_copies is not None:
+            run_copies(copies)
+        for _ in range(n_preempted):
+            preempted.append(self._preempt_last())
+        if lone_failed:
+            s = self.running.pop()
+            finished.append(s.id)
+            self._finish(s, LENGTH)
         if not plan:
             self._record(t0, [], preempted, finished)
             return not self.is_idle()
