@@ -164,3 +164,30 @@ def test_temperature_sampling_is_seeded_per_request(model_dirs):
         return [s.finished[i].tokens for i in ids]
     a, b = run(), run()
     assert a == b and a[0] == a[2] and a[0] != a[1]
+
+
+def test_the_native_plan_of_a_step_decodes_first_fills_the_budget_and_preempts_the_latest():
+    from glassbox_b200.cache import CacheManager, GroupSpec
+    m = CacheManager([GroupSpec(8, 16)], max_requests=8, share_prefixes=False)
+    for rid, have in (("a", 20), ("b", 0), ("c", 33)):          # a and c decode; b still has its prompt to run
+        m.add_request(rid)
+        if have:
+            m.reserve(rid, have)
+            m.commit(rid, list(range(have)))
+    # 8 pages: a holds 2, c holds 3; b may take what fits the budget
+    plan, copies, preempted, lone = m.plan_step(["a", "b", "c"], [1, 500, 1], 34)
+    assert plan == [(0, 1), (2, 1), (1, 32)] and not copies and preempted == 0 and not lone
+    m.commit("a", [1]); m.commit("c", [1]); m.commit("b", list(range(32)))
+    m.check_invariants()
+    assert m.free_pages() == 1
+    # the next portion of b needs 2 pages, one is free: c, admitted last, gives way (its 3 pages come back)
+    plan, copies, preempted, lone = m.plan_step(["a", "b", "c"], [1, 468, 1], 34)
+    assert preempted == 1 and not lone and plan == [(0, 1), (1, 32)]
+    assert m.length("c") == -1                                   # the library has forgotten it
+    m.free_request("c")                                          # and now the wrapper has too
+    m.check_invariants()
+    # a lone request that cannot fit is reported, nothing is reserved for it
+    lone_m = CacheManager([GroupSpec(2, 16)], max_requests=2, share_prefixes=False)
+    lone_m.add_request("x")
+    plan, copies, preempted, lone = lone_m.plan_step(["x"], [100], 64)
+    assert lone and plan == [] and preempted == 0 and lone_m.free_pages() == 2
