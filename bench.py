@@ -245,6 +245,7 @@ def main():
                 one(s)
             torch.cuda.synchronize()
             launches0 = kernels.launch_count
+            print(f"decode batch {batch}: {launches0} kernel launches before the timed steps (for ncu -s)", file=sys.stderr)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for s in range(warm, warm + steps):
