@@ -39,7 +39,8 @@ def test_embed(dtype, n, d, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n, d, eps", [(1, 7, 1e-5), (3, 576, 1e-6), (17, 1537, 3e-6), (9, 8192, 1e-5)])
+@pytest.mark.parametrize("n, d, eps", [(1, 7, 1e-5), (3, 576, 1e-6), (17, 1537, 3e-6), (9, 8192, 1e-5),
+                                       (2048, 576, 1e-5), (13, 2048, 1e-5), (5, 4096, 1e-6), (21, 132, 1e-5)])
 def test_rmsnorm(dtype, n, d, eps):
     from glassbox_b200 import kernels
     x = torch.randn(n + 3, d, device=DEV) * 3
