@@ -52,6 +52,10 @@ class LLM:
         tokens (one list, or a list of lists in the order given)."""
         single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple, np.ndarray))
         batch = [prompts] if single else list(prompts)
+        limit = self.engine.max_position
+        for i, p in enumerate(batch):
+            if not 0 < len(p) <= limit:
+                raise ValueError(f"prompt {i} has {len(p)} tokens; a prompt needs between 1 and max_position = {limit}")
         ids = []
         for i, p in enumerate(batch):
             cfg = SamplerConfig(temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p,
@@ -66,6 +70,12 @@ class LLM:
             reasons = [d.reason for d in done]
             return (outs[0], reasons[0]) if single else (outs, reasons)
         return outs[0] if single else outs
+
+
+    def fork(self, request_id: int, **kwargs) -> int:
+        """Fork a request that is in flight (see ``Scheduler.fork``); for callers that drive
+        ``llm.scheduler.submit`` / ``step`` themselves."""
+        return self.scheduler.fork(request_id, **kwargs)
 
 
 def load(model_dir: str, dtype: str = "bfloat16", **kwargs) -> LLM:

@@ -85,7 +85,11 @@ __global__ void __launch_bounds__(2 * DK) attention_decode_kernel(
     long long* rowoff = reinterpret_cast<long long*>(red + 2 * 4 * GT);  // [2][DK]
     __shared__ int is_last;
 
-    const int pos = positions[row];
+    int pos = positions[row];
+    if (pos >= 0 && pos / page_size >= max_pages) {   // a position the block table does not reach: reported, and the
+        if (tid == 0) atomicOr(status, GB_STATUS_BAD_POSITION);   // row is treated as padding (nothing is read)
+        pos = -1;
+    }
     T* orow = out + (size_t)row * out_stride;
     if (pos < 0) {  // padding row
         if (split == 0)

@@ -89,7 +89,11 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(
     // block table: step metadata that no kernel writes) runs before it waits for its predecessor,
     // which wrote the queries and this step's keys and values.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int pos = positions[row];
+    int pos = positions[row];
+    if (pos >= 0 && (pos >> page_shift) >= max_pages) {   // a position the block table does not reach: reported, and the
+        if (tid == 0) atomicOr(status, GB_STATUS_BAD_POSITION);   // row is treated as padding (nothing is read)
+        pos = -1;
+    }
     __nv_bfloat16* orow = out + (size_t)row * out_stride;
     if (pos < 0) {  // padding row
         asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -26,7 +26,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_rows_kernel(
     if (task >= (long long)n * nh) return;
     const int row = (int)(task / nh), head = (int)(task % nh);
     const int kvh = head / (nh / nkv);
-    const int pos = positions[row];
+    int pos = positions[row];
+    if (pos >= 0 && pos / page_size >= max_pages) {   // a position the block table does not reach: reported, the row reads nothing
+        if (lane == 0) atomicOr(status, GB_STATUS_BAD_POSITION);
+        pos = -1;
+    }
     const int* table = block_tables + (size_t)row_seq[row] * max_pages;
 
     const T* qrow = q + (size_t)row * q_stride + head * hd;

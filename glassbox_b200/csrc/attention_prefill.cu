@@ -64,7 +64,11 @@ __global__ void __launch_bounds__(256) attention_prefill_kernel(
     const int row0 = seq_first_row[seq];
     const int nrows = seq_first_row[seq + 1] - row0;
     if (qt * PF_BM >= nrows) return;
-    const int start_pos = seq_start_pos[seq];
+    int start_pos = seq_start_pos[seq];
+    if (start_pos >= 0 && ((start_pos + nrows - 1) >> page_shift) >= max_pages) {   // rows beyond the block table:
+        if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_POSITION);             // reported, treated as padding
+        start_pos = -1;
+    }
     if (start_pos < 0) {                          // a padding sequence of a fixed-shape batch (uniform for the block):
         for (int i = threadIdx.x; i < nrows * (HD / 2); i += blockDim.x)   // its rows read as zeros downstream
             *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + i / (HD / 2)) * out_stride + (size_t)head * HD + (i % (HD / 2)) * 2) = 0u;

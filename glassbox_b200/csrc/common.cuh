@@ -19,7 +19,7 @@ enum GbDtype : int { GB_F32 = 0, GB_BF16 = 1 };
 enum GbStatusBits : int {
     GB_STATUS_BAD_TOKEN = 1,      // a token id outside the vocabulary
     GB_STATUS_BAD_SLOT = 2,       // a cache slot or page id outside the pool
-    GB_STATUS_BAD_POSITION = 4,   // a position outside the rotary table
+    GB_STATUS_BAD_POSITION = 4,   // a position outside the rotary table, or beyond what a block table covers
     GB_STATUS_WAIT_TIMEOUT = 8,   // a bounded wait inside a kernel gave up
 };
 

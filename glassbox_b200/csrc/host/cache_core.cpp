@@ -252,6 +252,16 @@ GBH_EXPORT int gbh_cache_reserve(void* h, int64_t rid, int n, int* copies, int* 
             ++nc;
             gr.release(old);
             table[i] = page;
+        } else if (n > 0 && req->length % gr.page_size && req->length / gr.page_size < (int)table.size()) {
+            // The write lands in a partly filled page that this request holds alone. If the page is still
+            // indexed under the hash of what it held when it was full (a fork truncated into it while the
+            // other holder was alive, then that holder went away), the index must forget it now: its
+            // contents are about to change.
+            const int p = table[req->length / gr.page_size];
+            if (p >= 0 && gr.hashed[p]) {
+                gr.by_hash.erase(gr.page_hash[p]);
+                gr.hashed[p] = 0;
+            }
         }
         for (int k = 0; k < fresh[g]; ++k) table.push_back(gr.alloc());
     }
@@ -267,7 +277,10 @@ GBH_EXPORT int gbh_cache_commit(void* h, int64_t rid, const int32_t* tokens, int
     if (!req) return fail(UNKNOWN_REQUEST, "unknown request");
     const int start = req->length;
     req->length += n;
-    if ((int)req->tokens.size() < req->length) {
+    // The tokens named at admission are what the caller expected to run; what is hashed must be what ran.
+    const bool as_expected = (int)req->tokens.size() >= req->length &&
+                             (n == 0 || std::memcmp(req->tokens.data() + start, tokens, sizeof(int32_t) * (size_t)n) == 0);
+    if (!as_expected) {
         req->tokens.resize(std::min<size_t>(req->tokens.size(), (size_t)start));
         req->tokens.insert(req->tokens.end(), tokens, tokens + n);
     }
@@ -514,16 +527,16 @@ GBH_EXPORT int gbh_plan_step(void* h, int n_running, const int64_t* rids, const 
             plan.emplace_back(i, n);
             budget -= n;
         }
-    int live = n_running, nc = 0, pre = 0;
+    int live = n_running, pre = 0;
     *lone_failed = 0;
     size_t k = 0;
     std::vector<int> one(3 * std::max<size_t>(c->groups.size(), 1));
+    std::vector<std::vector<int>> work(plan.size());   // copy-on-write triples of each reserved plan entry
     while (k < plan.size()) {
         int got = 0;
         const int code = gbh_cache_reserve(h, rids[plan[k].first], plan[k].second, one.data(), &got);
         if (code == OK) {
-            std::memcpy(copies + 3 * nc, one.data(), sizeof(int) * 3 * got);
-            nc += got;
+            work[k].assign(one.begin(), one.begin() + 3 * got);
             ++k;
             continue;
         }
@@ -531,6 +544,7 @@ GBH_EXPORT int gbh_plan_step(void* h, int n_running, const int64_t* rids, const 
         if (live == 1) {
             *lone_failed = 1;
             plan.clear();
+            work.clear();
             break;
         }
         const int victim = --live;
@@ -538,14 +552,20 @@ GBH_EXPORT int gbh_plan_step(void* h, int n_running, const int64_t* rids, const 
         ++pre;
         for (size_t p = 0; p < plan.size(); ++p)
             if (plan[p].first == victim) {
+                // Its destination pages went back to the pool with everything else it held and may be handed
+                // out again in this very plan: its copies must not run.
                 plan.erase(plan.begin() + p);
+                work.erase(work.begin() + p);
                 if (p < k) --k;
                 break;
             }
     }
+    int nc = 0;
     for (size_t p = 0; p < plan.size(); ++p) {
         plan_idx[p] = plan[p].first;
         plan_n[p] = plan[p].second;
+        std::memcpy(copies + 3 * nc, work[p].data(), sizeof(int) * work[p].size());
+        nc += (int)work[p].size() / 3;
     }
     *n_plan = (int)plan.size();
     *n_copies = nc;

@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(256) kv_prefetch_kernel(const unsigned char* _
                                                           long long num_pages, long long tile_bytes, int window) {
     const int row = blockIdx.y;
     const int pos = positions[row];
-    if (pos < 0) return;
+    if (pos < 0 || pos / page_size >= max_pages) return;   // padding, or a position the block table does not reach
     const int* table = block_tables + (size_t)row_seq[row] * max_pages;
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int page_lo = first / page_size, page_hi = pos / page_size;

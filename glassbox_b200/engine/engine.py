@@ -253,8 +253,9 @@ class Engine:
              sampling=None) -> torch.Tensor:
         """Run one batch. Returns float32 logits ``[total wanted, vocab]`` on the device, in the
         order of the entries and of each entry's ``want``; the tensor is scratch that the next
-        step overwrites. With ``reserve`` False the caller has already reserved room for every
-        entry (the scheduler does, to decide about preemption first). With ``sampling`` =
+        step overwrites. With ``reserve`` True room is reserved for every entry first, all or nothing:
+        on ``OutOfPages`` no request holds more pages than before. With ``reserve`` False the caller has
+        already reserved room for every entry (the scheduler does, to decide about preemption first). With ``sampling`` =
         (temperatures, uniforms), one per wanted row, the sampling kernel runs in the same step
         and ``self.sampled`` holds the chosen token of each wanted row (int32, on the device).
 
@@ -264,8 +265,17 @@ class Engine:
         n = self._validate(entries)
         self.sampled = None
         if reserve:
-            for e in entries:
-                self.reserve(e.request, len(e.tokens))
+            done = []
+            try:
+                for e in entries:
+                    self.reserve(e.request, len(e.tokens))
+                    done.append(e.request)
+            except OutOfPages:
+                # all or nothing: the pages that earlier entries of this step were given go back (a page copied
+                # for a write stays with its request: it holds the same keys as the page it was copied from)
+                for rid in done:
+                    self.cache.truncate(rid, self.cache.length(rid))
+                raise
         self.device_cache.zero_slots(self.cache.drain_fresh_slots())
         n_groups = len(self.cache.groups)
         S = len(entries)

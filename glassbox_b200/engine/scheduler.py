@@ -108,6 +108,11 @@ class Scheduler:
     def submit(self, req: Request) -> int:
         if not len(req.prompt):
             raise ValueError("a request needs at least one prompt token")
+        limit = getattr(self.backend, "max_position", None)
+        if limit is not None and len(req.prompt) > limit:
+            # refused here, before it can fail inside a step that other requests share
+            # (the reference refuses such prompts at its door too: crates/glassbox-server/src/http.rs:199-208)
+            raise ValueError(f"a prompt of {len(req.prompt)} tokens is longer than the model's max_position {limit}")
         sid = self.next_id
         self.next_id += 1
         self.metrics.prompt_tokens += len(req.prompt)
@@ -130,6 +135,38 @@ class Scheduler:
                 self.waiting.remove(s)
                 self._finish(s, ABORTED)
                 return
+
+    def fork(self, sid: int, sampler: Optional[SamplerConfig] = None, max_tokens: Optional[int] = None) -> int:
+        """A new request that starts as a copy of request ``sid`` as it stands: everything the parent has (its
+        prompt and what it generated so far) is the child's prompt, and the child shares the parent's pages until
+        either writes (crates/glassbox-core/src/kv.rs:260-266). Without ``sampler`` the child takes the parent's
+        sampler with its random state as it stands (it then generates what the parent generates); with one it
+        goes its own way. ``max_tokens`` counts the child's own new tokens (default: what the parent has left).
+        The parent must be running or waiting; a child of a waiting parent simply waits behind it."""
+        import copy
+        parent = next((s for s in self.running if s.id == sid), None)
+        waiting = next((s for s in self.waiting if s.id == sid), None) if parent is None else None
+        src = parent or waiting
+        if src is None:
+            raise KeyError(f"request {sid} is neither running nor waiting")
+        left = max(src.req.max_tokens - src.generated, 0)
+        req = Request(prompt=list(src.tokens), max_tokens=left if max_tokens is None else int(max_tokens),
+                      sampler=sampler or src.req.sampler, stop=src.req.stop, on_token=src.req.on_token,
+                      on_done=src.req.on_done)
+        cid = self.next_id
+        self.next_id += 1
+        child = _Seq(cid, req, time.perf_counter())
+        if sampler is None:
+            child.sampler = copy.deepcopy(src.sampler)
+        self.metrics.prompt_tokens += len(req.prompt)
+        if parent is None or len(self.running) >= self.config.max_seqs or not self.backend.cache.free_slots:
+            self.waiting.insert(self.waiting.index(waiting) + 1, child) if waiting is not None else self.waiting.append(child)
+            return cid
+        self.backend.fork(parent.id, cid)
+        child.computed = parent.computed
+        child.admitted_before = True
+        self.running.append(child)
+        return cid
 
     def _finish(self, s: _Seq, reason: str) -> None:
         if self.backend.cache.has(s.id):

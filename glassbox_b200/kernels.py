@@ -20,7 +20,7 @@ F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a cache slot or page id outside the pool",
-               4: "a position outside the rotary table", 8: "a bounded wait inside a kernel gave up"}
+               4: "a position outside the rotary table or beyond a block table", 8: "a bounded wait inside a kernel gave up"}
 
 
 class KernelError(RuntimeError):

@@ -27,6 +27,10 @@ class PlainBackend:
         self.cache.free_request(rid)
         self.tokens.pop(rid, None)
 
+    def fork(self, parent, child):
+        self.cache.fork(parent, child)
+        self.tokens[child] = list(self.tokens[parent])
+
     def reserve(self, rid, n):
         self.cache.reserve(rid, n)
 

@@ -112,8 +112,9 @@ def _load(model_dir):
     return _LOADED[key]
 
 
-def forward_logits(model_dir, tokens, window=None):
-    """Whole sequence, no cache: model.rs:207-362 with every row wanted."""
+def forward_logits(model_dir, tokens, window=None, rows=None):
+    """Whole sequence, no cache: model.rs:207-362 with every row wanted, or (``rows``: a list of positions) with
+    only those rows taken through the final norm and the head (model.rs:350-361 does the same with ``want``)."""
     c, w = _load(model_dir)
     tokens = np.asarray(tokens, dtype=np.int64)
     T = tokens.shape[0]
@@ -134,6 +135,8 @@ def forward_logits(model_dir, tokens, window=None):
         g = h @ w[f"{p}.mlp.gate_proj.weight"].T                                # model.rs:335
         u = h @ w[f"{p}.mlp.up_proj.weight"].T
         x = x + swiglu(g, u) @ w[f"{p}.mlp.down_proj.weight"].T                 # model.rs:336-344
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     hs = rms_norm(x, w["model.norm.weight"], c["eps"])                          # model.rs:350-358
     head = w["model.embed_tokens.weight"] if c["tie"] or "lm_head.weight" not in w else w["lm_head.weight"]
     return hs @ head.T                                                          # model.rs:359-361, 190-192

@@ -13,11 +13,15 @@ TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 def live_tokens_needed(steps):
     """The smallest --max-tokens the trace may be given: the most tokens live requests hold at any
     time, each request's count rounded up to a multiple of 64."""
-    held, worst = {}, 0
+    held, away, worst = {}, {}, 0
     for st in steps:
+        for parent, child in st.get("fork", []):
+            held[child] = held[parent]                      # counted in full, although it shares pages at first
         for e in st["entries"]:
-            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+            held[e["id"]] = held.get(e["id"], away.pop(e["id"], 0)) + len(e["tokens"])
         worst = max(worst, sum(-(-n // 64) * 64 for n in held.values()))
+        for rid in st.get("preempt", []):
+            away[rid] = held.pop(rid)                       # holds nothing until it returns, then everything again
         for rid in st.get("end", []):
             held.pop(rid, None)
     return worst
@@ -38,6 +42,8 @@ def run_trace(model_dir, dtype, steps, out_dir, max_tokens=None, extra=()):
         vocab = json.load(f)["vocab_size"]
     per_request, pos = {}, {}
     for st in steps:
+        for parent, child in st.get("fork", []):
+            pos[child] = pos[parent]
         wanted = sum(len(e.get("want", [])) for e in st["entries"])
         path = os.path.join(out_dir, f"{st['step']}.f32")
         if not wanted:
@@ -133,6 +139,8 @@ def run_steps_inprocess(engine, steps):
     rep = Replayer(engine)
     per_request, pos = {}, {}
     for st in steps:
+        for parent, child in st.get("fork", []):
+            pos[child] = pos[parent]
         logits = rep.run_step(st)
         arr = logits.cpu().numpy().copy() if logits is not None else None
         row = 0
@@ -142,5 +150,44 @@ def run_steps_inprocess(engine, steps):
                 per_request.setdefault(e["id"], {})[base + w] = arr[row]
                 row += 1
             pos[e["id"]] = base + len(e["tokens"])
-    engine.cache.check_invariants()
+    rep.finish()
     return per_request
+
+
+def forks_preemption_and_shared_prefix(vocab, rng):
+    """A trace with the cache operations of a scheduler: a fork in the middle of a page (its first write copies the
+    shared page), a preemption after which a newcomer takes the victim's pages before the victim returns and is
+    computed again, and a request that starts on a 70-token prefix another request has already computed. Up to four
+    requests are live; logits are wanted at every row. Returns (steps, {request: all its tokens})."""
+    tok = lambda n: [rng.randrange(vocab) for _ in range(n)]
+    prefix = tok(70)
+    full = {"r0": tok(60), "r1": prefix + tok(14), "r2": prefix + tok(16), "r3": tok(56)}
+    full["c0"] = full["r0"][:37] + tok(20)
+    at = {"r0": 0, "r1": 0, "r2": 0, "r3": 0, "c0": 37}
+
+    def take(rid, n, want="all"):
+        toks = full[rid][at[rid]:at[rid] + n]
+        assert len(toks) == n, (rid, at[rid], n)
+        at[rid] += n
+        return {"id": rid, "tokens": toks, "want": list(range(n)) if want == "all" else want}
+
+    steps = [
+        {"entries": [take("r0", 37)]},                                            # ends in the middle of its third page
+        {"fork": [["r0", "c0"]], "entries": [take("c0", 5), take("r0", 3), take("r1", 40)]},   # both write: one copies
+        {"entries": [take("r0", 1), take("c0", 1), take("r1", 30)]},             # r1 has passed the shared prefix
+        {"entries": [take("r0", 1), take("c0", 1), take("r1", 2)], "preempt": ["r0"]},
+        {"entries": [take("r3", 50), take("c0", 1), take("r1", 1)]},             # r3 is given the pages r0 held
+        {"entries": [take("r2", 76, want=list(range(64, 76))), take("c0", 2), take("r3", 1)]},   # four live
+        {"entries": [take("r3", 1), take("r2", 1), take("c0", 1), take("r1", 1)], "end": ["r1"]},
+        {"entries": [take("r3", 4), take("r2", 2)], "end": ["r3"]},
+        {"entries": [take("r0", 1), take("r2", 2), take("c0", 1)]},              # r0 returns: 42 tokens run again
+        {"entries": [take("r0", 7), take("c0", 3)], "preempt": ["c0"]},
+        {"entries": [take("r0", 1), take("r2", 1)]},
+        {"entries": [take("c0", 1), take("r0", 1), take("r2", 1)]},              # c0 returns
+        {"entries": [take("c0", 4), take("r0", 5), take("r2", 3)], "end": ["c0", "r0", "r2"]},
+    ]
+    for i, st in enumerate(steps):
+        st["step"] = i
+        st.setdefault("end", [])
+    known = {rid: toks[:at[rid]] for rid, toks in full.items()}
+    return steps, known

@@ -264,3 +264,57 @@ def test_the_metadata_block_of_a_padded_step():
                                tc[2] * 16 + 0, -1, -1, -1, -1, -1]                         # cache slot of every row
     tables = sec(10).reshape(S, P)
     assert tables[0, :2].tolist() == ta and tables[4, :3].tolist() == tc and (tables[2:4] == -1).all() and (tables[5] == -1).all()
+
+
+def test_a_write_into_a_hashed_page_held_alone_drops_its_hash():
+    """Fork, the child truncates into a hashed page (still shared, so its hash stays), the parent goes away, the
+    child writes without a copy: the page's old hash must not outlive its contents."""
+    m = mgr(pages=6)
+    prompt = list(range(40))
+    m.add_request("p", prompt)
+    feed(m, "p", prompt)                           # pages 0 and 1 full and hashed
+    m.fork("p", "c")
+    m.truncate("c", 20)                            # into page 1, which the parent still holds
+    page1 = m.table(0, "c")[1]
+    assert m.page_hash(0, page1) is not None       # still valid for the parent
+    m.free_request("p")
+    assert m.reserve("c", 5) == []                 # alone on the page: no copy
+    assert m.page_hash(0, page1) is None           # and the index has forgotten it
+    m.commit("c", [7] * 5)
+    m.check_invariants()
+    m.free_request("c")
+    assert m.add_request("again", prompt) == 16    # only the untouched first page is found again
+    m.check_invariants()
+
+
+def test_commit_records_the_tokens_that_ran_not_the_ones_expected():
+    m = mgr(pages=6)
+    m.add_request("a", list(range(100, 140)))      # expected
+    feed(m, "a", [5] * 33)                         # what really ran
+    assert m.tokens("a") == [5] * 33
+    m.free_request("a")
+    assert m.add_request("b", list(range(100, 140))) == 0, "a page was indexed under tokens it never held"
+    m.free_request("b")
+    assert m.add_request("c", [5] * 40) == 32
+    m.check_invariants()
+
+
+def test_a_preempted_request_takes_its_copy_on_write_work_with_it():
+    """Three requests; the last admitted is a fork that decodes, so it is planned first and its write into the
+    shared partial page needs a copy. The prompt portion planned after it runs out of pages, the fork is preempted,
+    and its copy must go with it: the destination page is back in the pool and is handed out again in the same plan."""
+    m = mgr(pages=5, share=False)
+    m.add_request("p")
+    feed(m, "p", list(range(20)))                  # 2 pages
+    m.add_request("q")
+    feed(m, "q", list(range(16)))                  # 1 page, full
+    m.fork("p", "c")                               # shares p's 2 pages; 2 pages free
+    # c decodes (planned first, copies page 1 into a fresh page), p brings 5 tokens (fits its page), q's
+    # portion of 32 tokens needs 2 pages where 1 is left: c, admitted last, is preempted
+    plan, copies, preempted, lone = m.plan_step(["p", "q", "c"], [5, 32, 1], 64)
+    assert preempted == 1 and not lone and plan == [(0, 5), (1, 32)]
+    assert copies == [], "a copy for the preempted request was kept"
+    assert m.length("c") == -1
+    m.free_request("c")
+    assert len(set(m.table(0, "p")) | set(m.table(0, "q"))) == 5 and m.free_pages() == 0
+    m.check_invariants()

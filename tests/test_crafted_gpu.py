@@ -129,3 +129,30 @@ def test_mixed_batches_split_between_the_decode_and_the_flash_kernel(tmp_path, m
         eng = engine_for(str(tmp_path / "m"), "bfloat16", ru.live_tokens_needed(steps))
         check(info, ru.run_steps_inprocess(eng, steps), requests, "bfloat16", f"window {window} split mixed {seed}")
     assert any(0 < k < n for k, n in split_calls), "no batch was split: the test did not reach what it is about"
+
+
+@pytest.mark.parametrize("share", [False, True], ids=["no-sharing", "share-prefixes"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_forks_preemption_and_shared_prefixes_read_exactly_their_keys(tmp_path, monkeypatch, dtype, share):
+    """The same trace of cache operations as the replay test, on the probe model, where a key read from the wrong
+    page (a copy that did not run, a page taken over from another request) shows at full size in bfloat16 too."""
+    from glassbox_b200.engine.engine import Engine
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    info = toy_arch.write_probe_model(str(tmp_path / "m"), store=store, seed=4)
+    for seed in (1, 2):
+        steps, known = ru.forks_preemption_and_shared_prefix(info["vocab"], random.Random(seed))
+        eng = Engine(str(tmp_path / "m"), dtype, cache_tokens=ru.live_tokens_needed(steps), max_batch_tokens=512,
+                     max_requests=8, share_prefixes=share)
+        got = ru.run_steps_inprocess(eng, steps)
+        check(info, got, known, dtype, f"forks/preemption seed {seed}")
+        assert sum(len(v) for v in got.values()) == sum(len(e["want"]) for s in steps for e in s["entries"])
+        if share:
+            assert eng.cache.share_prefixes
+    # the test must be able to fail: without the copy that a write into a shared page needs, the fork's rows
+    # (or its parent's) read keys that the other wrote
+    steps, known = ru.forks_preemption_and_shared_prefix(info["vocab"], random.Random(1))
+    eng = Engine(str(tmp_path / "m"), dtype, cache_tokens=ru.live_tokens_needed(steps), max_batch_tokens=512, max_requests=8)
+    monkeypatch.setattr(eng, "run_copies", lambda copies: None)
+    got = ru.run_steps_inprocess(eng, steps)
+    with pytest.raises(AssertionError):
+        check(info, got, known, dtype, "without copies")

@@ -780,3 +780,186 @@ def test_gemm_tcgen05_many_tiles_per_block():
     acc = base.clone()
     kernels.gemm_tc(a, w, acc, accumulate=True, status=st)
     assert (acc - base - ref).abs().max() <= 1e-3 and int(st) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_position_beyond_the_block_table_is_reported_and_reads_nothing(dtype):
+    """The exported launchers take positions and a block table of a stated width from the caller. A position that the
+    table does not reach sets the status word and its row comes back as zeros; the rows beside it are served."""
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps = 4, 2, 64, 16
+    k, v, tables, dense = make_cache(dtype, 2, [40, 40], nkv, hd, ps, extra_pages=0)
+    width = tables.shape[1]                                   # 4 pages: positions up to 63
+    q = torch.randn(2, nh, hd).to(dtype)
+    qd = q.to(DEV).reshape(2, nh * hd)
+    row_seq = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([39, width * ps + 5], dtype=torch.int32, device=DEV)
+    ref = ref_attention(q[:1], dense, [0], [39], nh, nkv, hd ** -0.5, None)
+
+    def check(out, st):
+        assert int(st) == 4, "the status word must carry the bad-position bit, and only it"
+        got = out.cpu().double().reshape(2, nh, hd)
+        assert (got[0] - ref[0]).abs().max() <= tol(dtype, 2) and float(got[1].abs().max()) == 0.0
+
+    st, out = status(), torch.full((2, nh * hd), 7.0, device=DEV, dtype=dtype)
+    kernels.attention_rows(qd, out, k, v, tables, row_seq, positions, nh, nkv, hd, ps, hd ** -0.5, None, st)
+    check(out, st)
+    st, out = status(), torch.full((2, nh * hd), 7.0, device=DEV, dtype=dtype)
+    splits = 2
+    kernels.attention_decode(qd, out, k, v, tables, row_seq, positions, nh, nkv, hd, ps, hd ** -0.5, None, splits,
+                             torch.empty(2 * nh * splits * hd, device=DEV), torch.empty(2 * nh * splits * 2, device=DEV),
+                             torch.zeros(2 * nh, dtype=torch.int32, device=DEV), st)
+    check(out, st)
+    if dtype == torch.bfloat16:
+        st, out = status(), torch.full((2, nh * hd), 7.0, device=DEV, dtype=dtype)
+        kernels.attention_decode_mma(qd, out, k, v, tables, row_seq, positions, nh, nkv, hd, ps, hd ** -0.5, None, splits,
+                                     torch.empty(2 * nh * 4 * splits * hd, device=DEV),
+                                     torch.empty(2 * nh * 4 * splits * 2, device=DEV),
+                                     torch.zeros(2 * nkv, dtype=torch.int32, device=DEV), st)
+        check(out, st)
+        st, out = status(), torch.full((2, nh * hd), 7.0, device=DEV, dtype=dtype)
+        kernels.attention_prefill(qd, out, k, v, tables, torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV), positions,
+                                  1, nh, nkv, hd, ps, hd ** -0.5, None, st)
+        check(out, st)
+
+
+# ------------------------------------------------------------------- the context lengths that are benchmarked
+def long_cache(dtype, lens, nkv, hd, ps, seed=0):
+    """Random keys and values for sequences of the given lengths on shuffled pages, made on the GPU; returns the
+    cache, the block tables (one spare column) and a function that gathers a sequence's keys/values as float64."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    pages_per = [-(-l // ps) for l in lens]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g, device=DEV)
+    k = torch.randn(num_pages, nkv, ps, hd, generator=g, device=DEV).to(dtype)
+    v = torch.randn(num_pages, nkv, ps, hd, generator=g, device=DEV).to(dtype)
+    tables = torch.full((len(lens), max(pages_per) + 1), -1, dtype=torch.int32, device=DEV)
+    at = 0
+    for s, n in enumerate(pages_per):
+        tables[s, :n] = perm[at:at + n].int()
+        at += n
+
+    def dense(s):
+        ids = tables[s, :pages_per[s]].long()
+        kk = k[ids].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :lens[s]].double()
+        vv = v[ids].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :lens[s]].double()
+        return kk, vv
+    return k, v, tables, dense
+
+
+def ref_rows_gpu(q, kk, vv, positions, nh, nkv, scale):
+    """softmax(q k^T * scale) v in float64 on the GPU, row r seeing keys 0 .. positions[r]; q [n, nh, hd]."""
+    n, group = q.shape[0], nh // nkv
+    out = torch.empty(n, nh, q.shape[-1], dtype=torch.float64, device=q.device)
+    pos = torch.as_tensor(positions, device=q.device)
+    keys = torch.arange(kk.shape[1], device=q.device)
+    for h in range(nh):
+        s = (q[:, h].double() @ kk[h // group].T) * scale
+        s = s.masked_fill(keys[None, :] > pos[:, None], float("-inf"))
+        out[:, h] = torch.softmax(s, dim=-1) @ vv[h // group]
+    return out
+
+
+LONG_DECODE = [  # heads, kv heads: the benchmark's three models; every batch size it decodes at; 4,096 and 8,192 keys
+    (9, 3, 1), (9, 3, 8), (9, 3, 64), (15, 5, 8), (32, 32, 1), (32, 32, 8),
+]
+
+
+@pytest.mark.parametrize("L", [4096, 8192])
+@pytest.mark.parametrize("nh, nkv, B", LONG_DECODE)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_attention_at_the_benchmarked_context_lengths(dtype, nh, nkv, B, L):
+    """The split counts and kernel variants that the engine's own planner picks for these batches (kernels.decode_mma_plan
+    and kernels.decode_splits, with the table width a recorded step has), requests of slightly different lengths, and in
+    request 0 one far key that carries the whole softmax: near the start, at a split's edge or near the end."""
+    from glassbox_b200 import kernels
+    hd, ps = 64, 16
+    lens = [L - 37 * i for i in range(B)]
+    k, v, tables, dense = long_cache(dtype, lens, nkv, hd, ps, seed=B)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    q = torch.randn(B, nh, hd, generator=g, device=DEV)
+    kk0, vv0 = dense(0)
+    fars = [5, L // 2 - 1, L - 3]
+    for h in range(min(nh, 3)):                                   # heads 0..2 of request 0 each seek one key
+        key = kk0[h // (nh // nkv), fars[h]]
+        q[0, h] = (key / key.norm() ** 2 * 60.0 * 8.0).float()
+    q = q.to(dtype)
+    row_seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    positions = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    ref = torch.stack([ref_rows_gpu(q[s:s + 1], *dense(s), [lens[s] - 1], nh, nkv, hd ** -0.5)[0] for s in range(B)])
+    for h in range(min(nh, 3)):
+        assert (ref[0, h] - vv0[h // (nh // nkv), fars[h]]).abs().max() < 1e-3, "the crafted score does not dominate"
+    qd = q.reshape(B, nh * hd)
+    st = status()
+    out = torch.full((B, nh * hd), 7.0, device=DEV, dtype=dtype)
+    if dtype == torch.bfloat16:
+        splits, block_keys = kernels.decode_mma_plan(B, nkv, hd, L)
+        for sp, bk in {(splits, block_keys), (1, 0), (max(splits // 2, 1), 16)}:
+            kernels.attention_decode_mma(qd, out, k, v, tables, row_seq, positions, nh, nkv, hd, ps, hd ** -0.5, None, sp,
+                                         torch.empty(B * nh * 4 * sp * hd, device=DEV), torch.empty(B * nh * 4 * sp * 2, device=DEV),
+                                         torch.zeros(B * nkv, dtype=torch.int32, device=DEV), st, bk)
+            diff = (out.double().reshape(B, nh, hd) - ref).abs()
+            assert int(st) == 0 and diff.max() <= tol(dtype, 2), f"splits {sp}, {bk or 32}-key variant: off by {float(diff.max()):.3e}"
+            out.fill_(7.0)
+    splits = kernels.decode_splits(B, nh, nkv, L)
+    for sp in {splits, 1, 3}:
+        kernels.attention_decode(qd, out, k, v, tables, row_seq, positions, nh, nkv, hd, ps, hd ** -0.5, None, sp,
+                                 torch.empty(B * nh * sp * hd, device=DEV), torch.empty(B * nh * sp * 2, device=DEV),
+                                 torch.zeros(B * nh, dtype=torch.int32, device=DEV), st)
+        diff = (out.double().reshape(B, nh, hd) - ref).abs()
+        assert int(st) == 0 and diff.max() <= tol(dtype, 2), f"FMA decode kernel, splits {sp}: off by {float(diff.max()):.3e}"
+        out.fill_(7.0)
+
+
+def test_decode_attention_with_more_pages_than_a_block_stages():
+    """One block that covers more than 1,024 pages reads its page ids from the table as it goes instead of from shared
+    memory: 20,000 keys in 16-token pages, unsplit and split in two; one far key carries head 0."""
+    from glassbox_b200 import kernels
+    nh, nkv, hd, ps, L, dtype = 2, 1, 64, 16, 20000, torch.bfloat16
+    k, v, tables, dense = long_cache(dtype, [L], nkv, hd, ps, seed=7)
+    kk, vv = dense(0)
+    q = torch.randn(1, nh, hd, device=DEV)
+    q[0, 0] = (kk[0, 17001] / kk[0, 17001].norm() ** 2 * 60.0 * 8.0).float()
+    q = q.to(dtype)
+    ref = ref_rows_gpu(q, kk, vv, [L - 1], nh, nkv, hd ** -0.5)
+    assert (ref[0, 0] - vv[0, 17001]).abs().max() < 1e-3
+    out = torch.empty(1, nh * hd, device=DEV, dtype=dtype)
+    for splits in (1, 2):
+        st = status()
+        kernels.attention_decode_mma(q.reshape(1, -1), out, k, v, tables, torch.zeros(1, dtype=torch.int32, device=DEV),
+                                     torch.tensor([L - 1], dtype=torch.int32, device=DEV), nh, nkv, hd, ps, hd ** -0.5, None,
+                                     splits, torch.empty(nh * 4 * splits * hd, device=DEV),
+                                     torch.empty(nh * 4 * splits * 2, device=DEV), torch.zeros(nkv, dtype=torch.int32, device=DEV), st)
+        assert int(st) == 0 and (out.double().reshape(1, nh, hd) - ref).abs().max() <= tol(dtype, 2), f"splits {splits}"
+
+
+@pytest.mark.parametrize("nh, nkv, ps, start, rows", [(3, 1, 16, 0, 4096), (2, 2, 16, 7900, 292), (1, 1, 32, 0, 8192),
+                                                      (9, 3, 16, 4000, 96)])
+def test_prefill_attention_at_the_benchmarked_context_lengths(nh, nkv, ps, start, rows):
+    """Whole prompts of 4,096 and 8,192 tokens (32 and 64 query tiles) and portions that end at 4,096 and 8,192, through
+    the tcgen05 kernel and the mma.sync kernel; every 97th row seeks one far key of its own."""
+    from glassbox_b200 import kernels
+    hd, dtype, L = 64, torch.bfloat16, start + rows
+    k, v, tables, dense = long_cache(dtype, [L], nkv, hd, ps, seed=rows)
+    kk, vv = dense(0)
+    g = torch.Generator(device=DEV).manual_seed(2)
+    q = torch.randn(rows, nh, hd, generator=g, device=DEV)
+    seekers = list(range(0, rows, 97))
+    targets = [int(torch.randint(0, start + r + 1, (1,), generator=g, device=DEV)) for r in seekers]
+    for r, t_ in zip(seekers, targets):
+        key = kk[0, t_]
+        q[r, 0] = (key / key.norm() ** 2 * 60.0 * 8.0).float()
+    q = q.to(dtype)
+    positions = list(range(start, L))
+    ref = ref_rows_gpu(q, kk, vv, positions, nh, nkv, hd ** -0.5)
+    for r, t_ in zip(seekers, targets):
+        assert (ref[r, 0] - vv[0, t_]).abs().max() < 1e-3
+    qd = q.reshape(rows, nh * hd).contiguous()
+    first = torch.tensor([0, rows], dtype=torch.int32, device=DEV)
+    start_pos = torch.tensor([start], dtype=torch.int32, device=DEV)
+    for name, fn in (("tcgen05", kernels.attention_prefill_tc), ("mma.sync", kernels.attention_prefill)):
+        out = torch.full((rows, nh * hd), 7.0, device=DEV, dtype=dtype)
+        st = status()
+        fn(qd, out, k, v, tables, first, start_pos, rows, nh, nkv, hd, ps, hd ** -0.5, None, st)
+        diff = (out.double().reshape(rows, nh, hd) - ref).abs().amax(dim=(1, 2))
+        assert int(st) == 0 and diff.max() <= tol(dtype, 2), f"{name}: row {int(diff.argmax())} off by {float(diff.max()):.3e}"

@@ -82,3 +82,26 @@ def test_cutting_does_not_change_logits_beyond_rounding(model_dirs, sharp_dirs, 
             diff = np.abs(np.stack([other[rid][i] for i in idx]) - ref[idx]).max()
             bound = 2e-5 if dtype == "float32" else 0.03 * spread
             assert diff <= bound, f"{rid} {label}: {diff:.3e} > {bound:.3e} ({dtype})"
+
+
+@pytest.mark.parametrize("share", [False, True], ids=["no-sharing", "share-prefixes"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_forks_preemption_and_shared_prefixes(model_dirs, sharp_dirs, tmp_path, name, dtype, share):
+    """The cache operations of a scheduler, through bin/trace_run: a fork in the middle of a page and the copy its
+    first write needs, a preemption whose pages go to a newcomer before the victim returns and is computed again, a
+    request that starts on a prefix another one has computed; logits at every row against the plain implementation.
+    trace_run itself checks the cache's invariants at the end and that no page or slot leaked (exit code 3)."""
+    kinds = [("random-weights", model_dirs(name, dtype))]
+    if dtype == "float32":
+        kinds.append(("sharp", sharp_dirs(name, dtype)))
+    for kind, folder in kinds:
+        for seed in (1, 2):
+            steps, known = ru.forks_preemption_and_shared_prefix(TINY[name]["vocab_size"], random.Random(seed))
+            assert max(len(s["entries"]) for s in steps) == 4
+            got = ru.run_trace(folder, dtype, steps, str(tmp_path / f"{kind}{seed}"),
+                               extra=("--share-prefixes",) if share else ())
+            for rid, toks in known.items():
+                first = {"c0": 37, "r2": 64}.get(rid, 0)     # the fork starts where its parent stood; r2 asks from 64 on
+                assert sorted(got[rid]) == list(range(first, len(toks))), f"{rid} is missing positions"
+            check(folder, dtype, got, known, f"{name} forks/preemption {kind} seed {seed}", only_wanted=True)

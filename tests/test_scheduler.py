@@ -191,3 +191,46 @@ def test_the_native_plan_of_a_step_decodes_first_fills_the_budget_and_preempts_t
     lone_m.add_request("x")
     plan, copies, preempted, lone = lone_m.plan_step(["x"], [100], 64)
     assert lone and plan == [] and preempted == 0 and lone_m.free_pages() == 2
+
+
+def test_an_over_long_prompt_is_refused_at_the_door_and_harms_nobody(model_dirs):
+    folder = model_dirs("A")                                              # max_position 128
+    backend = PlainBackend(folder, num_pages=64)
+    s = Scheduler(backend, SchedulerConfig(token_budget=32, max_seqs=4))
+    ok = [s.submit(Request(prompt=[3, 4, 5], max_tokens=3)), s.submit(Request(prompt=list(range(1, 60)), max_tokens=2))]
+    with pytest.raises(ValueError, match="max_position"):
+        s.submit(Request(prompt=[1] * 129, max_tokens=4))
+    edge = s.submit(Request(prompt=[2] * 128, max_tokens=4))              # fills the context exactly: one token, then length
+    s.run_until_idle()
+    assert s.finished[ok[0]].tokens == greedy(folder, [3, 4, 5], 3)
+    assert len(s.finished[ok[1]].tokens) == 2
+    assert s.finished[edge].reason == LENGTH and len(s.finished[edge].tokens) == 1
+    backend.cache.check_invariants()
+    assert backend.cache.free_pages() == 64
+
+
+def test_fork_shares_the_parents_pages_and_goes_its_own_way(model_dirs):
+    folder = model_dirs("B")
+    backend = PlainBackend(folder, num_pages=16, share_prefixes=False)
+    s = Scheduler(backend, SchedulerConfig(token_budget=64, max_seqs=4))
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5, 8, 9, 7, 9, 3, 2, 3, 8, 4, 6]
+    parent = s.submit(Request(prompt=prompt, max_tokens=10, sampler=SamplerConfig(temperature=0.9, seed=1)))
+    for _ in range(4):
+        s.step()
+    used = backend.cache.used_pages()
+    child = s.fork(parent, sampler=SamplerConfig(temperature=0.9, seed=2), max_tokens=8)
+    twin = s.fork(parent)
+    assert backend.cache.used_pages() == used, "a fork takes no page until somebody writes"
+    backend.cache.check_invariants()
+    late = s.submit(Request(prompt=[7, 7, 7], max_tokens=2))
+    cousin = s.fork(late, max_tokens=3)                       # its parent still waits: it waits right behind it
+    assert [x.id for x in s.waiting] == [late, cousin]
+    s.run_until_idle()
+    backend.cache.check_invariants()
+    assert backend.cache.free_pages() == 16 and len(backend.cache.free_slots) == backend.cache.max_requests
+    p_out, c_out, t_out = (s.finished[i].tokens for i in (parent, child, twin))
+    assert len(p_out) == 10 and len(c_out) == 8 and t_out == p_out[4:] and c_out[:6] != p_out[4:]
+    assert s.finished[child].prompt_tokens == len(prompt) + 4
+    assert len(s.finished[cousin].tokens) == 3 and s.finished[cousin].tokens[:2] == s.finished[late].tokens
+    with pytest.raises(KeyError):
+        s.fork(parent)                                        # it has finished
