@@ -9,6 +9,7 @@ Trace replay, the scheduler and the generator all drive this same function.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -432,8 +433,18 @@ class Engine:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = kernels.launch_count
-        with torch.cuda.graph(graph):
-            logits = run()
+        # Nothing may free device memory while the stream records: an engine that was dropped earlier and is
+        # collected now would destroy its own graphs and their memory pools in the middle of this recording,
+        # which invalidates it. So what is garbage is collected first and the collector rests meanwhile.
+        was_enabled = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = run()
+        finally:
+            if was_enabled:
+                gc.enable()
         g = {"graph": graph, "meta": meta, "logits": logits, "sampled": sampled, "ctx": ctx,
              "nodes": kernels.launch_count - before}
         self._graphs[key] = g
