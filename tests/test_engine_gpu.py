@@ -159,20 +159,19 @@ def test_scheduler_on_the_engine_logits_survive_preemption_and_recomputation(mod
     llm = glassbox_b200.load(folder, dtype, blocks=9, budget=64, max_seqs=8, prefix_cache=True)   # pages run out
     spy = StepSpy(llm.engine)
     ids_before = llm.scheduler.next_id
+    llm.scheduler.trace = []
     outs, reasons = llm.generate(prompts, 20, return_reasons=True)
     assert llm.scheduler.metrics.preemptions > 0, "the test did not exercise preemption"
+    victims = {sid for rec in llm.scheduler.trace for sid in rec["preempted"]}
+    assert victims and all(r == "length" for r in reasons)     # every victim came back and ran to its 20 tokens
     llm.engine.cache.check_invariants()
     assert llm.engine.cache.free_pages() == 9
     full = {ids_before + i: p + out for i, (p, out) in enumerate(zip(prompts, outs))}
     ref = {sid: forward_logits(folder, toks) for sid, toks in full.items()}
-    seen_again = 0
-    places = set()
     by_request = {}
     for sid, pos, row in spy.rows:
-        seen_again += (sid, pos) in places          # the same place computed twice: once before, once after a preemption
-        places.add((sid, pos))
         by_request.setdefault(sid, []).append((pos, row))
-    assert seen_again > 0, "no row was computed again after a preemption"
+    assert all(len(by_request[sid]) == 20 for sid in victims), "a preempted request lost or repeated a token"
     for sid, rows in by_request.items():
         got = np.stack([r for _, r in rows])
         assert_logits_close(got, ref[sid][[p for p, _ in rows]], dtype, f"request {sid} through the scheduler")
