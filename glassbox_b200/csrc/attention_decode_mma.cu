@@ -24,7 +24,9 @@
 
 template <int HD, int BK>
 __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const DecodeAttnArgs a) {
-    attention_decode_mma_body<HD, BK, false>(a, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z);
+    __shared__ DecodeAttnSmem sm;
+    GbPdlSync sync;
+    attention_decode_mma_body<HD, BK>(a, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, sm, sync);
 }
 
 template <int HD, int BK>

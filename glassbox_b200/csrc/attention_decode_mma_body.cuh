@@ -70,10 +70,18 @@ template <> struct RowLoad<8> {
     }
 };
 
-// PERSIST: called from the persistent kernel (no dependent-launch instructions; queries, which another block of the
-// same launch wrote, are read past L1).
-template <int HD, int BK, bool PERSIST>
-__device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& a, const int split, const int kvh, const int row) {
+// `sync` says how to wait for the work before (GbPdlSync in the stand-alone kernel, a barrier's wait in a persistent
+// one). Queries, which another block of the same launch may have written, are read past L1.
+// Shared memory of the body, provided by the caller.
+struct DecodeAttnSmem {
+    int pages[MMA_MAX_PAGES];
+    float weights[MMA_MAX_MERGE];
+    int is_last;
+};
+
+template <int HD, int BK, class Sync>
+__device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& a, const int split, const int kvh, const int row,
+                                                          DecodeAttnSmem& sm, Sync& sync) {
     const __nv_bfloat16* __restrict__ q = a.q;
     const long long q_stride = a.q_stride, out_stride = a.out_stride;
     __nv_bfloat16* __restrict__ out = a.out;
@@ -101,12 +109,12 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     const int G = nh / nkv;
     const int head0 = kvh * G;
     const int S4 = splits * 4;
-    __shared__ int is_last;
+    int& is_last = sm.is_last;
 
     // Let the next kernel in the stream begin its prologue. This kernel's own prologue (positions,
     // block table: step metadata that no kernel writes) runs before it waits for its predecessor,
     // which wrote the queries and this step's keys and values.
-    if constexpr (!PERSIST) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    sync.start();
     int pos = positions[row];
     if (pos >= 0 && (pos >> page_shift) >= max_pages) {   // a position the block table does not reach: reported, and the
         if (tid == 0) atomicOr(status, GB_STATUS_BAD_POSITION);   // row is treated as padding (nothing is read)
@@ -114,7 +122,8 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     }
     __nv_bfloat16* orow = out + (size_t)row * out_stride;
     if (pos < 0) {  // padding row
-        if constexpr (!PERSIST) asm volatile("griddepcontrol.wait;" ::: "memory");
+        sync.wait();
+        if (sync.gave_up()) return;
         if (split == 0)
             for (int i = tid; i < G * HD; i += 128) orow[head0 * HD + i] = __float2bfloat16_rn(0.f);
         return;
@@ -141,7 +150,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     // of two >= 16 keys) and its addresses are a few integer operations. Loads never branch. They
     // run one block of keys ahead of the arithmetic (two register sets), so that a warp always has
     // loads in flight.
-    __shared__ int pages_s[MMA_MAX_PAGES];
+    int* pages_s = sm.pages;
     const int page_mask = page_size - 1;
     const int page_lo = k_begin >> page_shift;
     const int n_pages = nblocks > 0 ? ((k_end - 1) >> page_shift) - page_lo + 1 : 0;
@@ -160,7 +169,8 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
         }
         __syncthreads();
     }
-    if constexpr (!PERSIST) asm volatile("griddepcontrol.wait;" ::: "memory");   // the predecessor's writes (q, this step's K/V) are visible from here
+    sync.wait();   // the writes of the work before (q, this step's K/V) are visible from here
+    if (sync.gave_up()) return;
     // Q as the A operand: rows g and g+8 are query heads head0+g and head0+g+8 (zero beyond G).
     uint32_t qf[KS][4];
     {
@@ -321,7 +331,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     // Merge: one warp per head turns the (maximum, sum) pairs of all sub-splits into normalised
     // weights in shared memory; then every thread adds up its channel over the sub-splits with
     // independent loads.
-    __shared__ float weights[MMA_MAX_MERGE];
+    float* weights = sm.weights;
     const int per_pass = MMA_MAX_MERGE / S4;                 // heads whose weights fit at once
     for (int h0 = 0; h0 < G; h0 += per_pass) {
         const int hcount = min(per_pass, G - h0);

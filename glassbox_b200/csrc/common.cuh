@@ -66,6 +66,16 @@ int gb_pdl_enabled();
 __device__ __forceinline__ void gb_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void gb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// How a kernel body that can run in several settings meets the work before it. A body calls start() first and
+// wait() at the point from which it reads what earlier work wrote; before wait() it may only read what no kernel of
+// the step writes (weights, step metadata). A bounded wait may give up: the body then returns at once, having written nothing. Stand-alone kernels use GbPdlSync (programmatic dependent launch); a
+// persistent kernel passes an object whose wait() is its barrier's wait.
+struct GbPdlSync {
+    __device__ __forceinline__ void start() { gb_pdl_launch_dependents(); }
+    __device__ __forceinline__ void wait() { gb_pdl_wait(); }
+    __device__ __forceinline__ bool gave_up() const { return false; }   // after wait(): true = do nothing more
+};
+
 enum { GB_PDL_ELEMENTWISE = 1, GB_PDL_GEMM = 2, GB_PDL_ATTENTION = 4 };   // bits of the switch
 
 template <typename... KArgs, typename... Args>

@@ -33,7 +33,10 @@
 
 template <int NT, bool PAIR, int KC>
 __global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
-    gemm_stream_body<NT, PAIR, KC, false>(a, (int)blockIdx.x);
+    __shared__ __align__(16) unsigned char xs[gemm_stream_smem_bytes<NT, KC>()];
+    __shared__ float srow[NT * 8];
+    GbPdlSync sync;
+    gemm_stream_body<NT, PAIR, KC, false>(a, (int)blockIdx.x, xs, srow, sync);
 }
 
 template <int NT, bool PAIR, int KC>

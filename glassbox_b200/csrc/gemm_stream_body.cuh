@@ -85,16 +85,21 @@ __device__ __forceinline__ void gemm_stream_prefetch_block(const StreamArgs& a, 
 }
 
 // KC: k per shared-memory chunk (256 or 512); each warp has KC/128 blocks of 32 k in flight per strip row.
-// PERSIST: called from the persistent kernel (no cluster, no dependent-launch instructions; `vblock` is the strip
-// and its whole K), else from the stand-alone kernel (`vblock` = blockIdx.x).
-template <int NT, bool PAIR, int KC, bool PERSIST>
-__device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int vblock) {
+// PERSIST: called from a persistent kernel (no split of K over a cluster; `vblock` is the strip and its whole K),
+// else from the stand-alone kernel (`vblock` = blockIdx.x). `sync` says how to wait for the work before (GbPdlSync
+// in the stand-alone kernel).
+// The caller provides the shared memory: `xs_raw` of gemm_stream_smem_bytes<NT, KC>() bytes, 16-byte aligned (the
+// activation tile, reused for the partial sums), and `srow` of NT * 8 floats.
+template <int NT, int KC>
+__host__ __device__ constexpr int gemm_stream_smem_bytes() { return NT * 8 * (KC + WS_PAD) * 2; }
+
+template <int NT, bool PAIR, int KC, bool PERSIST, class Sync>
+__device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int vblock, void* xs_raw, float* srow, Sync& sync) {
     constexpr int ROWS = NT * 8;   // activation rows held
     constexpr int SETS = PAIR ? 2 : 1;
     constexpr int WS_KC = KC;
     constexpr int WS_BPW = KC / 32 / 4;   // k32 blocks per warp per chunk
-    __shared__ __align__(16) __nv_bfloat16 xs[ROWS][WS_KC + WS_PAD];
-    __shared__ float srow[ROWS];
+    __nv_bfloat16 (*xs)[WS_KC + WS_PAD] = reinterpret_cast<__nv_bfloat16 (*)[WS_KC + WS_PAD]>(xs_raw);
     // the partial sums of the four warps reuse the activation tile once the k loop is over
     static_assert(sizeof(float) * 4 * SETS * 16 * ROWS <= sizeof(__nv_bfloat16) * ROWS * (WS_KC + WS_PAD), "red fits in xs");
     float* red = reinterpret_cast<float*>(&xs[0][0]);
@@ -103,7 +108,7 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
     const int M = a.M, N = a.N, K = a.K;
 
     // let the next kernel in the stream start its own prologue
-    if constexpr (!PERSIST) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    sync.start();
 
     // a cluster shares one strip: block `crank` of `csize` takes k in [kbeg, kend)
     int csize = 1, crank = 0;
@@ -158,15 +163,16 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
     };
 
     if (nchunks > 0) fetch(0);   // weights do not depend on the previous kernel
-    if constexpr (!PERSIST) {
-        if (a.prefetch != nullptr) {
+    {
+        if (!PERSIST && a.prefetch != nullptr) {
             // While this kernel waits for its predecessor and works, the weights of a kernel further down
             // the stream travel from HBM to L2: each block asks for its share, one 128-byte line per thread.
             const long long lines = (a.prefetch_bytes + 127) / 128;
             for (long long i = (long long)blockIdx.x * 128 + tid; i < lines; i += (long long)gridDim.x * 128)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(a.prefetch + i * 128));
         }
-        asm volatile("griddepcontrol.wait;" ::: "memory");   // everything below reads what it wrote
+        sync.wait();   // everything below reads what earlier work wrote
+        if (sync.gave_up()) return;
     }
 
     const bool normalise = a.X == nullptr;

@@ -118,6 +118,7 @@ class StepContext:
         self.temperature = self.uniform = None
         self.weight_order: Optional[WeightOrder] = None
         self.side_stream = None           # a second CUDA stream for work beside the main chain (prefetch)
+        self.program = None               # a kernels.Program: decode steps of few rows run as one persistent kernel
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)

@@ -53,7 +53,7 @@ class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", *, cache_tokens: Optional[int] = None,
                  num_pages: Optional[int] = None, page_size: int = 16, max_batch_tokens: int = 2048,
                  max_requests: int = 64, share_prefixes: bool = False, device: str = "cuda:0",
-                 config: Optional[ModelConfig] = None, use_graphs: bool = True):
+                 config: Optional[ModelConfig] = None, use_graphs: bool = True, use_programs: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("glassbox_b200 needs a CUDA device: every kernel is CUDA and there is no CPU path")
         self.device = torch.device(device)
@@ -89,6 +89,9 @@ class Engine:
         self.ctx.weight_order = self.weight_order
         self.side_stream = torch.cuda.Stream(device=self.device)
         self.ctx.side_stream = self.side_stream
+        self.use_programs = bool(use_programs) and self.dtype == torch.bfloat16 and self.model.program_safe
+        if self.use_programs:
+            self.ctx.program = kernels.Program()
         self._meta_dev = torch.empty(1 << 16, dtype=torch.int32, device=self.device)
         self._stage = [torch.empty(1 << 16, dtype=torch.int32).pin_memory() for _ in range(4)]
         self._stage_np = [t.numpy() for t in self._stage]
@@ -414,6 +417,8 @@ class Engine:
         self._bind(ctx, meta, off, n, S, n_want, Pb)
         ctx.weight_order = self.weight_order
         ctx.side_stream = self.side_stream
+        if self.use_programs:
+            ctx.program = kernels.Program()
         ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(S)]
         ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, max_rows, decode_only
         ctx.leading_single = lead

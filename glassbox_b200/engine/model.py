@@ -10,10 +10,17 @@ from typing import Dict, List
 
 import torch
 
+from .. import kernels
 from ..config.specs import ModelConfig
 from ..parts import Embedding, LmHead, build_block, build_part
 from ..parts.base import Mixer, Part
 from ..weights.binding import ParamSpec
+
+
+def _all_parts(part: Part):
+    yield part
+    for sub in part.sub_parts().values():
+        yield from _all_parts(sub)
 
 
 def _collect(prefix: str, part: Part, out: Dict[str, ParamSpec], owners: Dict[str, tuple]) -> None:
@@ -40,6 +47,10 @@ class DecoderModel:
             _collect(f"layers.{i}", layer, self._specs, self._owners)
         _collect("final_norm", self.final_norm, self._specs, self._owners)
         _collect("head", self.head, self._specs, self._owners)
+        #: whether a decode step of this model may be recorded as a program for the persistent kernel: only when
+        #: no part enqueues device work behind the kernel library's back
+        self.program_safe = all(p.launches_through_kernels_only
+                                for top in (self.embed, *self.layers, self.final_norm, self.head) for p in _all_parts(top))
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return dict(self._specs)
@@ -84,9 +95,23 @@ class DecoderModel:
         if getattr(ctx, "weight_order", None) is not None:
             ctx.weight_order.start_step()
         x = ctx.scratch("x", (n, d), torch.float32)
+        program = getattr(ctx, "program", None)
+        if program is not None and not (ctx.decode_only and self.program_safe and program.takes_rows(n)):
+            program = None
+        if program is not None:
+            kernels.program_begin(program, ctx.status)
+        try:
+            return self._forward(ctx, x, program is not None)
+        finally:
+            if program is not None:
+                kernels.program_end()
+
+    def _forward(self, ctx, x, in_program: bool) -> torch.Tensor:
+        n, d = ctx.n, self.config.hidden_size
         self.embed.forward(ctx, ctx.tokens, x)
         schedule = self.config.schedule
-        side = ctx.side_stream if ctx.decode_only else None
+        # (a program's persistent kernel asks for the next layer's keys and values itself)
+        side = ctx.side_stream if ctx.decode_only and not in_program else None
         pending = False
         for i, run in enumerate(schedule):
             hook = None

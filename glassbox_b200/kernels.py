@@ -62,6 +62,16 @@ _SIGNATURES = {
     "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P],
     "gb_gemm_tcgen05_supported": [_P, _P, _I, _I, _I, _LL, _LL],
     "gb_gemm_tcgen05_gated": [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P],
+    "gb_program_encode_gemm": [_P, _P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _I],
+    "gb_program_encode_gemm_qkv": [_P, _P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I,
+                                   _I, _LL, _I, _P],
+    "gb_program_encode_attention": [_P, _P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
+                                    _P, _P, _I],
+    "gb_program_launch": [_P, _I, _I, _I, _I, _I, _P, _P, _I, _P],
+    "gb_program_launch_with_absent_blocks": [_P, _I, _I, _I, _I, _I, _P, _P, _I, _LL, _P],
+    "gb_program_launch_traced": [_P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "gb_program_op_bytes": [],
+    "gb_program_max_rows": [],
 }
 
 
@@ -106,10 +116,136 @@ launch_count = 0
 
 def _call(name: str, *args) -> None:
     global launch_count
+    if _program is not None:
+        _program.flush()          # a kernel that is launched now must come after what was recorded before it
     launch_count += 1
     rc = getattr(lib(), name)(*args)
     if rc != 0:
         raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or f"{name} failed with code {rc}")
+
+
+# -------------------------------------------------------------------------------------- decode programs
+BY_ROWS, BY_OPERATIONS = 0, 1
+#: the default way in which a program's persistent kernel shares the work (see ``Program.how``)
+PROGRAM_HOW = BY_ROWS
+
+
+class Program:
+    """A chain of small decode kernels written down as operations and run by one persistent kernel
+    (``csrc/decode_program.cu``). While a program is open (``program_begin`` .. ``program_end``), the products of at
+    most ``max_rows`` rows that ``gemm_stream`` / ``gemm_stream_qkv`` would launch and the attention that
+    ``attention_decode_mma`` would launch are appended to it instead; any other kernel launched through this module
+    first runs what has been recorded so far, so the order of the work never changes. Nothing here knows what the
+    operations belong to: parts call the same functions as ever.
+
+    A program object remembers the operation arrays it has run (one per flush of a step, in order). When a step
+    records exactly the same operations again (same buffers, same shapes: the second run of a step that is being
+    recorded into a CUDA graph, or the next step of the same shape), the copy on the device is reused."""
+
+    def __init__(self):
+        handle = lib()
+        self.op_bytes = int(handle.gb_program_op_bytes())
+        self.max_rows = int(handle.gb_program_max_rows())
+        self.segments = []
+        self.cursor = 0
+        self.absent_blocks, self.wait_cycles = 0, 0
+        self.trace_next, self.traces = False, []
+        #: how the persistent kernel shares the work: BY_ROWS (a thread-block cluster per group of rows runs the whole
+        #: program for them) or BY_OPERATIONS (all resident blocks share each operation and meet at a barrier)
+        self.how = PROGRAM_HOW
+        self._buf = ctypes.create_string_buffer(self.op_bytes)
+        self._reset()
+
+    def _reset(self):
+        self._pending, self._n, self._rows, self._hd, self._bk, self._max_vblocks = [], 0, 0, 0, 0, 1
+        self._status = None
+
+    def start_step(self):
+        self.cursor = 0
+        self._reset()
+
+    def _add(self, name, vblocks, rows, *args):
+        rc = getattr(lib(), name)(ctypes.addressof(self._buf), *args)
+        if rc != 0:
+            raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or f"{name} failed with code {rc}")
+        self._pending.append(self._buf.raw)
+        self._n += 1
+        self._rows = max(self._rows, rows)
+        self._max_vblocks = max(self._max_vblocks, vblocks)
+
+    def takes_rows(self, rows: int) -> bool:
+        return 1 <= rows <= self.max_rows
+
+    def takes_attention(self, hd: int, block_keys: int) -> bool:
+        """One program runs one attention variant; a second one waits for the next program."""
+        bk = 16 if (hd == 64 and block_keys == 16) or hd == 128 else 32
+        return self._hd in (0, hd) and (self._hd == 0 or self._bk == bk)
+
+    def flush(self) -> None:
+        """Run what has been recorded (one launch) and start an empty recording."""
+        global launch_count
+        if not self._n:
+            return
+        host = b"".join(self._pending)
+        n, rows, hd, bk, max_vblocks, status = self._n, self._rows, self._hd, self._bk, self._max_vblocks, self._status
+        self._reset()
+        k = self.cursor
+        if k < len(self.segments) and self.segments[k]["host"] == host:
+            seg = self.segments[k]
+        else:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("a decode program changed between the run that prepared a CUDA graph and its recording")
+            dev = torch.empty(len(host), dtype=torch.uint8, device=status.device)
+            dev.copy_(torch.frombuffer(bytearray(host), dtype=torch.uint8))
+            seg = {"host": host, "dev": dev, "barrier": torch.zeros(1, dtype=torch.int32, device=status.device)}
+            del self.segments[k:]
+            self.segments.append(seg)
+        self.cursor = k + 1
+        launch_count += 1
+        if self.trace_next:        # (a measurement: per-operation clock values of the first and the last block)
+            self.traces.append((n, torch.zeros(2 * n * 4, dtype=torch.int64, device=status.device), host))
+            rc = lib().gb_program_launch_traced(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks, seg["barrier"].data_ptr(),
+                                                status.data_ptr(), self.how, self.traces[-1][1].data_ptr(), _stream())
+        elif self.absent_blocks:     # (a test of the barrier's bounded wait)
+            rc = lib().gb_program_launch_with_absent_blocks(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks,
+                                                            seg["barrier"].data_ptr(), status.data_ptr(), self.absent_blocks,
+                                                            self.wait_cycles, _stream())
+        else:
+            rc = lib().gb_program_launch(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks, seg["barrier"].data_ptr(),
+                                         status.data_ptr(), self.how, _stream())
+        if rc != 0:
+            raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or f"gb_program_launch failed with code {rc}")
+
+
+_program: Optional[Program] = None
+
+
+def program_begin(program: Program, status: torch.Tensor) -> None:
+    """Start recording into ``program``; ``status`` is the device status word its kernel reports to."""
+    global _program
+    if _program is not None:
+        raise KernelError("a decode program is already being recorded")
+    program.start_step()
+    program._status = status
+    program._default_status = status
+    _program = program
+
+
+def program_end() -> None:
+    """Run what is still recorded and stop recording."""
+    global _program
+    if _program is not None:
+        try:
+            _program.flush()
+        finally:
+            _program = None
+
+
+def _program_for(status: Optional[torch.Tensor] = None) -> Optional[Program]:
+    p = _program
+    if p is not None and p._status is None:
+        p._status = status if status is not None else p._default_status
+    return p
 
 
 def _ptr(t: Optional[torch.Tensor]) -> int:
@@ -258,6 +394,11 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
         mode = 0 if c.dtype == torch.bfloat16 else 1
         assert c.dtype in (torch.bfloat16, torch.float32)
     x, ldx, xres, ldr, gain, eps = _stream_input(a, norm)
+    prog = _program_for()
+    if prog is not None and prog.takes_rows(M):
+        prog._add("gb_program_encode_gemm", -(-N // 16), M, x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(c),
+                  c.stride(0), mode, M, N, K)
+        return
     _call("gb_gemm_stream", x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(c), c.stride(0), mode, M, N, K,
           *_prefetch_args(prefetch), 1 if USE_PDL else 0, _stream())
 
@@ -290,6 +431,13 @@ def gemm_stream_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_s
     if cos_sin is not None:
         assert cos_sin.shape[1] == hd // 2
     x, ldx, xres, ldr, gain, eps = _stream_input(a, norm)
+    prog = _program_for(status)
+    if prog is not None and prog.takes_rows(M):
+        prog._add("gb_program_encode_gemm_qkv", (nh + 2 * nkv) * (hd // 32), M, x, ldx, xres, ldr, gain, eps, _ptr(w),
+                  w.stride(0), _ptr(q_out), q_out.stride(0), M, K, _ptr(cos_sin),
+                  cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slots), _ptr(kcache), _ptr(vcache),
+                  nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status))
+        return
     _call("gb_gemm_stream_qkv", x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(q_out), q_out.stride(0), M, K,
           _ptr(cos_sin), cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slots), _ptr(kcache),
           _ptr(vcache), nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status),
@@ -449,6 +597,17 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
     assert part_acc.numel() >= n * nh * 4 * splits * hd and part_ml.numel() >= n * nh * 4 * splits * 2
     assert counters.numel() >= n * nkv
+    prog = _program_for(status)
+    if prog is not None and prog.takes_rows(n):
+        if not prog.takes_attention(hd, block_keys):
+            prog.flush()
+            prog._status = status
+        prog._add("gb_program_encode_attention", splits * nkv * n, n, _ptr(q), q.stride(0), _ptr(out), out.stride(0),
+                  _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n,
+                  nh, nkv, hd, page_size, kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc),
+                  _ptr(part_ml), _ptr(counters), _ptr(status), int(block_keys))
+        prog._hd, prog._bk = hd, (16 if (hd == 64 and block_keys == 16) or hd == 128 else 32)
+        return
     _call("gb_attention_decode_mma_pdl", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
           _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
           kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml), _ptr(counters),

@@ -19,6 +19,7 @@ from .linear import _resolve, linear, weights_ahead
 
 class GqaAttention(Mixer):
     accepts_deferred_input = True
+    launches_through_kernels_only = True
 
     def __init__(self, spec, *, hidden_size: int):
         super().__init__(spec)

@@ -50,6 +50,12 @@ class StateSpec:
 
 
 class Part:
+    #: True when every piece of device work this part does is a call into ``glassbox_b200.kernels``. Only then may
+    #: its calls be recorded into a decode program and run later, in order, by one persistent kernel; a part that
+    #: also enqueues work of its own (torch operations, other libraries) keeps the default and always runs
+    #: kernel by kernel.
+    launches_through_kernels_only = False
+
     def __init__(self, spec: Any):
         self.spec = spec
         self.params: Dict[str, torch.Tensor] = {}

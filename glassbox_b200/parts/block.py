@@ -10,6 +10,8 @@ from .base import DeferredNorm, Part, build_part, register_part
 
 
 class PreNormBlock(Part):
+    launches_through_kernels_only = True
+
     def __init__(self, spec, *, hidden_size: int):
         super().__init__(spec)
         self.hidden_size = hidden_size

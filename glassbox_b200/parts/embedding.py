@@ -13,6 +13,8 @@ from .linear import linear
 
 
 class Embedding(Part):
+    launches_through_kernels_only = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         super().__init__(None)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
@@ -25,6 +27,8 @@ class Embedding(Part):
 
 
 class LmHead(Part):
+    launches_through_kernels_only = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         super().__init__(None)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size

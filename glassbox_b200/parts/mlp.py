@@ -11,6 +11,7 @@ from .linear import gated_linear, linear
 
 class SwiGlu(FeedForward):
     accepts_deferred_input = True
+    launches_through_kernels_only = True
 
     def __init__(self, spec, *, hidden_size: int):
         super().__init__(spec)

@@ -8,6 +8,8 @@ from .base import Norm, register_part
 
 
 class RmsNorm(Norm):
+    launches_through_kernels_only = True
+
     def __init__(self, spec, *, hidden_size: int):
         super().__init__(spec)
         self.eps = float(spec.eps)

@@ -27,6 +27,8 @@ def rotary_table(theta: float, rotary_dim: int, max_position: int) -> torch.Tens
 
 
 class Rope(Position):
+    launches_through_kernels_only = True
+
     def __init__(self, spec, **_):
         super().__init__(spec)
         if spec.pairing != "half":
@@ -44,6 +46,8 @@ class Rope(Position):
 
 
 class NoPosition(Position):
+    launches_through_kernels_only = True
+
     def __init__(self, spec=None, **_):
         super().__init__(spec)
 

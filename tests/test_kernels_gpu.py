@@ -963,3 +963,147 @@ def test_prefill_attention_at_the_benchmarked_context_lengths(nh, nkv, ps, start
         fn(qd, out, k, v, tables, first, start_pos, rows, nh, nkv, hd, ps, hd ** -0.5, None, st)
         diff = (out.double().reshape(rows, nh, hd) - ref).abs().amax(dim=(1, 2))
         assert int(st) == 0 and diff.max() <= tol(dtype, 2), f"{name}: row {int(diff.argmax())} off by {float(diff.max()):.3e}"
+
+
+# ---------------------------------------------------------------------------- the persistent decode program
+def _decode_chain(M, d, nh, nkv, hd, inter, layers, ps, ctx_len, seed):
+    """Operands of a chain of decode operations as a model's layers would issue them (norm + QKV + rotation + cache
+    write, attention, O projection into the residual, norm + gate/up + SwiGLU, down projection into the residual),
+    for M rows that each continue a request of its own."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    bf = torch.bfloat16
+    rnd = lambda *shape, s=0.05: (torch.randn(*shape, generator=g, device=DEV) * s).to(bf)
+    lens = [ctx_len - 3 * i for i in range(M)]
+    k, v, tables, dense = long_cache(bf, lens, nkv, hd, ps, seed=seed)
+    w = [dict(wqkv=rnd((nh + 2 * nkv) * hd, d), wo=rnd(d, nh * hd), wgu=rnd(2 * inter, d), wdown=rnd(d, inter),
+              g1=1 + 0.1 * torch.randn(d, generator=g, device=DEV), g2=1 + 0.1 * torch.randn(d, generator=g, device=DEV))
+         for _ in range(layers)]
+    x0 = torch.randn(M, d, generator=g, device=DEV)
+    positions = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    row_seq = torch.arange(M, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(tables[s, (l - 1) // ps]) * ps + (l - 1) % ps for s, l in enumerate(lens)], dtype=torch.int32, device=DEV)
+    from glassbox_b200.parts.rope import rotary_table
+    rope = rotary_table(10000.0, hd, ctx_len + 8).to(DEV)
+    return dict(k=k, v=v, tables=tables, w=w, x0=x0, positions=positions, row_seq=row_seq, slots=slots, rope=rope, lens=lens)
+
+
+def _run_chain(c, M, d, nh, nkv, hd, inter, ps, st, splits):
+    from glassbox_b200 import kernels
+    bf = torch.bfloat16
+    x = c["x0"].clone()
+    k, v = c["k"].clone(), c["v"].clone()
+    qkv = torch.zeros(M, (nh + 2 * nkv) * hd, device=DEV, dtype=bf)
+    att = torch.zeros(M, nh * hd, device=DEV, dtype=bf)
+    act = torch.zeros(M, inter, device=DEV, dtype=bf)
+    part_acc = torch.empty(M * nh * 4 * splits * hd, device=DEV)
+    part_ml = torch.empty(M * nh * 4 * splits * 2, device=DEV)
+    counters = torch.zeros(M * nkv, dtype=torch.int32, device=DEV)
+    for lw in c["w"]:
+        kernels.gemm_stream_qkv(x, lw["wqkv"], qkv, c["rope"], c["positions"], c["slots"], k, v, nh, nkv, hd, ps, True, st,
+                                norm=(lw["g1"], 1e-5))
+        kernels.attention_decode_mma(qkv[:, :nh * hd], att, k, v, c["tables"], c["row_seq"], c["positions"], nh, nkv, hd, ps,
+                                     hd ** -0.5, None, splits, part_acc, part_ml, counters, st)
+        kernels.gemm_stream(att, lw["wo"], x, accumulate=True)
+        kernels.gemm_stream(x, lw["wgu"], act, gated=True, norm=(lw["g2"], 1e-5))
+        kernels.gemm_stream(act, lw["wdown"], x, accumulate=True)
+    return x, k, v, (qkv, att, act, part_acc, part_ml, counters)
+
+
+@pytest.mark.parametrize("how", ["by rows", "by operations"])
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("d, nh, nkv, hd, inter", [(576, 9, 3, 64, 512), (96, 3, 1, 32, 176), (256, 2, 2, 128, 320)])
+def test_decode_program_runs_the_operations_the_kernels_would(M, d, nh, nkv, hd, inter, how):
+    """The same chain of calls, once launched kernel by kernel and once recorded into a program and run by the
+    persistent kernel: with every K below 1,024 the stand-alone kernels take the same 512-wide chunks and no cluster,
+    so the sums are formed in the same order and the results must be equal bit for bit, residual rows and cache alike.
+    Run twice, so that the barrier word and the attention's counters are shown to come back to their start."""
+    from glassbox_b200 import kernels
+    ps, layers, ctx_len, splits = 16, 3, 300, 3
+    c = _decode_chain(M, d, nh, nkv, hd, inter, layers, ps, ctx_len, seed=M)
+    st = status()
+    want_x, want_k, want_v, _ = _run_chain(c, M, d, nh, nkv, hd, inter, ps, st, splits)
+    assert int(st) == 0
+    prog = kernels.Program()
+    prog.how = kernels.BY_ROWS if how == "by rows" else kernels.BY_OPERATIONS
+    for rep in range(2):
+        before = kernels.launch_count
+        kernels.program_begin(prog, st)
+        try:
+            got_x, got_k, got_v, keep = _run_chain(c, M, d, nh, nkv, hd, inter, ps, st, splits)
+        finally:
+            kernels.program_end()
+        assert kernels.launch_count - before == 1, "the chain was not one launch"
+        assert int(st) == 0
+        assert torch.equal(got_x, want_x) and torch.equal(got_k, want_k) and torch.equal(got_v, want_v), f"pass {rep}"
+        assert len(prog.segments) == 1
+        del keep
+
+
+@pytest.mark.parametrize("how", ["by rows", "by operations"])
+def test_decode_program_with_long_k_and_a_kernel_in_between(how):
+    """K of 1,536 and 2,048 (the stand-alone kernel would split these over a cluster: another order of the sums, so the
+    comparison is with a float64 statement), and a kernel that is not part of programs in the middle of the chain: what was
+    recorded before it must run before it, what comes after it after."""
+    from glassbox_b200 import kernels
+    M, d, inter = 7, 2048, 1536
+    g = torch.Generator(device=DEV).manual_seed(3)
+    bf = torch.bfloat16
+    a = (torch.randn(M, d, generator=g, device=DEV)).to(bf)
+    w1 = (torch.randn(inter * 2, d, generator=g, device=DEV) * 0.03).to(bf)
+    w2 = (torch.randn(d, inter, generator=g, device=DEV) * 0.03).to(bf)
+    act = torch.zeros(M, inter, device=DEV, dtype=bf)
+    acted = torch.zeros(M, inter, device=DEV, dtype=bf)
+    x = torch.zeros(M, d, device=DEV)
+    gate_up = torch.zeros(M, 2 * inter, device=DEV, dtype=bf)
+    prog, st = kernels.Program(), status()
+    prog.how = kernels.BY_ROWS if how == "by rows" else kernels.BY_OPERATIONS
+    kernels.program_begin(prog, st)
+    try:
+        kernels.gemm_stream(a, w1, gate_up)                       # recorded
+        kernels.swiglu(gate_up, acted)                            # launched: flushes the product before it
+        kernels.gemm_stream(a, w1, act, gated=True)               # recorded
+        kernels.gemm_stream(act, w2, x, accumulate=True)          # recorded: reads what the one before wrote
+    finally:
+        kernels.program_end()
+    assert len(prog.segments) == 2 and int(st) == 0
+    gu = a.double() @ w1.double().T
+    ref_act = (gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:])
+    assert (acted.double() - ref_act).abs().max() <= 0.02 * ref_act.abs().max()
+    assert torch.equal(act, acted) or (act.double() - acted.double()).abs().max() <= 0.01 * ref_act.abs().max()
+    ref_x = act.double() @ w2.double().T
+    assert (x.double() - ref_x).abs().max() <= 2e-3 * ref_x.abs().max()
+
+
+def test_a_wait_at_the_programs_barrier_that_runs_out_is_reported_and_harms_nothing():
+    """The persistent kernel's barrier waits are bounded. Here every barrier is told to expect one block more than the
+    grid has and to give up after a millisecond of cycles: the kernel must return by itself, the status word must carry
+    the wait-timeout bit, the operations behind the first barrier must not have run, and the same program launched
+    normally right afterwards must work."""
+    from glassbox_b200 import kernels
+    M, d = 4, 256
+    g = torch.Generator(device=DEV).manual_seed(5)
+    a = torch.randn(M, d, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(d, d, generator=g, device=DEV) * 0.05).to(torch.bfloat16)
+    h = torch.zeros(M, d, device=DEV, dtype=torch.bfloat16)
+    out = torch.full((M, d), 7.0, device=DEV)
+
+    def chain(prog, st):
+        kernels.program_begin(prog, st)
+        try:
+            kernels.gemm_stream(a, w, h)
+            kernels.gemm_stream(h, w, out)
+        finally:
+            kernels.program_end()
+
+    prog, st = kernels.Program(), status()
+    prog.absent_blocks, prog.wait_cycles = 1, 2_000_000
+    chain(prog, st)
+    torch.cuda.synchronize()
+    assert int(st) == 8, "the wait-timeout bit, and only it"
+    assert float((out - 7.0).abs().max()) == 0.0, "an operation behind the barrier ran although the barrier never opened"
+    with pytest.raises(kernels.KernelError, match="bounded wait"):
+        kernels.check_status(st)
+    prog.absent_blocks = 0
+    chain(prog, st)
+    ref = (a.double() @ w.double().T).to(torch.bfloat16).double() @ w.double().T
+    assert int(st) == 0 and (out.double() - ref).abs().max() <= 1e-2 * ref.abs().max()
