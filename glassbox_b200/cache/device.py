@@ -57,6 +57,9 @@ class DeviceCache:
                 self.state[c] = torch.zeros((max_requests,) + tuple(spec.shape), dtype=spec.dtype, device=device)
             elif spec is not None:
                 raise TypeError(f"cache layer {c}: unknown cache spec {spec!r}")
+        # Sampling state of each live request, in its state slot: {generator state low word, high word, temperature
+        # bits, unused}; zero (greedy) for a fresh slot, copied on fork like every other per-request state.
+        self.sampling = torch.zeros((max_requests, 4), dtype=torch.int32, device=device)
         self.group_pages = [int(pages_per_group(s)) for s in self.group_specs]
         self.k: List[torch.Tensor] = []
         self.v: List[torch.Tensor] = []
@@ -85,11 +88,26 @@ class DeviceCache:
         return None
 
     def zero_slots(self, slots: List[int]) -> None:
-        if slots and self.state:
-            idx = torch.tensor(slots, dtype=torch.long, device=next(iter(self.state.values())).device)
+        """Fresh slots start from zero: the mixers' states, and the sampling state (temperature 0: greedy)."""
+        if slots:
+            idx = torch.tensor(slots, dtype=torch.long, device=self.sampling.device)
+            self.sampling.index_fill_(0, idx, 0)
             for t in self.state.values():
                 t.index_fill_(0, idx, 0)
 
     def copy_slot(self, src: int, dst: int) -> None:
         for t in self.state.values():
             t[dst].copy_(t[src])
+        self.sampling[dst].copy_(self.sampling[src])
+
+    def set_sampling(self, slot: int, temperature: float, rng_state: int) -> None:
+        import struct
+        bits = struct.unpack("<i", struct.pack("<f", float(temperature)))[0]
+        lo, hi = rng_state & 0xFFFFFFFF, (rng_state >> 32) & 0xFFFFFFFF
+        as_i32 = lambda u: u - (1 << 32) if u >= (1 << 31) else u
+        row = torch.tensor([as_i32(lo), as_i32(hi), bits, 0], dtype=torch.int32)
+        self.sampling[slot].copy_(row, non_blocking=False)
+
+    def get_rng_state(self, slot: int) -> int:
+        lo, hi = (int(v) & 0xFFFFFFFF for v in self.sampling[slot, :2].tolist())
+        return (hi << 32) | lo

@@ -69,6 +69,21 @@ class SwiGluSpec:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """Token embedding: the float32 residual row of a token is its row of the table, as it is
+    (crates/glassbox-core/src/model.rs:228-231). Another kind (a scaled table, a learned position added to it) is
+    another registered "embedding" part."""
+    kind: str = "embedding"
+
+
+@dataclass(frozen=True)
+class LmHeadSpec:
+    """Output head: float32 logits = hidden states times the head matrix, no bias, no cap
+    (crates/glassbox-core/src/model.rs:359-361). Another kind is another registered "head" part."""
+    kind: str = "lm_head"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One layer: a mixer and a feed-forward, each behind its norm.
 
@@ -107,6 +122,8 @@ class ModelConfig:
     schedule: Tuple[RunSpec, ...]
     final_norm: Any
     raw: dict = field(default_factory=dict, compare=False, hash=False)
+    embedding: Any = EmbeddingSpec()
+    head: Any = LmHeadSpec()
 
     @property
     def num_cache_layers(self) -> int:

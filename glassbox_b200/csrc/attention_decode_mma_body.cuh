@@ -73,7 +73,7 @@ template <> struct RowLoad<8> {
 // `sync` says how to wait for the work before (GbPdlSync in the stand-alone kernel, a barrier's wait in a persistent
 // one). Queries, which another block of the same launch may have written, are read past L1.
 // Shared memory of the body, provided by the caller.
-struct DecodeAttnSmem {
+struct __align__(16) DecodeAttnSmem {   // (a multiple of 16 bytes, so that arrays of it keep what follows aligned)
     int pages[MMA_MAX_PAGES];
     float weights[MMA_MAX_MERGE];
     int is_last;
@@ -104,7 +104,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     constexpr int KT = BK / 8;    // n8 tiles over the keys of a block (scores)
     constexpr int KB = BK / 16;   // k16 steps over the keys of a block (output)
     constexpr int VW = NT / 2;    // 32-bit words of a value row per thread
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = sync.thread(), lane = tid & 31, warp = tid >> 5;   // 128 threads work on one virtual block
     const int g = lane >> 2, t = lane & 3;
     const int G = nh / nkv;
     const int head0 = kvh * G;
@@ -167,7 +167,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
             }
             pages_s[i] = page;
         }
-        __syncthreads();
+        sync.group_barrier();
     }
     sync.wait();   // the writes of the work before (q, this step's K/V) are visible from here
     if (sync.gave_up()) return;
@@ -318,14 +318,14 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     }
     // ---- the block that arrives last merges every warp of every split
     __threadfence();
-    __syncthreads();
+    sync.group_barrier();
     if (tid == 0) {
         int* counter = counters + (size_t)row * nkv + kvh;
         const int prev = atomicAdd(counter, 1);
         is_last = (prev == splits - 1);
         if (is_last) *counter = 0;
     }
-    __syncthreads();
+    sync.group_barrier();
     if (!is_last) return;
     __threadfence();
     // Merge: one warp per head turns the (maximum, sum) pairs of all sub-splits into normalised
@@ -351,7 +351,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
             __syncwarp();
             for (int sidx = lane; sidx < S4; sidx += 32) weights[hi * S4 + sidx] *= inv;
         }
-        __syncthreads();
+        sync.group_barrier();
         for (int i = tid; i < hcount * HD; i += 128) {
             const int hi = i / HD, d = i % HD;
             const float* pa = part_acc + ((size_t)row * nh + head0 + h0 + hi) * S4 * HD + d;
@@ -361,7 +361,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
             for (int sidx = 0; sidx < S4; ++sidx) v = fmaf(__ldcg(pa + (size_t)sidx * HD), w[sidx], v);
             orow[(head0 + h0 + hi) * HD + d] = __float2bfloat16_rn(v);
         }
-        __syncthreads();
+        sync.group_barrier();
     }
 }
 

@@ -74,6 +74,9 @@ struct GbPdlSync {
     __device__ __forceinline__ void start() { gb_pdl_launch_dependents(); }
     __device__ __forceinline__ void wait() { gb_pdl_wait(); }
     __device__ __forceinline__ bool gave_up() const { return false; }   // after wait(): true = do nothing more
+    // the threads that share one virtual block: here the whole thread block
+    __device__ __forceinline__ int thread() const { return (int)threadIdx.x; }
+    __device__ __forceinline__ void group_barrier() { __syncthreads(); }
 };
 
 enum { GB_PDL_ELEMENTWISE = 1, GB_PDL_GEMM = 2, GB_PDL_ATTENTION = 4 };   // bits of the switch

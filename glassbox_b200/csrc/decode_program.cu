@@ -99,11 +99,15 @@ struct GridSync {
         if (*go == 0) failed = true;
     }
     __device__ __forceinline__ bool gave_up() const { return failed; }
+    __device__ __forceinline__ int thread() const { return (int)threadIdx.x; }
+    __device__ __forceinline__ void group_barrier() { __syncthreads(); }
 };
 
-// The hardware barrier of a thread-block cluster, split in two.
-struct ClusterSync {
+// The hardware barrier of a thread-block cluster, split in two, for blocks in which every 128
+// threads (a group) work on a virtual block of their own.
+struct RowsSync {
     bool waited;
+    int group, group_thread;
     __device__ __forceinline__ void start() {}
     __device__ __forceinline__ void arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
     __device__ __forceinline__ void wait() {
@@ -112,6 +116,8 @@ struct ClusterSync {
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     __device__ __forceinline__ bool gave_up() const { return false; }
+    __device__ __forceinline__ int thread() const { return group_thread; }
+    __device__ __forceinline__ void group_barrier() { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 };
 
 // The share of block `b` of `nb` in bringing the keys and values that an attention operation will read into L2.
@@ -216,75 +222,263 @@ __global__ void __launch_bounds__(128) decode_program_grid_kernel(const ProgramO
 }
 
 // ------------------------------------------------------------------------------------------------ by rows
-// One cluster runs the whole program for rows [cluster * rows_per_cluster, ...). The operations are written for all
-// rows of the step; the cluster's copy of each is moved to its own rows.
-template <int NT, int HD, int BK>
-__global__ void __launch_bounds__(128) decode_program_cluster_kernel(const ProgramOp* __restrict__ ops, int n_ops,
-                                                                     int rows_per_cluster, long long* __restrict__ trace) {
-    __shared__ __align__(16) unsigned char xs[gemm_stream_smem_bytes<NT, 512>()];
-    __shared__ float srow[NT * 8];
-    __shared__ DecodeAttnSmem attn_sm;
+// One cluster of blocks of 256 threads runs the whole program for rows [cluster * R, ...). The rows of a decode step
+// never read each other's activations, so the cluster's own barrier is all the waiting there is. A product is done
+// the plain way for so few rows: a warp owns output features (or pairs of them, where the epilogue needs two: gate
+// and up, the two halves of a rotated head), streams their weight rows in 16-byte pieces (one piece of 1,024 k ahead
+// of the arithmetic, the very first before the wait for the operation before), multiplies with the activation
+// row(s) held in shared memory in float32, and adds up with shuffles. Sums are float32 throughout; what the stand-alone
+// kernel rounds to bfloat16 on the way in (the normalised activations) is rounded here too.
+constexpr int ROWS_THREADS = 256, ROWS_WARPS = 8, ROWS_GROUPS = 2;   // (255 registers a thread: the bodies need them)
+constexpr int ROWS_KC = 1024;   // k per piece: four 16-byte loads per lane and weight row
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// bfloat16 pair in a 32-bit word -> two floats (a bfloat16 is the upper half of a float)
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// acc += dot(8 bfloat16 weights in w, 8 floats x0 x1)
+__device__ __forceinline__ float dot8(const uint4 w, const float4 x0, const float4 x1, float acc) {
+    acc = fmaf(bf16_lo(w.x), x0.x, acc); acc = fmaf(bf16_hi(w.x), x0.y, acc);
+    acc = fmaf(bf16_lo(w.y), x0.z, acc); acc = fmaf(bf16_hi(w.y), x0.w, acc);
+    acc = fmaf(bf16_lo(w.z), x1.x, acc); acc = fmaf(bf16_hi(w.z), x1.y, acc);
+    acc = fmaf(bf16_lo(w.w), x1.z, acc); acc = fmaf(bf16_hi(w.w), x1.w, acc);
+    return acc;
+}
+
+// R: rows the cluster holds (1 or 2). xs: [R][K] floats; red: [R][ROWS_WARPS] floats.
+template <int R>
+__device__ __forceinline__ void rows_product(const StreamArgs& a, float* xs, float* red, const int row0, const int nrows,
+                                             const int gwarp, const int nwarps, RowsSync& sync) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = a.K, mode = a.mode;
+    const bool pair = mode == WS_GLU_BF16 || mode == WS_ROPE_QKV;
+    const int half = a.hd / 2;
+    const int units = mode == WS_ROPE_QKV ? (a.nh + 2 * a.nkv) * half : a.N;
+    const int pieces = (K + ROWS_KC - 1) / ROWS_KC;
+    auto rows_of = [&](int u, int& ra, int& rb) {
+        if (mode == WS_ROPE_QKV) {
+            ra = (u / half) * a.hd + u % half;
+            rb = ra + half;
+        } else {
+            ra = u;
+            rb = u + a.N;   // (gated: the up row)
+        }
+    };
+    uint4 cur[2][4], nxt[2][4];
+    auto fetch = [&](int u, int c, uint4 (&buf)[2][4]) {
+        int ra, rb;
+        rows_of(u, ra, rb);
+        const __nv_bfloat16* wa = a.W + (size_t)ra * a.ldw;
+        const __nv_bfloat16* wb = a.W + (size_t)rb * a.ldw;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = c * ROWS_KC + j * 256 + lane * 8;
+            buf[0][j] = k < K ? ldg_stream(wa + k) : make_uint4(0, 0, 0, 0);
+            if (pair) buf[1][j] = k < K ? ldg_stream(wb + k) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    int u = gwarp, c = 0;
+    if (u < units) fetch(u, 0, cur);      // weights do not depend on the operation before
+    sync.wait();                          // ... the activations do
+
+    // ---- the cluster's activation rows into shared memory, as float32
+    if (a.X != nullptr) {
+        for (int idx = tid * 8; idx < nrows * K; idx += ROWS_THREADS * 8) {
+            const int r = idx / K, k = idx - r * K;
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(a.X + (size_t)(row0 + r) * a.ldx + k));
+            float4* dst = reinterpret_cast<float4*>(xs + (size_t)r * K + k);
+            dst[0] = make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
+            dst[1] = make_float4(bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w));
+        }
+    } else {   // RMSNorm on the way in: gain * (x * s), rounded to bfloat16 as the separate norm kernel writes it
+        float ss[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            ss[r] = 0.f;
+            if (r < nrows) {
+                const float* xr = a.xres + (size_t)(row0 + r) * a.ldr;
+                for (int k = tid * 4; k < K; k += ROWS_THREADS * 4) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(xr + k));
+                    ss[r] = fmaf(v.x, v.x, ss[r]); ss[r] = fmaf(v.y, v.y, ss[r]);
+                    ss[r] = fmaf(v.z, v.z, ss[r]); ss[r] = fmaf(v.w, v.w, ss[r]);
+                }
+            }
+            ss[r] = gb_warp_sum(ss[r]);
+            if (lane == 0) red[r * ROWS_WARPS + warp] = ss[r];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (r >= nrows) continue;
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < ROWS_WARPS; ++w) tot += red[r * ROWS_WARPS + w];
+            const float sc = 1.0f / sqrtf(tot / (float)K + a.eps);
+            const float* xr = a.xres + (size_t)(row0 + r) * a.ldr;
+            for (int k = tid * 4; k < K; k += ROWS_THREADS * 4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(xr + k));
+                const float4 g = *reinterpret_cast<const float4*>(a.gain + k);
+                *reinterpret_cast<float4*>(xs + (size_t)r * K + k) =
+                    make_float4(bf16_round(g.x * (v.x * sc)), bf16_round(g.y * (v.y * sc)), bf16_round(g.z * (v.z * sc)),
+                                bf16_round(g.w * (v.w * sc)));
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- this warp's output features: two register sets of weights take turns, one in flight while the other is used
+    float acc[2][R];
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2)
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[s2][r] = 0.f;
+    auto use = [&](const int uu, const int cc, const uint4 (&buf)[2][4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = cc * ROWS_KC + j * 256 + lane * 8;
+            if (k < K) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    if (r >= nrows) continue;
+                    const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)r * K + k);
+                    const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)r * K + k + 4);
+                    acc[0][r] = dot8(buf[0][j], x0, x1, acc[0][r]);
+                    if (pair) acc[1][r] = dot8(buf[1][j], x0, x1, acc[1][r]);
+                }
+            }
+        }
+        if (cc != pieces - 1) return;
+        // the feature's last piece: add up over the lanes, then lane r finishes row r
+        float mine0 = 0.f, mine1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float s0 = gb_warp_sum(acc[0][r]);
+            const float s1 = pair ? gb_warp_sum(acc[1][r]) : 0.f;
+            if (lane == r) {
+                mine0 = s0;
+                mine1 = s1;
+            }
+            acc[0][r] = 0.f;
+            acc[1][r] = 0.f;
+        }
+        if (lane >= nrows) return;
+        const int tok = row0 + lane;
+        if (mode == WS_ROPE_QKV) {
+            const int pos = a.positions[tok];
+            if (pos < 0) return;   // a padding row
+            const int head = uu / half, i = uu % half;
+            float y0 = mine0, y1 = mine1;
+            if (head < a.nh + a.nkv && a.rope != nullptr) {
+                if (pos >= a.max_pos) {
+                    atomicOr(a.status, GB_STATUS_BAD_POSITION);
+                } else {
+                    const float2 cs = a.rope[(size_t)pos * half + i];
+                    y0 = mine0 * cs.x - mine1 * cs.y;
+                    y1 = mine1 * cs.x + mine0 * cs.y;
+                }
+            }
+            if (head < a.nh) {
+                __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)tok * a.ldc + (size_t)head * a.hd;
+                q[i] = __float2bfloat16_rn(y0);
+                q[i + half] = __float2bfloat16_rn(y1);
+            } else if (a.write_kv) {
+                const long long slot = a.slots[tok];
+                if (slot < 0 || slot >= a.num_slots) {
+                    atomicOr(a.status, GB_STATUS_BAD_SLOT);
+                } else {
+                    const bool is_k = head < a.nh + a.nkv;
+                    const int kvh = is_k ? head - a.nh : head - a.nh - a.nkv;
+                    __nv_bfloat16* base = is_k ? a.kcache : a.vcache;
+                    __nv_bfloat16* dst = base + (((slot / a.page_size) * a.nkv + kvh) * a.page_size + slot % a.page_size) * a.hd;
+                    dst[i] = __float2bfloat16_rn(y0);
+                    dst[i + half] = __float2bfloat16_rn(y1);
+                }
+            }
+        } else if (mode == WS_GLU_BF16) {
+            reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + uu] = __float2bfloat16_rn(mine0 / (1.0f + __expf(-mine0)) * mine1);
+        } else if (mode == WS_STORE_BF16) {
+            reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + uu] = __float2bfloat16_rn(mine0);
+        } else if (mode == WS_STORE_F32) {
+            reinterpret_cast<float*>(a.C)[(size_t)tok * a.ldc + uu] = mine0;
+        } else {
+            float* p = reinterpret_cast<float*>(a.C) + (size_t)tok * a.ldc + uu;
+            __stcg(p, __ldcg(p) + mine0);
+        }
+    };
+    auto step = [&](int& uu, int& cc) {   // the piece after (uu, cc) in this warp's order
+        if (++cc >= pieces) {
+            cc = 0;
+            uu += nwarps;
+        }
+    };
+    while (u < units) {
+        int u1 = u, c1 = c;
+        step(u1, c1);
+        if (u1 < units) fetch(u1, c1, nxt);
+        use(u, c, cur);
+        if (u1 >= units) break;
+        u = u1; c = c1;
+        step(u, c);
+        if (u < units) fetch(u, c, cur);
+        use(u1, c1, nxt);
+    }
+}
+
+template <int HD, int BK>
+__device__ __noinline__ void rows_attention(const DecodeAttnArgs& a, int split, int kvh, int row, DecodeAttnSmem& sm, RowsSync& sync) {
+    attention_decode_mma_body<HD, BK>(a, split, kvh, row, sm, sync);
+}
+
+// Dynamic shared memory: the attention groups' scratch, then R * (longest K of the program) floats. With a trace buffer ([2, n_ops, 4] clock64
+// values) the first and the last block of the first cluster note, for every operation, when they started it, had its
+// description, had done their share (and seen the barrier before it), and had arrived at the barrier behind it.
+template <int R, int HD, int BK>
+__global__ void __launch_bounds__(ROWS_THREADS, 1) decode_program_rows_kernel(const ProgramOp* __restrict__ ops, int n_ops,
+                                                                              int total_rows, long long* __restrict__ trace) {
+    extern __shared__ __align__(16) unsigned char dyn[];   // [ROWS_GROUPS] DecodeAttnSmem, then the activation rows
+    DecodeAttnSmem* attn_sm = reinterpret_cast<DecodeAttnSmem*>(dyn);
+    static_assert(sizeof(DecodeAttnSmem) % 16 == 0, "the activation rows behind the attention scratch are read 16 bytes at a time");
+    float* xs_dyn = reinterpret_cast<float*>(dyn + ROWS_GROUPS * sizeof(DecodeAttnSmem));
+    __shared__ float red[R * ROWS_WARPS];
     __shared__ ProgramSmem ps;
     unsigned rank, csize, cluster;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
     asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(cluster));
-    const int tid = threadIdx.x, b = (int)rank, nb = (int)csize;
-    const int row0 = (int)cluster * rows_per_cluster;
-    const int traced = (trace != nullptr && tid == 0 && cluster == 0) ? (b == 0 ? 0 : (b == nb - 1 ? 1 : -1)) : -1;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int row0 = (int)cluster * R, nrows = min(R, total_rows - row0);
+    const int traced = (trace != nullptr && tid == 0 && cluster == 0) ? (rank == 0 ? 0 : (rank == csize - 1 ? 1 : -1)) : -1;
     auto mark = [&](int i, int what) {
         if (traced >= 0) trace[((size_t)traced * n_ops + i) * 4 + what] = clock64();
     };
-    ClusterSync sync;
+    RowsSync sync;
+    sync.group = tid >> 7;
+    sync.group_thread = tid & 127;
     for (int i = 0; i < n_ops; ++i) {
         __syncthreads();
         mark(i, 0);
         load_op(ps, ops, i);
         __syncthreads();
-        const int kind = ps.op.kind;
-        int nrows = 0;
-        if (kind == OP_GEMM) {
-            nrows = min(rows_per_cluster, ps.op.gemm.M - row0);
-            if (tid == 0 && nrows > 0) {   // this cluster's rows of the operands
-                StreamArgs& a = ps.op.gemm;
-                if (a.X != nullptr) a.X += (size_t)row0 * a.ldx;
-                if (a.xres != nullptr) a.xres += (size_t)row0 * a.ldr;
-                const size_t elem = (a.mode == WS_STORE_F32 || a.mode == WS_ADD_F32) ? 4 : 2;
-                a.C = reinterpret_cast<unsigned char*>(a.C) + (size_t)row0 * a.ldc * elem;
-                if (a.positions != nullptr) a.positions += row0;
-                if (a.slots != nullptr) a.slots += row0;
-                a.M = nrows;
-            }
-        } else if (kind == OP_ATTENTION) {
-            nrows = min(rows_per_cluster, ps.op.attn.n - row0);
-        }
-        __syncthreads();
-        if (i + 1 < n_ops && ops[i + 1].kind == OP_ATTENTION) {
-            const int nr = min(rows_per_cluster, ops[i + 1].attn.n - row0);
-            if (nr > 0) attention_prefetch(ops[i + 1].attn, b, nb, row0, nr);
-        }
         mark(i, 1);
         sync.waited = (i == 0);
-        if (kind == OP_GEMM && nrows > 0) {
-            const bool pair = ps.op.pair != 0;
-            for (int vb = b; vb < ps.op.vblocks; vb += nb) {
-                __syncthreads();
-                if (pair) program_gemm<NT, true>(ps.op.gemm, vb, xs, srow, sync);
-                else program_gemm<NT, false>(ps.op.gemm, vb, xs, srow, sync);
-            }
-        } else if (kind == OP_ATTENTION && nrows > 0) {
+        const int kind = ps.op.kind;
+        if (kind == OP_GEMM) {
+            rows_product<R>(ps.op.gemm, xs_dyn, red, row0, nrows, (int)rank * ROWS_WARPS + warp, (int)csize * ROWS_WARPS, sync);
+        } else if (kind == OP_ATTENTION) {
             if constexpr (HD > 0) {
                 const int splits = ps.op.attn.splits, nkv = ps.op.attn.nkv;
                 const int items = nrows * splits * nkv;
-                for (int vb = b; vb < items; vb += nb) {
-                    __syncthreads();
+                for (int vb = (int)rank * ROWS_GROUPS + sync.group; vb < items; vb += (int)csize * ROWS_GROUPS) {
+                    sync.group_barrier();
                     const int split = vb % splits, rest = vb / splits;
-                    program_attention<HD, BK>(ps.op.attn, split, rest % nkv, row0 + rest / nkv, attn_sm, sync);
+                    rows_attention<HD, BK>(ps.op.attn, split, rest % nkv, row0 + rest / nkv, attn_sm[sync.group], sync);
                 }
             }
         }
+        sync.wait();   // (threads that had no share still have to pass the barrier before this operation)
         __syncthreads();
-        sync.wait();
         mark(i, 2);
         if (i + 1 < n_ops) sync.arrive();
         mark(i, 3);
@@ -429,17 +623,28 @@ static int launch_grid(const ProgramOp* ops, int n_ops, int max_vblocks, unsigne
     return gb_check_launch("gb_program_launch");
 }
 
-// Clusters of 16 blocks where the chip can hold as many of them as there are row groups, else of 8.
-template <int NT, int HD, int BK>
-static int launch_clusters(const ProgramOp* ops, int n_ops, int rows, long long* trace, cudaStream_t stream) {
-    auto kernel = decode_program_cluster_kernel<NT, HD, BK>;
-    static int active16 = -1, active8 = -1;   // clusters of each size that can run at once
+// Clusters of 16 blocks where the chip can hold as many of them as there are row groups, else of 8. Returns -1 when the
+// rows do not fit the clusters that can run at once (the caller then shares the work by operations).
+template <int R, int HD, int BK>
+static int launch_rows(const ProgramOp* ops, int n_ops, int rows, int max_k, long long* trace, cudaStream_t stream) {
+    auto kernel = decode_program_rows_kernel<R, HD, BK>;
+    const size_t smem = ROWS_GROUPS * sizeof(DecodeAttnSmem) + (size_t)R * max_k * sizeof(float);
+    static int active16 = -1, active8 = -1;   // clusters of each size that can run at once (with the smallest buffer)
+    static size_t smem_allowed = 0;
+    if (smem > smem_allowed) {
+        GB_REQUIRE(smem <= 200 * 1024, "gb_program_launch: K = %d is too long for a program's activation buffer", max_k);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        GB_REQUIRE(e == cudaSuccess, "gb_program_launch: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        smem_allowed = smem;
+        active16 = -1;
+    }
     if (active16 < 0) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         for (int size : {16, 8}) {
             cudaLaunchConfig_t probe = {};
             probe.gridDim = dim3(size * 32);
-            probe.blockDim = dim3(128);
+            probe.blockDim = dim3(ROWS_THREADS);
+            probe.dynamicSmemBytes = smem_allowed;
             cudaLaunchAttribute pa[1];
             pa[0].id = cudaLaunchAttributeClusterDimension;
             pa[0].val.clusterDim.x = size; pa[0].val.clusterDim.y = 1; pa[0].val.clusterDim.z = 1;
@@ -451,27 +656,22 @@ static int launch_clusters(const ProgramOp* ops, int n_ops, int rows, long long*
         }
         cudaGetLastError();
     }
-    GB_REQUIRE(active8 > 0 || active16 > 0, "gb_program_launch: the device runs no thread-block clusters of this kernel");
-    const int per_row = NT == 1 ? 8 : 16;   // rows one cluster can take
-    int size = 16, groups = rows;           // one row per cluster if they all run at once
-    auto fits = [&](int sz, int act) { return act > 0 && (rows + act - 1) / act <= per_row; };
-    if (active16 >= rows) { size = 16; }
-    else if (active8 >= rows) { size = 8; }
-    else if (fits(16, active16)) { size = 16; groups = active16; }
-    else { size = active8 > 0 ? 8 : 16; groups = active8 > 0 ? active8 : active16; }
-    const int rows_per_cluster = (rows + groups - 1) / groups;
-    GB_REQUIRE(rows_per_cluster <= per_row, "gb_program_launch: %d rows per cluster are too many", rows_per_cluster);
-    const int clusters = (rows + rows_per_cluster - 1) / rows_per_cluster;
+    const int clusters = (rows + R - 1) / R;
+    int size = 0;
+    if (active16 >= clusters) size = 16;
+    else if (active8 >= clusters) size = 8;
+    if (size == 0) return -1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(clusters * size);
-    cfg.blockDim = dim3(128);
+    cfg.blockDim = dim3(ROWS_THREADS);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = size; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ops, n_ops, rows_per_cluster, trace);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ops, n_ops, rows, trace);
     if (e != cudaSuccess) {
         gb_set_error("gb_program_launch: cluster launch failed: %s", cudaGetErrorString(e));
         return 2;
@@ -481,18 +681,27 @@ static int launch_clusters(const ProgramOp* ops, int n_ops, int rows, long long*
 
 enum { PROGRAM_BY_ROWS = 0, PROGRAM_BY_OPERATIONS = 1 };
 
-static int program_dispatch(const void* ops, int n_ops, int rows, int hd, int block_keys, int max_vblocks, void* barrier,
-                            int* status, int how, int absent, long long wait_cycles, long long* trace, cudaStream_t stream) {
-    GB_REQUIRE(ops && n_ops >= 0 && barrier && status && max_vblocks >= 1, "gb_program_launch: bad arguments");
+static int program_dispatch(const void* ops, int n_ops, int rows, int hd, int block_keys, int max_vblocks, int max_k,
+                            void* barrier, int* status, int how, int absent, long long wait_cycles, long long* trace,
+                            cudaStream_t stream) {
+    GB_REQUIRE(ops && n_ops >= 0 && barrier && status && max_vblocks >= 1 && max_k >= 8, "gb_program_launch: bad arguments");
     GB_REQUIRE(rows >= 1 && rows <= 16, "gb_program_launch: %d rows are outside a program's range (1..16)", rows);
     GB_REQUIRE(how == PROGRAM_BY_ROWS || how == PROGRAM_BY_OPERATIONS, "gb_program_launch: unknown way %d of sharing the work", how);
     if (n_ops == 0) return 0;
     const ProgramOp* o = static_cast<const ProgramOp*>(ops);
     unsigned* bar = static_cast<unsigned*>(barrier);
-#define GB_PROG(NTT, HH, BB)                                                                  \
-    return how == PROGRAM_BY_ROWS                                                             \
-               ? launch_clusters<1, HH, BB>(o, n_ops, rows, trace, stream)                    \
-               : launch_grid<NTT, HH, BB>(o, n_ops, max_vblocks, bar, status, absent, wait_cycles, trace, stream);
+    // By rows: one row per cluster where that many clusters run at once, else two; if even that does not fit, by
+    // operations. (A head size of 128 takes the 16-key variant either way.)
+#define GB_PROG(NTT, HH, BB)                                                                                          \
+    {                                                                                                                 \
+        if (how == PROGRAM_BY_ROWS) {                                                                                 \
+            constexpr int RB = HH == 64 ? 16 : BB;   /* blocks of 512 threads have 128 registers a thread */           \
+            int rc = launch_rows<1, HH, RB>(o, n_ops, rows, max_k, trace, stream);                                    \
+            if (rc == -1) rc = launch_rows<2, HH, RB>(o, n_ops, rows, max_k, trace, stream);                          \
+            if (rc != -1) return rc;                                                                                  \
+        }                                                                                                             \
+        return launch_grid<NTT, HH, BB>(o, n_ops, max_vblocks, bar, status, absent, wait_cycles, trace, stream);      \
+    }
 #define GB_PROG_HD(NTT)                                   \
     if (hd == 0) { GB_PROG(NTT, 0, 32) }                  \
     if (hd == 16) { GB_PROG(NTT, 16, 32) }                \
@@ -509,11 +718,12 @@ static int program_dispatch(const void* ops, int n_ops, int rows, int hd, int bl
 
 // Run a program: `ops` on the device (n_ops operations written by the encode functions and copied there), every
 // product with at most `rows` rows, every attention with head size `hd` (0: none) and `block_keys` keys per warp
-// iteration; `max_vblocks` the most virtual blocks any operation has; `barrier` one unsigned word on the device.
+// iteration; `max_vblocks` the most virtual blocks any operation has, `max_k` the longest K of its products;
+// `barrier` one unsigned word on the device.
 // how: 0 = by rows (a thread-block cluster per group of rows), 1 = by operations (all blocks share each operation).
-GB_EXPORT int gb_program_launch(const void* ops, int n_ops, int rows, int hd, int block_keys, int max_vblocks, void* barrier,
-                                int* status, int how, cudaStream_t stream) {
-    return program_dispatch(ops, n_ops, rows, hd, block_keys, max_vblocks, barrier, status, how, 0, PROGRAM_WAIT_CYCLES, nullptr, stream);
+GB_EXPORT int gb_program_launch(const void* ops, int n_ops, int rows, int hd, int block_keys, int max_vblocks, int max_k,
+                                void* barrier, int* status, int how, cudaStream_t stream) {
+    return program_dispatch(ops, n_ops, rows, hd, block_keys, max_vblocks, max_k, barrier, status, how, 0, PROGRAM_WAIT_CYCLES, nullptr, stream);
 }
 
 // For a test of the bounded wait: the by-operations kernel, but every barrier expects `absent` blocks more than the
@@ -521,10 +731,10 @@ GB_EXPORT int gb_program_launch(const void* ops, int n_ops, int rows, int hd, in
 // runs out, the blocks record GB_STATUS_WAIT_TIMEOUT and return, and the operations behind that barrier do not
 // change anything.
 GB_EXPORT int gb_program_launch_with_absent_blocks(const void* ops, int n_ops, int rows, int hd, int block_keys, int max_vblocks,
-                                                   void* barrier, int* status, int absent, long long wait_cycles,
+                                                   int max_k, void* barrier, int* status, int absent, long long wait_cycles,
                                                    cudaStream_t stream) {
     GB_REQUIRE(absent >= 0 && wait_cycles > 0 && wait_cycles <= PROGRAM_WAIT_CYCLES, "gb_program_launch_with_absent_blocks: bad arguments");
-    return program_dispatch(ops, n_ops, rows, hd, block_keys, max_vblocks, barrier, status, PROGRAM_BY_OPERATIONS, absent,
+    return program_dispatch(ops, n_ops, rows, hd, block_keys, max_vblocks, max_k, barrier, status, PROGRAM_BY_OPERATIONS, absent,
                             wait_cycles, nullptr, stream);
 }
 
@@ -532,9 +742,9 @@ GB_EXPORT int gb_program_launch_with_absent_blocks(const void* ops, int n_ops, i
 // values into `trace` (int64 [2, n_ops, 4] on the device): for each operation, when the block started it, had issued
 // its hints, had done its share and waited for the others' share of the operation before, and had arrived at the
 // barrier behind it. For measurements: where a step's time goes.
-GB_EXPORT int gb_program_launch_traced(const void* ops, int n_ops, int rows, int hd, int block_keys, int max_vblocks, void* barrier,
-                                       int* status, int how, void* trace, cudaStream_t stream) {
+GB_EXPORT int gb_program_launch_traced(const void* ops, int n_ops, int rows, int hd, int block_keys, int max_vblocks, int max_k,
+                                       void* barrier, int* status, int how, void* trace, cudaStream_t stream) {
     GB_REQUIRE(trace != nullptr, "gb_program_launch_traced: no trace buffer");
-    return program_dispatch(ops, n_ops, rows, hd, block_keys, max_vblocks, barrier, status, how, 0, PROGRAM_WAIT_CYCLES,
+    return program_dispatch(ops, n_ops, rows, hd, block_keys, max_vblocks, max_k, barrier, status, how, 0, PROGRAM_WAIT_CYCLES,
                             static_cast<long long*>(trace), stream);
 }

@@ -575,9 +575,10 @@ GBH_EXPORT int gbh_plan_step(void* h, int n_running, const int64_t* rids, const 
 
 // ------------------------------------------------------------------------------ a step's metadata
 // Fills the int32 block that a step copies to the device. Its sections start at the offsets given:
-//   off[0..8]: tokens [n], positions [n], row_seq [n], want [n_want], seq_first_row [S+1], seq_start_pos [S],
-//   seq_slots [S], temperature [n_want], uniform [n_want] (float bits); then per group g: off[9+2g] slots [n],
-//   off[10+2g] tables [S, max_pages].
+//   off[0..7]: tokens [n], positions [n], row_seq [n], want [n_want], seq_first_row [S+1], seq_start_pos [S],
+//   seq_slots [S], want_slots [n_want]; then per group g: off[8+2g] slots [n], off[9+2g] tables [S, max_pages].
+// want_slots names, for each wanted row that is to be sampled from its request's own sampling state (sample_mask,
+// one byte per wanted row of the entries, or null: none), the request's state slot, and -1 for every other wanted row.
 // The E entries bring tok_count[e] tokens each (flat in tokens) and ask for want_count[e] of their rows
 // (indices within the entry, flat in want). The step has a fixed shape of S >= E sequences and n rows:
 // pad_after padding sequences follow the first `lead` entries (so that a batch whose leading single-token
@@ -591,8 +592,7 @@ GBH_EXPORT int gbh_plan_step(void* h, int n_running, const int64_t* rids, const 
 GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok_count, const int32_t* tokens,
                              const int* want_count, const int* want, int lead, int pad_after, int n, int S, int n_want,
                              int max_pages, const long long* off, long long size, int32_t* host,
-                             const float* temperature, const float* uniform, int n_sampling, int* seq_info,
-                             int* max_ctx) {
+                             const unsigned char* sample_mask, int n_mask, int* seq_info, int* max_ctx) {
     Cache* c = static_cast<Cache*>(h);
     const int G = (int)c->groups.size();
     if (S < E + pad_after || lead < 0 || lead > E || pad_after < 0) return fail(BAD_VALUE, "fewer sequences than entries");
@@ -610,10 +610,12 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
     int32_t* h_first = host + off[4];
     int32_t* h_start = host + off[5];
     int32_t* h_slots = host + off[6];
+    int32_t* h_want_slots = host + off[7];
     std::fill(h_pos, h_pos + n, -1);
+    std::fill(h_want_slots, h_want_slots + n_want, -1);
     for (int g = 0; g < G; ++g) {
-        std::fill(host + off[9 + 2 * g], host + off[9 + 2 * g] + n, -1);
-        std::fill(host + off[10 + 2 * g], host + off[10 + 2 * g] + (long long)S * max_pages, -1);
+        std::fill(host + off[8 + 2 * g], host + off[8 + 2 * g] + n, -1);
+        std::fill(host + off[9 + 2 * g], host + off[9 + 2 * g] + (long long)S * max_pages, -1);
     }
     std::vector<int> pad_rows;
     int row = 0, wi = 0, longest = 0, tcur = 0, wcur = 0, seq = 0;
@@ -639,7 +641,10 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
             h_pos[row + i] = start + i;
             h_row_seq[row + i] = seq;
         }
-        for (int i = 0; i < want_count[e]; ++i) h_want[wi++] = row + want[wcur + i];
+        for (int i = 0; i < want_count[e]; ++i) {
+            if (sample_mask && wi < n_mask && sample_mask[wi]) h_want_slots[wi] = req->slot;
+            h_want[wi++] = row + want[wcur + i];
+        }
         h_first[seq] = row;
         h_start[seq] = start;
         h_slots[seq] = req->slot;
@@ -649,8 +654,8 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
             if ((int)table.size() > max_pages) return fail(BAD_VALUE, "a block table is wider than the step's tables");
             if ((start + k + gr.page_size - 1) / gr.page_size > (int)table.size())
                 return fail(BAD_VALUE, "a request brings tokens for which no page was reserved");
-            std::memcpy(host + off[10 + 2 * g] + (long long)seq * max_pages, table.data(), sizeof(int) * table.size());
-            int32_t* sl = host + off[9 + 2 * g] + row;
+            std::memcpy(host + off[9 + 2 * g] + (long long)seq * max_pages, table.data(), sizeof(int) * table.size());
+            int32_t* sl = host + off[8 + 2 * g] + row;
             for (int i = 0; i < k; ++i) {
                 const int pos = start + i;
                 sl[i] = table[pos / gr.page_size] * gr.page_size + pos % gr.page_size;
@@ -668,10 +673,6 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
     h_first[S] = row;
     for (int r = row; r < n; ++r) h_row_seq[r] = S - 1;   // rows behind the last sequence: skipped by their position
     for (size_t p = 0; wi < n_want; ++p) h_want[wi++] = p < pad_rows.size() ? pad_rows[p] : 0;
-    if (temperature && uniform && n_sampling > 0) {
-        std::memcpy(host + off[7], temperature, sizeof(float) * std::min(n_sampling, n_want));
-        std::memcpy(host + off[8], uniform, sizeof(float) * std::min(n_sampling, n_want));
-    }
     *max_ctx = longest;
     return OK;
 }

@@ -53,7 +53,11 @@ class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", *, cache_tokens: Optional[int] = None,
                  num_pages: Optional[int] = None, page_size: int = 16, max_batch_tokens: int = 2048,
                  max_requests: int = 64, share_prefixes: bool = False, device: str = "cuda:0",
-                 config: Optional[ModelConfig] = None, use_graphs: bool = True, use_programs: bool = False):
+                 config: Optional[ModelConfig] = None, use_graphs: bool = True, use_programs: bool = False,
+                 group_pages=None):
+        """``cache_tokens`` / ``num_pages`` size the page pool of every cache group alike; ``group_pages`` (a function
+        from a group's ``PagedKvSpec`` to a number of pages) sizes each group on its own, for models whose groups need
+        different amounts: a group that keeps a window of keys needs far fewer pages than one that keeps them all."""
         if not torch.cuda.is_available():
             raise RuntimeError("glassbox_b200 needs a CUDA device: every kernel is CUDA and there is no CPU path")
         self.device = torch.device(device)
@@ -74,10 +78,10 @@ class Engine:
         self.max_batch_tokens = int(max_batch_tokens)
         self.max_requests = int(max_requests)
         layer_specs = self.model.cache_layer_specs()
-        self.device_cache = DeviceCache(layer_specs, lambda spec: self.num_pages, self.page_size, self.max_requests,
-                                        self.dtype, self.device)
-        groups = [GroupSpec(num_pages=self.num_pages, page_size=self.page_size, window=s.window, name=f"group{i}")
-                  for i, s in enumerate(self.device_cache.group_specs)]
+        pages_for = group_pages if group_pages is not None else (lambda spec: self.num_pages)
+        self.device_cache = DeviceCache(layer_specs, pages_for, self.page_size, self.max_requests, self.dtype, self.device)
+        groups = [GroupSpec(num_pages=self.device_cache.group_pages[i], page_size=self.page_size, window=s.window,
+                            name=f"group{i}") for i, s in enumerate(self.device_cache.group_specs)]
         self.cache = CacheManager(groups, max_requests=self.max_requests, share_prefixes=share_prefixes,
                                   has_state=self.device_cache.has_state)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -111,8 +115,11 @@ class Engine:
 
     # ---------------------------------------------------------------------------- requests
     def add_request(self, request, prompt: Sequence[int] = ()) -> int:
-        """Admit a request; returns how many leading prompt tokens are already cached."""
-        return self.cache.add_request(request, prompt)
+        """Admit a request; returns how many leading prompt tokens are already cached. Its state slot starts from zero
+        (mixers' states; greedy sampling until ``set_sampling`` says otherwise)."""
+        reused = self.cache.add_request(request, prompt)
+        self.device_cache.zero_slots(self.cache.drain_fresh_slots())
+        return reused
 
     def free_request(self, request) -> None:
         self.cache.free_request(request)
@@ -172,8 +179,7 @@ class Engine:
             self._layouts.clear()
         off, cur = {}, 0
         for name, size in (("tokens", n), ("positions", n), ("row_seq", n), ("want", n_want),
-                           ("seq_first_row", S + 1), ("seq_start_pos", S), ("seq_slots", S),
-                           ("temperature", n_want), ("uniform", n_want)):
+                           ("seq_first_row", S + 1), ("seq_start_pos", S), ("seq_slots", S), ("want_slots", n_want)):
             off[name] = cur
             cur += size
         for g in range(len(self.cache.groups)):
@@ -182,8 +188,8 @@ class Engine:
             off[f"tables{g}"] = cur
             cur += S * max_pages
         off["_size"] = cur
-        names = ["tokens", "positions", "row_seq", "want", "seq_first_row", "seq_start_pos", "seq_slots", "temperature",
-                 "uniform"] + [f"{kind}{g}" for g in range(len(self.cache.groups)) for kind in ("slots", "tables")]
+        names = ["tokens", "positions", "row_seq", "want", "seq_first_row", "seq_start_pos", "seq_slots", "want_slots"] + \
+            [f"{kind}{g}" for g in range(len(self.cache.groups)) for kind in ("slots", "tables")]
         off["_array"] = np.array([off[k] for k in names], dtype=np.int64)   # the order the host library reads
         self._layouts[key] = off
         return off
@@ -202,12 +208,13 @@ class Engine:
         want = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(want_count.sum()))
         self._tok_count, self._tokens = tok_count, tokens      # kept for the commit that follows the step
         host = self._stage_buffer(off["_size"])
-        temps = unif = None
+        mask = None
         if sampling is not None:
-            temps = np.ascontiguousarray(sampling[0], dtype=np.float32)
-            unif = np.ascontiguousarray(sampling[1], dtype=np.float32)
+            mask = np.ascontiguousarray(sampling, dtype=np.uint8)
+            if mask.size != int(want_count.sum()):
+                raise ValueError(f"sampling names {mask.size} rows, the step wants {int(want_count.sum())}")
         info, self._max_ctx = self.cache.fill_step([e.request for e in entries], tok_count, tokens, want_count, want,
-                                                   n, S, n_want, max_pages, off["_array"], host, temps, unif, lead, pad_after)
+                                                   n, S, n_want, max_pages, off["_array"], host, mask, lead, pad_after)
         self._seqs = [SeqInfo(request=e.request, slot=int(info[i, 1]), start_pos=int(info[i, 0]), n_rows=int(tok_count[i]),
                               first_row=int(info[i, 2])) for i, e in enumerate(entries)]
         return host
@@ -222,8 +229,7 @@ class Engine:
         ctx.seq_first_row = dev[off["seq_first_row"]:off["seq_first_row"] + S + 1]
         ctx.seq_start_pos = dev[off["seq_start_pos"]:off["seq_start_pos"] + S]
         ctx.seq_slots = dev[off["seq_slots"]:off["seq_slots"] + S]
-        ctx.temperature = dev[off["temperature"]:off["temperature"] + n_want].view(torch.float32)
-        ctx.uniform = dev[off["uniform"]:off["uniform"] + n_want].view(torch.float32)
+        ctx.want_slots = dev[off["want_slots"]:off["want_slots"] + n_want]
         ctx.group_slots = [dev[off[f"slots{g}"]:off[f"slots{g}"] + n] for g in range(n_groups)]
         ctx.group_tables = [dev[off[f"tables{g}"]:off[f"tables{g}"] + S * max_pages].view(S, max_pages)
                             for g in range(n_groups)]
@@ -259,9 +265,11 @@ class Engine:
         order of the entries and of each entry's ``want``; the tensor is scratch that the next
         step overwrites. With ``reserve`` True room is reserved for every entry first, all or nothing:
         on ``OutOfPages`` no request holds more pages than before. With ``reserve`` False the caller has
-        already reserved room for every entry (the scheduler does, to decide about preemption first). With ``sampling`` =
-        (temperatures, uniforms), one per wanted row, the sampling kernel runs in the same step
-        and ``self.sampled`` holds the chosen token of each wanted row (int32, on the device).
+        already reserved room for every entry (the scheduler does, to decide about preemption first). With ``sampling`` (one
+        flag per wanted row) the sampling kernel runs in the same step and ``self.sampled`` holds the chosen token of
+        each wanted row (int32, on the device): rows whose flag is set are drawn from their request's own sampling
+        state (``set_sampling``: temperature and random generator, kept in the request's state slot on the device and
+        advanced there), the others are the row's greedy choice.
 
         A step made only of single decoded tokens runs as a CUDA graph of fixed shape (batch and
         table sizes rounded up to powers of two, padding rows skipped by every kernel); any other
@@ -287,7 +295,7 @@ class Engine:
             if n_groups else 1
         n_want = sum(len(e.want) for e in entries)
         decode_only = self.use_graphs and n == S and n_want == S and S <= self.max_graph_batch \
-            and not self.device_cache.has_state
+            and self.model.recordable(True)
         if decode_only:
             logits = self._step_graph(entries, S, max_pages, sampling)
         else:
@@ -297,7 +305,7 @@ class Engine:
             while lead < S and len(entries[lead].tokens) == 1:
                 lead += 1
             small_logits = (n_want + 8) * self.config.vocab_size * 4 <= (64 << 20)   # each graph owns its logits buffer
-            if self.use_graphs and not self.device_cache.has_state and small_logits:
+            if self.use_graphs and small_logits and self.model.recordable(n == S):
                 # A step is replayed as a CUDA graph of a rounded shape, so that batches which differ a little share
                 # one: the single-token requests at its head counted in eights (padding sequences behind them), the
                 # other requests in powers of two, the rows in 64s, the wanted rows in eights, the table width in
@@ -348,7 +356,7 @@ class Engine:
                 logits = self.model.forward(ctx)
                 if sampling is not None and n_want:
                     self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
-                    kernels.sample(logits, self.sampled, ctx.temperature, ctx.uniform)
+                    kernels.sample(logits, self.sampled, want_slots=ctx.want_slots, state=self.device_cache.sampling)
         if commit:
             self.cache.commit_many([e.request for e in entries], self._tok_count, self._tokens)
         self.steps += 1
@@ -371,7 +379,7 @@ class Engine:
         two up to ``max_batch``) at every table width (powers of two up to ``max_context`` tokens). Recording
         a graph takes tens of milliseconds; without this it happens inside the first step of each new shape,
         also when a batch shrinks because requests end. Returns the number of graphs recorded."""
-        if not self.use_graphs or self.device_cache.has_state:
+        if not self.use_graphs or not self.model.recordable(True):
             return 0
         before = len(self._graphs)
         max_pages = -(-min(int(max_context), self.config.max_position) // self.page_size)
@@ -395,8 +403,6 @@ class Engine:
         Sb = 1 << max(S - 1, 0).bit_length()
         Pb = max(8, 1 << max(max_pages - 1, 0).bit_length())
         off = self._layout(Sb, Sb, Sb, Pb)
-        if sampling is None:
-            sampling = ([0.0] * S, [0.0] * S)
         g = self._decode_graph(Sb, Pb)          # (may fill a blank batch of its own: before this step's metadata)
         host = self._fill(entries, off, Sb, Sb, Sb, Pb, sampling)
         self._stage_copy(host, g["meta"])
@@ -420,14 +426,16 @@ class Engine:
         if self.use_programs:
             ctx.program = kernels.Program()
         ctx.seqs = [SeqInfo(request=None, slot=0, start_pos=0, n_rows=1, first_row=i) for i in range(S)]
-        ctx.max_context, ctx.max_rows_per_seq, ctx.decode_only = self.config.max_position, max_rows, decode_only
+        # (the longest context a step of this shape can hold: what its block tables cover)
+        ctx.max_context = min(self.config.max_position, Pb * self.page_size)
+        ctx.max_rows_per_seq, ctx.decode_only = max_rows, decode_only
         ctx.leading_single = lead
         meta.copy_(torch.from_numpy(host))
         sampled = torch.zeros(max(n_want, 1), dtype=torch.int32, device=self.device)
 
         def run():
             logits = self.model.forward(ctx)
-            kernels.sample(logits, sampled[:n_want], ctx.temperature, ctx.uniform)
+            kernels.sample(logits, sampled[:n_want], want_slots=ctx.want_slots, state=self.device_cache.sampling)
             return logits
 
         side = torch.cuda.Stream()
@@ -459,28 +467,28 @@ class Engine:
     def max_position(self) -> int:
         return self.config.max_position
 
-    def sampling_inputs(self, n_want: int, rows: Sequence[int], samplers):
-        """(temperatures, uniforms) per wanted row for the device kernel; rows whose sampler needs
-        the host path, and rows that are not sampled, get temperature 0 (their argmax is unused)."""
-        temps = np.zeros(n_want, dtype=np.float32)
-        unif = np.zeros(n_want, dtype=np.float32)
-        for r, s in zip(rows, samplers):
-            if not s.config.needs_host and not s.config.greedy:
-                temps[r] = s.config.temperature
-                unif[r] = s.uniform()
-        return temps, unif
+    def set_sampling(self, request, temperature: float, rng_state: int) -> None:
+        """Put a request's sampling state into its state slot on the device: the temperature (0: greedy) and the state
+        of its xorshift64* generator. From then on ``step(..., sampling=...)`` draws the request's tokens on the device
+        and advances the generator there; a fork copies the state with the slot."""
+        self.device_cache.set_sampling(self.cache.slot_of(request), temperature, rng_state)
+
+    def rng_state(self, request) -> int:
+        """The state of the request's random generator as the device has advanced it (synchronises)."""
+        return self.device_cache.get_rng_state(self.cache.slot_of(request))
+
+    def rng_state_of_slot(self, slot: int) -> int:
+        """... by slot number: what the slot's last holder left (a slot keeps its contents until it is given out again)."""
+        return self.device_cache.get_rng_state(slot)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers, contexts) -> List[int]:
-        """Next token for ``logits[rows[i]]`` under ``samplers[i]``. Greedy and plain temperature
-        sampling run in the device kernel (the random number comes from the request's own
-        generator); requests with further filters are sampled on the host from a copy of the row.
-        If the step already ran the kernel (``step(..., sampling=...)``), its result is read."""
+        """Next token for ``logits[rows[i]]`` under ``samplers[i]``. Greedy and plain temperature sampling were done
+        by the device kernel inside the step (``step(..., sampling=...)``, from the request's own state slot) and are
+        only read here; requests with further filters are sampled on the host from a copy of their row."""
         w = logits.shape[0]
         if self.sampled is None or self.sampled.shape[0] != w:
-            temps, unif = self.sampling_inputs(w, rows, samplers)
-            params = torch.from_numpy(np.stack([temps, unif])).to(self.device, non_blocking=True)
             self.sampled = self.scratch.get("sampled", (w, 1), torch.int32, grow=True).view(-1)
-            kernels.sample(logits, self.sampled, params[0], params[1])
+            kernels.sample(logits, self.sampled)
         if self._sampled_host is None or self._sampled_host.numel() < w:
             self._sampled_host = torch.empty(max(w, 64), dtype=torch.int32).pin_memory()
         self._sampled_host[:w].copy_(self.sampled, non_blocking=True)

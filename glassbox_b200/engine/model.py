@@ -1,5 +1,6 @@
 """The one model class: an embedding, layers built from parts, an execution order, a final norm
-and a head. Which architecture it is shows only in its ``ModelConfig``.
+and a head, every one of them a registered part named by the configuration. Which architecture it is
+shows only in its ``ModelConfig``.
 
 Forward order follows crates/glassbox-core/src/model.rs:207-362: embed every row, run the layers
 (here: the entries of ``config.schedule``), then final norm and head on the wanted rows only.
@@ -12,7 +13,7 @@ import torch
 
 from .. import kernels
 from ..config.specs import ModelConfig
-from ..parts import Embedding, LmHead, build_block, build_part
+from ..parts import build_block, build_part
 from ..parts.base import Mixer, Part
 from ..weights.binding import ParamSpec
 
@@ -36,10 +37,10 @@ class DecoderModel:
         config.validate()
         self.config = config
         d = config.hidden_size
-        self.embed = Embedding(config.vocab_size, d)
+        self.embed = build_part("embedding", config.embedding, vocab_size=config.vocab_size, hidden_size=d)
         self.layers = [build_block(spec, hidden_size=d) for spec in config.layers]
         self.final_norm = build_part("norm", config.final_norm, hidden_size=d)
-        self.head = LmHead(config.vocab_size, d)
+        self.head = build_part("head", config.head, vocab_size=config.vocab_size, hidden_size=d)
         self._owners: Dict[str, tuple] = {}
         self._specs: Dict[str, ParamSpec] = {}
         _collect("embed", self.embed, self._specs, self._owners)
@@ -49,11 +50,18 @@ class DecoderModel:
         _collect("head", self.head, self._specs, self._owners)
         #: whether a decode step of this model may be recorded as a program for the persistent kernel: only when
         #: no part enqueues device work behind the kernel library's back
-        self.program_safe = all(p.launches_through_kernels_only
-                                for top in (self.embed, *self.layers, self.final_norm, self.head) for p in _all_parts(top))
+        self.program_safe = all(p.launches_through_kernels_only for p in self.parts())
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return dict(self._specs)
+
+    def parts(self):
+        for top in (self.embed, *self.layers, self.final_norm, self.head):
+            yield from _all_parts(top)
+
+    def recordable(self, decode_only: bool) -> bool:
+        """Whether every part lets a step of this kind be replayed as a CUDA graph (see ``Part.recordable``)."""
+        return all(p.recordable(decode_only) for p in self.parts())
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         grouped: Dict[int, tuple] = {}

@@ -20,9 +20,15 @@ Policy, after crates/glassbox-server/src/scheduler.rs:239-415:
    ``max_tokens`` or ``max_position`` end it with "length" (scheduler.rs:370-404).
 6. *Finish*: pages and the state slot go back to the pool (scheduler.rs:405-410, 210-226).
 
+Sampling state (temperature, random generator) of a request that the device kernel can sample (greedy or plain
+temperature) lives in the request's state slot on the device: it is written at admission, advanced by the kernel, copied
+by a fork, read back when the request is preempted and written again when it returns. Requests with further filters
+(top-k, top-p, min-p, repetition penalty) are sampled on the host with their ``Sampler``.
+
 The scheduler talks to a *backend* (the ``Engine``, or a stand-in in tests) through:
-``cache`` (a ``CacheManager``), ``add_request``, ``free_request``, ``reserve``,
-``step(entries, reserve=False)``, ``sample(logits, samplers, contexts)`` and ``max_position``.
+``cache`` (a ``CacheManager``), ``add_request``, ``free_request``, ``reserve``, ``fork``,
+``step(entries, reserve=False, sampling=flags)``, ``sample(logits, rows, samplers, contexts)``, ``set_sampling``,
+``rng_state`` and ``max_position``.
 """
 from __future__ import annotations
 
@@ -74,6 +80,9 @@ class _Seq:
         self.prompt_len = len(self.tokens)
         self.computed = 0
         self.sampler = Sampler(req.sampler)
+        #: state of the request's random generator while it holds no state slot (before admission, after a preemption)
+        self.rng_state = self.sampler.rng.state
+        self.slot: Optional[int] = None
         self.arrival = now
         self.first_token: Optional[float] = None
         self.last_token: Optional[float] = None
@@ -158,11 +167,16 @@ class Scheduler:
         child = _Seq(cid, req, time.perf_counter())
         if sampler is None:
             child.sampler = copy.deepcopy(src.sampler)
+            child.rng_state = src.rng_state
         self.metrics.prompt_tokens += len(req.prompt)
         if parent is None or len(self.running) >= self.config.max_seqs or not self.backend.cache.free_slots:
             self.waiting.insert(self.waiting.index(waiting) + 1, child) if waiting is not None else self.waiting.append(child)
             return cid
-        self.backend.fork(parent.id, cid)
+        self.backend.fork(parent.id, cid)               # the slot's contents (sampling state included) are copied
+        if sampler is not None:
+            self._place_sampling(child)
+        else:
+            child.slot = self.backend.cache.slot_of(cid)
         child.computed = parent.computed
         child.admitted_before = True
         self.running.append(child)
@@ -180,17 +194,37 @@ class Scheduler:
         if s.req.on_done:
             s.req.on_done(s.id, reason)
 
+    def _on_device(self, s: _Seq) -> bool:
+        return not s.req.sampler.needs_host
+
+    def _place_sampling(self, s: _Seq) -> None:
+        """A request that has just been given a state slot: its sampling state goes there."""
+        s.slot = self.backend.cache.slot_of(s.id)
+        if self._on_device(s) and hasattr(self.backend, "set_sampling"):
+            self.backend.set_sampling(s.id, s.req.sampler.temperature if not s.req.sampler.greedy else 0.0, s.rng_state)
+
     def _preempt_last(self) -> int:
+        """The most recently admitted request goes back to the front of the queue (the cache library has already taken
+        its pages and its slot); the state of its random generator comes back from the device with it."""
         s = self.running.pop()
+        if self._on_device(s) and s.slot is not None and hasattr(self.backend, "rng_state_of_slot"):
+            s.rng_state = self.backend.rng_state_of_slot(s.slot)    # the slot's contents outlive its holder until reused
+        s.slot = None
         self.backend.free_request(s.id)
         s.computed = 0
         self.metrics.preemptions += 1
         self.waiting.appendleft(s)
         return s.id
 
-    def _free_pages(self) -> int:
+    def _fits(self, span: int) -> bool:
+        """Whether every cache group has the pages for ``span`` more tokens of a request plus one to grow into. A
+        group that keeps a window of keys only ever holds the window and one step's rows of a request."""
         cache = self.backend.cache
-        return min(cache.free_pages(g) for g in range(len(cache.groups))) if cache.groups else 1 << 30
+        for g, group in enumerate(cache.groups):
+            held = span if group.window is None else min(span, group.window + self.config.token_budget)
+            if cache.free_pages(g) < cache.pages_needed(held, g) + 1:
+                return False
+        return True
 
     # ---------------------------------------------------------------------------------- step
     def step(self) -> bool:
@@ -203,11 +237,11 @@ class Scheduler:
         while len(self.running) < cfg.max_seqs and self.waiting:
             s = self.waiting[0]
             span = len(s.tokens) if s.admitted_before else min(len(s.tokens), cfg.token_budget)
-            need = cache.pages_needed(span) + 1
-            if self.running and (self._free_pages() < need or not cache.free_slots):
+            if self.running and (not self._fits(span) or not cache.free_slots):
                 break
             self.waiting.popleft()
             reused = self.backend.add_request(s.id, s.tokens)
+            self._place_sampling(s)
             if not s.admitted_before:
                 self.metrics.prefix_hit_tokens += min(reused, s.prompt_len)
             s.admitted_before = True
@@ -252,8 +286,12 @@ class Scheduler:
             rows.append(j)
             samplers.append(s.sampler)
             contexts.append(s.tokens)
-        # The device kernel samples inside the step; its random numbers are drawn here, one per row.
-        sampling = self.backend.sampling_inputs(len(wants_for), rows, samplers) if rows else None
+        # The device kernel samples inside the step, each row from its request's own state slot.
+        sampling = None
+        if rows:
+            sampling = [0] * len(wants_for)
+            for j, smp in zip(rows, samplers):
+                sampling[j] = 0 if smp.config.needs_host else 1
         logits = self.backend.step(entries, reserve=False, sampling=sampling)
 
         batch_desc = []

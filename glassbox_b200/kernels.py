@@ -40,7 +40,7 @@ _SIGNATURES = {
     "gb_copy_pages": [_P, _P, _P, _I, _LL, _LL, _I, _P],
     "gb_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _LL, _LL, _LL, _P],
     "gb_attention_rows": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
-    "gb_sample": [_P, _LL, _P, _P, _P, _I, _I, _P],
+    "gb_sample": [_P, _LL, _P, _P, _P, _P, _I, _P, _I, _I, _P],
     "gb_attention_decode": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                             _P, _P, _P],
     "gb_attention_decode_counters": [_I, _I, _I],
@@ -67,9 +67,9 @@ _SIGNATURES = {
                                    _I, _LL, _I, _P],
     "gb_program_encode_attention": [_P, _P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                                     _P, _P, _I],
-    "gb_program_launch": [_P, _I, _I, _I, _I, _I, _P, _P, _I, _P],
-    "gb_program_launch_with_absent_blocks": [_P, _I, _I, _I, _I, _I, _P, _P, _I, _LL, _P],
-    "gb_program_launch_traced": [_P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "gb_program_launch": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P],
+    "gb_program_launch_with_absent_blocks": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _LL, _P],
+    "gb_program_launch_traced": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
 }
@@ -157,14 +157,14 @@ class Program:
         self._reset()
 
     def _reset(self):
-        self._pending, self._n, self._rows, self._hd, self._bk, self._max_vblocks = [], 0, 0, 0, 0, 1
+        self._pending, self._n, self._rows, self._hd, self._bk, self._max_vblocks, self._max_k = [], 0, 0, 0, 0, 1, 8
         self._status = None
 
     def start_step(self):
         self.cursor = 0
         self._reset()
 
-    def _add(self, name, vblocks, rows, *args):
+    def _add(self, name, vblocks, rows, k, *args):
         rc = getattr(lib(), name)(ctypes.addressof(self._buf), *args)
         if rc != 0:
             raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or f"{name} failed with code {rc}")
@@ -172,9 +172,17 @@ class Program:
         self._n += 1
         self._rows = max(self._rows, rows)
         self._max_vblocks = max(self._max_vblocks, vblocks)
+        self._max_k = max(self._max_k, k)
+
+    #: a product whose weights are larger than this is launched by itself (all SMs stream it) instead of recorded: in a
+    #: program shared by rows a cluster would have to stream it alone
+    MAX_WEIGHT_BYTES = 12 << 20
 
     def takes_rows(self, rows: int) -> bool:
         return 1 <= rows <= self.max_rows
+
+    def takes_product(self, rows: int, w: torch.Tensor) -> bool:
+        return self.takes_rows(rows) and w.numel() * w.element_size() <= self.MAX_WEIGHT_BYTES
 
     def takes_attention(self, hd: int, block_keys: int) -> bool:
         """One program runs one attention variant; a second one waits for the next program."""
@@ -187,7 +195,8 @@ class Program:
         if not self._n:
             return
         host = b"".join(self._pending)
-        n, rows, hd, bk, max_vblocks, status = self._n, self._rows, self._hd, self._bk, self._max_vblocks, self._status
+        n, rows, hd, bk, max_vblocks, max_k, status = (self._n, self._rows, self._hd, self._bk, self._max_vblocks, self._max_k,
+                                                        self._status)
         self._reset()
         k = self.cursor
         if k < len(self.segments) and self.segments[k]["host"] == host:
@@ -204,14 +213,14 @@ class Program:
         launch_count += 1
         if self.trace_next:        # (a measurement: per-operation clock values of the first and the last block)
             self.traces.append((n, torch.zeros(2 * n * 4, dtype=torch.int64, device=status.device), host))
-            rc = lib().gb_program_launch_traced(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks, seg["barrier"].data_ptr(),
+            rc = lib().gb_program_launch_traced(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks, max_k, seg["barrier"].data_ptr(),
                                                 status.data_ptr(), self.how, self.traces[-1][1].data_ptr(), _stream())
         elif self.absent_blocks:     # (a test of the barrier's bounded wait)
-            rc = lib().gb_program_launch_with_absent_blocks(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks,
+            rc = lib().gb_program_launch_with_absent_blocks(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks, max_k,
                                                             seg["barrier"].data_ptr(), status.data_ptr(), self.absent_blocks,
                                                             self.wait_cycles, _stream())
         else:
-            rc = lib().gb_program_launch(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks, seg["barrier"].data_ptr(),
+            rc = lib().gb_program_launch(seg["dev"].data_ptr(), n, rows, hd, bk, max_vblocks, max_k, seg["barrier"].data_ptr(),
                                          status.data_ptr(), self.how, _stream())
         if rc != 0:
             raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or f"gb_program_launch failed with code {rc}")
@@ -395,8 +404,8 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
         assert c.dtype in (torch.bfloat16, torch.float32)
     x, ldx, xres, ldr, gain, eps = _stream_input(a, norm)
     prog = _program_for()
-    if prog is not None and prog.takes_rows(M):
-        prog._add("gb_program_encode_gemm", -(-N // 16), M, x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(c),
+    if prog is not None and prog.takes_product(M, w):
+        prog._add("gb_program_encode_gemm", -(-N // 16), M, K, x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(c),
                   c.stride(0), mode, M, N, K)
         return
     _call("gb_gemm_stream", x, ldx, xres, ldr, gain, eps, _ptr(w), w.stride(0), _ptr(c), c.stride(0), mode, M, N, K,
@@ -432,8 +441,8 @@ def gemm_stream_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_s
         assert cos_sin.shape[1] == hd // 2
     x, ldx, xres, ldr, gain, eps = _stream_input(a, norm)
     prog = _program_for(status)
-    if prog is not None and prog.takes_rows(M):
-        prog._add("gb_program_encode_gemm_qkv", (nh + 2 * nkv) * (hd // 32), M, x, ldx, xres, ldr, gain, eps, _ptr(w),
+    if prog is not None and prog.takes_product(M, w):
+        prog._add("gb_program_encode_gemm_qkv", (nh + 2 * nkv) * (hd // 32), M, K, x, ldx, xres, ldr, gain, eps, _ptr(w),
                   w.stride(0), _ptr(q_out), q_out.stride(0), M, K, _ptr(cos_sin),
                   cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slots), _ptr(kcache), _ptr(vcache),
                   nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status))
@@ -602,7 +611,7 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
         if not prog.takes_attention(hd, block_keys):
             prog.flush()
             prog._status = status
-        prog._add("gb_program_encode_attention", splits * nkv * n, n, _ptr(q), q.stride(0), _ptr(out), out.stride(0),
+        prog._add("gb_program_encode_attention", splits * nkv * n, n, 8, _ptr(q), q.stride(0), _ptr(out), out.stride(0),
                   _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n,
                   nh, nkv, hd, page_size, kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc),
                   _ptr(part_ml), _ptr(counters), _ptr(status), int(block_keys))
@@ -673,11 +682,18 @@ def kv_prefetch(kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
-           uniform: Optional[torch.Tensor] = None) -> None:
-    """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or no temperatures are given), else a
-    draw from softmax(logits[r] / temperature[r]) using uniform[r] in [0, 1)."""
-    _cuda(logits, out, temperature, uniform)
+           uniform: Optional[torch.Tensor] = None, want_slots: Optional[torch.Tensor] = None,
+           state: Optional[torch.Tensor] = None) -> None:
+    """out[r] = argmax(logits[r]) where the row's temperature is <= 0 (or none is given), else a draw from
+    softmax(logits[r] / temperature) with a uniform number in [0, 1). Temperature and number come from
+    ``temperature[r]`` and ``uniform[r]``, or, for rows with ``want_slots[r] >= 0``, from the request's sampling
+    state ``state[want_slots[r]]`` (int32 [slots, 4]: generator state low and high word, temperature bits, unused),
+    whose xorshift64* generator the kernel advances by one draw."""
+    _cuda(logits, out, temperature, uniform, want_slots, state)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
-    _call("gb_sample", _ptr(logits), logits.stride(0), _ptr(temperature), _ptr(uniform), _ptr(out), rows, vocab,
-          _stream())
+    if want_slots is not None:
+        assert want_slots.dtype == torch.int32 and want_slots.numel() >= rows
+        assert state is not None and state.dtype == torch.int32 and state.shape[1] == 4 and state.is_contiguous()
+    _call("gb_sample", _ptr(logits), logits.stride(0), _ptr(temperature), _ptr(uniform), _ptr(want_slots), _ptr(state),
+          state.shape[0] if state is not None else 0, _ptr(out), rows, vocab, _stream())

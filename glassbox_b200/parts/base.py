@@ -6,6 +6,10 @@ the batch. No part knows which model it sits in, which layer it is, or what its 
 
 Interfaces (``ctx`` is ``glassbox_b200.engine.context.StepContext``):
 
+* Embedding: ``forward(ctx, tokens, x)``: ``tokens`` int32 [n] on the device; writes the float32 residual rows
+             ``x`` [n, d] (padding rows carry token 0 and are ignored downstream).
+* Head:      ``forward(ctx, hs, logits)``: ``hs`` [w, d] (activation dtype, already normed), writes float32
+             ``logits`` [w, vocab].
 * Norm:      ``forward(ctx, x, out, rows=None)``: ``x`` float32 [n, d] residual stream, ``out``
              [m, d] in the activation dtype; ``rows`` (int32 [m]) picks input rows.
 * Position:  ``fused_table(device)`` -> float32 [max_position, rotary_dim/2, 2] of (cos, sin) that
@@ -55,6 +59,14 @@ class Part:
     #: also enqueues work of its own (torch operations, other libraries) keeps the default and always runs
     #: kernel by kernel.
     launches_through_kernels_only = False
+
+    def recordable(self, decode_only: bool) -> bool:
+        """Whether a step through this part can be recorded once and replayed as a CUDA graph (``decode_only``: a step
+        in which every request brings exactly one row). It can when the part reads everything that changes from step
+        to step (tokens, positions, slots, block tables, state slots: the tensors of ``ctx``) on the device, and
+        nothing of it on the host (``ctx.seqs``, Python numbers taken from tensors). Parts that cannot say False
+        and their model's steps of that kind are launched kernel by kernel."""
+        return True
 
     def __init__(self, spec: Any):
         self.spec = spec
@@ -133,7 +145,17 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-ROLES = ("norm", "position", "mixer", "ffn", "arrangement")
+class TokenEmbedding(Part):
+    def forward(self, ctx, tokens, x) -> None:
+        raise NotImplementedError
+
+
+class OutputHead(Part):
+    def forward(self, ctx, hs, logits) -> None:
+        raise NotImplementedError
+
+
+ROLES = ("norm", "position", "mixer", "ffn", "arrangement", "embedding", "head")
 _REGISTRY: Dict[str, Dict[str, Callable[..., Any]]] = {r: {} for r in ROLES}
 
 

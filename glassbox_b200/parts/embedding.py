@@ -8,15 +8,15 @@ from __future__ import annotations
 
 from .. import kernels
 from ..weights.binding import ParamSpec
-from .base import Part
+from .base import OutputHead, TokenEmbedding, register_part
 from .linear import linear
 
 
-class Embedding(Part):
+class Embedding(TokenEmbedding):
     launches_through_kernels_only = True
 
-    def __init__(self, vocab_size: int, hidden_size: int):
-        super().__init__(None)
+    def __init__(self, spec=None, *, vocab_size: int, hidden_size: int):
+        super().__init__(spec)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
 
     def param_specs(self):
@@ -26,11 +26,11 @@ class Embedding(Part):
         kernels.embed(self.params["weight"], tokens, x, ctx.status)
 
 
-class LmHead(Part):
+class LmHead(OutputHead):
     launches_through_kernels_only = True
 
-    def __init__(self, vocab_size: int, hidden_size: int):
-        super().__init__(None)
+    def __init__(self, spec=None, *, vocab_size: int, hidden_size: int):
+        super().__init__(spec)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
 
     def param_specs(self):
@@ -38,3 +38,7 @@ class LmHead(Part):
 
     def forward(self, ctx, hs, logits) -> None:
         linear(ctx, hs, self.params["weight"], logits)
+
+
+register_part("embedding", "embedding", Embedding, replace=True)
+register_part("head", "lm_head", LmHead, replace=True)

@@ -34,9 +34,6 @@ class PlainBackend:
     def reserve(self, rid, n):
         self.cache.reserve(rid, n)
 
-    def sampling_inputs(self, n_want, rows, samplers):
-        return None
-
     def step(self, entries, reserve=True, sampling=None):
         rows = []
         self.step_log.append([(e.request, len(e.tokens), list(e.want)) for e in entries])

@@ -1013,9 +1013,10 @@ def _run_chain(c, M, d, nh, nkv, hd, inter, ps, st, splits):
 @pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
 @pytest.mark.parametrize("d, nh, nkv, hd, inter", [(576, 9, 3, 64, 512), (96, 3, 1, 32, 176), (256, 2, 2, 128, 320)])
 def test_decode_program_runs_the_operations_the_kernels_would(M, d, nh, nkv, hd, inter, how):
-    """The same chain of calls, once launched kernel by kernel and once recorded into a program and run by the
-    persistent kernel: with every K below 1,024 the stand-alone kernels take the same 512-wide chunks and no cluster,
-    so the sums are formed in the same order and the results must be equal bit for bit, residual rows and cache alike.
+    """The same chain of calls, once launched kernel by kernel and once recorded into a program and run by a
+    persistent kernel. Shared by operations, the persistent kernel runs the stand-alone kernels' own bodies: with every K
+    below 1,024 those take the same 512-wide chunks and no cluster, so the sums are formed in the same order and the
+    results must be equal bit for bit, residual rows and cache alike. Shared by rows, it forms plain dot products.
     Run twice, so that the barrier word and the attention's counters are shown to come back to their start."""
     from glassbox_b200 import kernels
     ps, layers, ctx_len, splits = 16, 3, 300, 3
@@ -1034,7 +1035,13 @@ def test_decode_program_runs_the_operations_the_kernels_would(M, d, nh, nkv, hd,
             kernels.program_end()
         assert kernels.launch_count - before == 1, "the chain was not one launch"
         assert int(st) == 0
-        assert torch.equal(got_x, want_x) and torch.equal(got_k, want_k) and torch.equal(got_v, want_v), f"pass {rep}"
+        if how == "by operations":
+            assert torch.equal(got_x, want_x) and torch.equal(got_k, want_k) and torch.equal(got_v, want_v), f"pass {rep}"
+        else:   # the by-rows kernel adds up in another order (plain dot products): equal within bfloat16 rounding of the chain
+            scale = float(want_x.abs().max())
+            assert float((got_x - want_x).abs().max()) <= 2e-2 * scale, f"pass {rep}: {float((got_x - want_x).abs().max()):.3e} of {scale:.3e}"
+            assert float((got_k.float() - want_k.float()).abs().max()) <= 2e-2 * float(want_k.float().abs().max())
+            assert float((got_v.float() - want_v.float()).abs().max()) <= 2e-2 * float(want_v.float().abs().max())
         assert len(prog.segments) == 1
         del keep
 

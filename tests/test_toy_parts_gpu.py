@@ -173,3 +173,94 @@ def test_routed_feed_forward_and_a_learned_position_encoding_beside_the_stock_pa
                 assert np.abs(row - want[rid][p]).max() <= 1e-4, f"{label} {rid} position {p}"
     assert eng.graph_replays > 0, "steps of these parts replay as CUDA graphs like any others"
     assert eng.cache.free_pages() == eng.cache.num_pages()
+
+
+def test_a_state_mixer_decodes_on_recorded_graphs(tmp_path):
+    """State slots have fixed addresses and the toy mixer reads its slot numbers on the device, so its decode steps
+    are recorded and replayed like any others; its prompt portions, which walk the host's list of sequences, are not."""
+    from glassbox_b200.engine.engine import Engine
+    w = write_toy(str(tmp_path), RAW, seed=2)
+    eng = Engine(str(tmp_path), "float32", cache_tokens=448, max_batch_tokens=256, max_requests=4)
+    assert eng.device_cache.has_state and eng.model.recordable(True) and not eng.model.recordable(False)
+    rng = random.Random(6)
+    requests = {f"r{i}": [rng.randrange(RAW["vocab_size"]) for _ in range(n)] for i, n in enumerate([70, 45, 120])}
+    want = {rid: truth(RAW, w, toks) for rid, toks in requests.items()}
+    # the three requests decode side by side (a batch of three in a graph of four: one padding request), then two, then one
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:20], "want": []} for r, t in requests.items()], "end": []}]
+    for p in range(20, 120):
+        live = [r for r, t in requests.items() if p < len(t)]
+        steps.append({"step": len(steps), "entries": [{"id": r, "tokens": [requests[r][p]], "want": [0]} for r in live],
+                      "end": [r for r in live if p == len(requests[r]) - 1]})
+    got = ru.run_steps_inprocess(eng, steps)
+    assert eng.graph_replays >= 90, "the decode steps of a model with state slots did not replay as graphs"
+    for rid, toks in requests.items():
+        assert sorted(got[rid]) == list(range(20, len(toks)))
+        for p, row in got[rid].items():
+            assert np.abs(row - want[rid][p]).max() <= 1e-4, f"{rid} position {p}"
+    assert len(eng.cache.free_slots) == 4
+
+
+def test_an_embedding_and_a_head_of_ones_own(tmp_path):
+    """The embedding and the head are registered parts like the others: a model with an embedding that scales its rows
+    and a head with a bias (both exist only in these tests) against the plain implementation run on the same weights
+    with the scale folded into the table and the bias added afterwards."""
+    from safetensors.torch import load_file, save_file
+    import glassbox_b200
+    from conftest import tiny_raw
+    from glassbox_b200.engine.engine import Engine
+    raw = tiny_raw("B")                                                  # untied head
+    plain_dir, toy_dir = str(tmp_path / "plain"), str(tmp_path / "toy")
+    glassbox_b200.write_random_model(plain_dir, raw, 3, torch.float32)
+    tensors = load_file(os.path.join(plain_dir, "model.safetensors"))
+    scale = 3.5
+    bias = torch.randn(raw["vocab_size"], generator=torch.Generator().manual_seed(1))
+    toy = dict(tensors)
+    toy["lm_head.bias"] = bias
+    os.makedirs(toy_dir)
+    save_file(toy, os.path.join(toy_dir, "model.safetensors"))
+    with open(os.path.join(toy_dir, "config.json"), "w") as f:
+        json.dump(dict(raw, architectures=["ToyScaledForCausalLM"], embedding_scale=scale), f)
+    folded = dict(tensors)
+    folded["model.embed_tokens.weight"] = tensors["model.embed_tokens.weight"] * scale
+    save_file(folded, os.path.join(plain_dir, "model.safetensors"))
+    rng = random.Random(8)
+    requests = {f"r{i}": [rng.randrange(raw["vocab_size"]) for _ in range(n)] for i, n in enumerate([60, 17, 100])}
+    eng = Engine(toy_dir, "float32", cache_tokens=256, max_batch_tokens=128, max_requests=4)
+    for label, steps in (("whole", ru.whole(requests)), ("tail", ru.tail_one_by_one(requests)),
+                         ("mixed", ru.mixed(requests, random.Random(3)))):
+        got = ru.run_steps_inprocess(eng, steps)
+        for rid, toks in requests.items():
+            want = lp.forward_logits(plain_dir, toks) + bias.double().numpy()
+            for p, row in got.get(rid, {}).items():
+                assert np.abs(row - want[p]).max() <= 1e-4, f"{label} {rid} position {p}"
+    assert eng.graph_replays > 0
+
+
+def test_cache_groups_are_sized_on_their_own(tmp_path):
+    """``group_pages`` sizes each cache group from its spec: the toy model's attention keeps a window of 24 keys, and its
+    group gets 10 pages where the engine's default would have given it 64. Requests far longer than 10 pages run, alone
+    and two side by side through the scheduler, because the window gives pages back as it goes, and admission counts
+    what a windowed group really holds (the window and one step's rows), not the length of the request."""
+    from glassbox_b200.engine.engine import Engine
+    from glassbox_b200.engine.scheduler import Request, Scheduler, SchedulerConfig
+    raw = dict(RAW, window=24, max_position=320)
+    w = write_toy(str(tmp_path), raw, seed=9)
+    sized = []
+
+    def pages(spec):
+        sized.append(spec)
+        return 10 if spec.window is not None else 40
+
+    eng = Engine(str(tmp_path), "float32", cache_tokens=1024, max_batch_tokens=32, max_requests=3, group_pages=pages)
+    assert [s.window for s in sized] == [24] and eng.cache.num_pages(0) == 10 and eng.device_cache.k[0].shape[1] == 10
+    toks = [random.Random(5).randrange(raw["vocab_size"]) for _ in range(300)]
+    want = truth(raw, w, toks)
+    got = ru.run_steps_inprocess(eng, ru.changing_portions({"a": toks}, sizes=(9, 2, 16, 1, 30, 3)))
+    assert max(np.abs(got["a"][p] - want[p]).max() for p in range(300)) <= 1e-4
+    s = Scheduler(eng, SchedulerConfig(token_budget=16, max_seqs=2))
+    assert s._fits(300) and not Scheduler(eng, SchedulerConfig(token_budget=512, max_seqs=2))._fits(300)
+    ids = [s.submit(Request(prompt=toks[:200], max_tokens=3)), s.submit(Request(prompt=toks[50:250], max_tokens=3))]
+    s.step()
+    assert len(s.running) == 2
+    s.run_until_idle()
+    assert all(len(s.finished[i].tokens) == 3 for i in ids) and eng.cache.free_pages(0) == 10

@@ -22,7 +22,7 @@ import torch
 from glassbox_b200.config import (GqaAttentionSpec, LayerSpec, ModelConfig, NoPositionSpec, RmsNormSpec, RopeSpec,
                                   RunSpec, SwiGluSpec)
 from glassbox_b200.config.registry import Architecture, register_architecture
-from glassbox_b200.parts import FeedForward, Mixer, Norm, Position, StateSpec, register_part
+from glassbox_b200.parts import FeedForward, Mixer, Norm, OutputHead, Position, StateSpec, TokenEmbedding, register_part
 from glassbox_b200.weights.binding import ParamSpec, Stacked
 
 
@@ -71,8 +71,23 @@ class RunningState(Mixer):
     def cache_spec(self):
         return StateSpec((self.d,), torch.float32)
 
+    def recordable(self, decode_only):
+        return decode_only                         # prompt portions walk the host's list of sequences (below)
+
     def forward(self, ctx, h, residual, cache, writes_cache):
         w = self.params["w"].float()
+        if ctx.decode_only:
+            # one row per request: everything from the device, so that the step can be replayed as a graph. Padding
+            # requests of a graph's fixed shape (start position -1) must leave every slot as it is.
+            n = h.shape[0]
+            live = (ctx.seq_start_pos[:n] >= 0).unsqueeze(1)
+            idx = ctx.seq_slots[:n].clamp(min=0).long()
+            old = cache.state.index_select(0, idx)
+            new = self.spec.decay * old + h.float()
+            residual += torch.where(live, new @ w.T, torch.zeros_like(new))
+            if writes_cache:
+                cache.state.index_add_(0, idx, torch.where(live, new - old, torch.zeros_like(new)))
+            return
         for seq in ctx.seqs:                       # rows of one request are consecutive and in order
             s = cache.state[seq.slot].clone()
             for r in range(seq.first_row, seq.first_row + seq.n_rows):
@@ -150,6 +165,49 @@ class LearnedOffsetPosition(Position):
         heads += add
 
 
+@dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    """The residual row of a token is its table row times a constant."""
+    scale: float
+    kind: str = "test_scaled_embedding"
+
+
+class ScaledEmbedding(TokenEmbedding):
+    def __init__(self, spec, *, vocab_size, hidden_size):
+        super().__init__(spec)
+        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.vocab_size, self.hidden_size))}
+
+    def forward(self, ctx, tokens, x):
+        from glassbox_b200 import kernels
+        kernels.embed(self.params["weight"], tokens, x, ctx.status)
+        x.mul_(self.spec.scale)
+
+
+@dataclass(frozen=True)
+class BiasedHeadSpec:
+    """logits = hs H^T + b."""
+    kind: str = "test_biased_head"
+
+
+class BiasedHead(OutputHead):
+    def __init__(self, spec, *, vocab_size, hidden_size):
+        super().__init__(spec)
+        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.vocab_size, self.hidden_size)), "bias": ParamSpec((self.vocab_size,), role="gain")}
+
+    def forward(self, ctx, hs, logits):
+        from glassbox_b200.parts.linear import linear
+        linear(ctx, hs, self.params["weight"], logits)
+        logits += self.params["bias"]
+
+
+register_part("embedding", "test_scaled_embedding", ScaledEmbedding, replace=True)
+register_part("head", "test_biased_head", BiasedHead, replace=True)
 register_part("ffn", "test_routed_ffn", RoutedFfn, replace=True)
 register_part("position", "test_learned_offset", LearnedOffsetPosition, replace=True)
 register_part("mixer", "test_zero_mixer", ZeroMixer, replace=True)
@@ -241,6 +299,26 @@ def _bind_toy_routed(config):
 
 
 register_architecture(Architecture("ToyRoutedForCausalLM", _parse_toy_routed, _bind_toy_routed), replace=True)
+
+
+def _parse_toy_scaled(raw):
+    """``ToyScaledForCausalLM``: the stock Llama layers between an embedding that scales its rows and a head with a bias;
+    both are parts that exist only here."""
+    import dataclasses
+    from glassbox_b200.models.llama import parse_llama_config
+    cfg = parse_llama_config(raw)
+    return dataclasses.replace(cfg, architecture="ToyScaledForCausalLM", embedding=ScaledEmbeddingSpec(scale=float(raw["embedding_scale"])),
+                               head=BiasedHeadSpec())
+
+
+def _bind_toy_scaled(config):
+    from glassbox_b200.models.llama import bind_llama_weights
+    b = bind_llama_weights(config)
+    b["head.bias"] = Stacked(("lm_head.bias",))
+    return b
+
+
+register_architecture(Architecture("ToyScaledForCausalLM", _parse_toy_scaled, _bind_toy_scaled), replace=True)
 
 
 def _parse_one_part(raw):
