@@ -31,8 +31,9 @@
 //    order (a fixed order: the result does not depend on timing) and runs the epilogue.
 #include "gemm_stream_body.cuh"
 
+// (the smallest variant is held to 128 registers, four blocks per SM: its choice of cluster size counts on that)
 template <int NT, bool PAIR, int KC>
-__global__ void __launch_bounds__(128) gemm_stream_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(128, (NT == 1 && !PAIR) ? 4 : 1) gemm_stream_kernel(const StreamArgs a) {
     __shared__ __align__(16) unsigned char xs[gemm_stream_smem_bytes<NT, KC>()];
     __shared__ float srow[NT * 8];
     GbPdlSync sync;

@@ -63,6 +63,14 @@ __device__ __forceinline__ uint32_t ws_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Activations and residual rows: in a persistent kernel another block of the same launch wrote them, so they are read
+// past L1 (which is not coherent between SMs); in the stand-alone kernel an earlier kernel wrote them and L1 may keep them.
+template <bool PERSIST, typename V>
+__device__ __forceinline__ V ld_act(const V* p) {
+    if constexpr (PERSIST) return __ldcg(p);
+    else return *p;
+}
+
 // Ask the memory system to bring the weights of virtual block `vblock` of a product into L2 (a hint; it writes and
 // needs nothing): what a resident block of the persistent kernel does for its next product before it waits.
 template <bool PAIR>
@@ -182,7 +190,7 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             if (m < M) {
                 const float* xr = a.xres + (size_t)m * a.ldr;
                 for (int k = lane * 4; k < K; k += 128) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(xr + k));
+                    const float4 v = ld_act<PERSIST>(reinterpret_cast<const float4*>(xr + k));
                     ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
                 }
             }
@@ -200,7 +208,7 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
         for (int i = 0; i < XPT; ++i) {
             const int c = tid + i * 128;
             const int row = c / (WS_KC / 8), k = kbeg + chunk * WS_KC + (c % (WS_KC / 8)) * 8;
-            xr[i] = (row < M && k < kend) ? __ldcg(reinterpret_cast<const uint4*>(a.X + (size_t)row * a.ldx + k)) : make_uint4(0, 0, 0, 0);
+            xr[i] = (row < M && k < kend) ? ld_act<PERSIST>(reinterpret_cast<const uint4*>(a.X + (size_t)row * a.ldx + k)) : make_uint4(0, 0, 0, 0);
         }
     };
     if (!normalise && nchunks > 0) xload(0);
@@ -215,7 +223,7 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
                 uint4 v = make_uint4(0, 0, 0, 0);
                 if (row < M && k < kend) {
                     const float* xrow = a.xres + (size_t)row * a.ldr + k;
-                    const float4 x0 = __ldcg(reinterpret_cast<const float4*>(xrow)), x1 = __ldcg(reinterpret_cast<const float4*>(xrow + 4));
+                    const float4 x0 = ld_act<PERSIST>(reinterpret_cast<const float4*>(xrow)), x1 = ld_act<PERSIST>(reinterpret_cast<const float4*>(xrow + 4));
                     const float4 g0 = *reinterpret_cast<const float4*>(a.gain + k);
                     const float4 g1 = *reinterpret_cast<const float4*>(a.gain + k + 4);
                     const float s = srow[row];
@@ -353,7 +361,8 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             reinterpret_cast<float*>(a.C)[(size_t)tok * a.ldc + n] = v[0];
         } else {
             float* p = reinterpret_cast<float*>(a.C) + (size_t)tok * a.ldc + n;
-            __stcg(p, __ldcg(p) + v[0]);
+            if constexpr (PERSIST) __stcg(p, __ldcg(p) + v[0]);
+            else *p += v[0];
         }
     }
 }
