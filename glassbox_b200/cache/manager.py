@@ -74,6 +74,7 @@ _SIGNATURES = {
     "gbh_cache_ids": ([_P, _I, _P, _I], _I),
     "gbh_chain_hash": ([ctypes.c_uint64, _P, _I], ctypes.c_uint64),
     "gbh_plan_step": ([_P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P], _I),
+    "gbh_decode_plan": ([_P, _I, _P, _I, _P, _P, _P], _I),
     "gbh_fill_step": ([_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _P, _I, _P, _P], _I),
 }
 _lib = None
@@ -274,7 +275,7 @@ class CacheManager:
     def commit_many(self, rids, tok_count: np.ndarray, tokens: np.ndarray) -> None:
         """``commit`` for several requests in one call: request e brings ``tok_count[e]`` tokens, flat in
         ``tokens`` (int32)."""
-        ids = np.fromiter((self._id(r) for r in rids), dtype=np.int64, count=len(rids))
+        ids = rids if isinstance(rids, np.ndarray) else np.fromiter((self._id(r) for r in rids), dtype=np.int64, count=len(rids))
         code = self._lib.gbh_cache_commit_many(self._h, len(rids), ids.ctypes.data, tok_count.ctypes.data, tokens.ctypes.data)
         if code:
             self._raise(code)
@@ -336,6 +337,23 @@ class CacheManager:
         triples = [(int(copies[3 * j]), int(copies[3 * j + 1]), int(copies[3 * j + 2])) for j in range(nc)]
         return plan, triples, int(tail[2]), bool(tail[3])
 
+    def native_ids(self, rids) -> np.ndarray:
+        """The 64-bit names under which the library knows these requests (for the calls that take them directly)."""
+        return np.fromiter((self._ids[r] for r in rids), dtype=np.int64, count=len(rids))
+
+    def decode_plan(self, ids: np.ndarray, max_position: int):
+        """Room for one more token of every request named by ``ids`` (native names), all or nothing, in one call (see
+        ``gbh_decode_plan``). Returns (code, copy-on-write triples, widest block table): code 0 = reserved; 1 = out of
+        pages and 2 = a request is at ``max_position`` (nothing was reserved either way)."""
+        n = int(ids.size)
+        out = np.empty(3 * max(len(self.groups), 1) * max(n, 1) + 2, dtype=np.int32)
+        code = self._lib.gbh_decode_plan(self._h, n, ids.ctypes.data, int(max_position), out.ctypes.data,
+                                         out[-2:].ctypes.data, out[-1:].ctypes.data)
+        if code:
+            return code, [], 0
+        nc = int(out[-2])
+        return 0, [(int(out[3 * j]), int(out[3 * j + 1]), int(out[3 * j + 2])) for j in range(nc)], int(out[-1])
+
     # ------------------------------------------------------------------------------ a step's metadata
     def fill_step(self, rids, tok_count: np.ndarray, tokens: np.ndarray, want_count: np.ndarray, want: np.ndarray,
                   n: int, S: int, n_want: int, max_pages: int, offsets: np.ndarray, host: np.ndarray,
@@ -345,7 +363,7 @@ class CacheManager:
         ``sample_mask`` (uint8, one per wanted row) marks the wanted rows that are sampled from their request's own
         sampling state. Returns ((start position, slot, first row) per entry as an int32 array [E, 3], longest context)."""
         E = len(rids)
-        ids = np.fromiter((self._ids[r] for r in rids), dtype=np.int64, count=E)
+        ids = rids if isinstance(rids, np.ndarray) else np.fromiter((self._ids[r] for r in rids), dtype=np.int64, count=E)
         info = np.empty((max(E, 1), 3), dtype=np.int32)
         longest = ctypes.c_int(0)
         k = 0 if sample_mask is None else int(sample_mask.size)

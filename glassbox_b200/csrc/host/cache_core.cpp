@@ -573,6 +573,37 @@ GBH_EXPORT int gbh_plan_step(void* h, int n_running, const int64_t* rids, const 
     return OK;
 }
 
+// A step in which every running request decodes one token, planned in one call: the requests must all have room below
+// `max_position` (else BAD_VALUE: the caller's general path ends the request that has none), a slot for one more token
+// is reserved for each, all or nothing (else OUT_OF_PAGES and nothing is held that was not held before: the caller's
+// general path decides whom to preempt). Out: copy-on-write triples, and the widest block table among the requests.
+GBH_EXPORT int gbh_decode_plan(void* h, int n, const int64_t* rids, int max_position, int* copies, int* n_copies, int* max_pages) {
+    Cache* c = static_cast<Cache*>(h);
+    for (int e = 0; e < n; ++e) {
+        Request* req = find(c, rids[e]);
+        if (!req) return fail(UNKNOWN_REQUEST, "unknown request");
+        if (req->length + 1 > max_position) return fail(BAD_VALUE, "a request has reached max_position");
+    }
+    std::vector<int> one(3 * std::max<size_t>(c->groups.size(), 1));
+    int nc = 0;
+    for (int e = 0; e < n; ++e) {
+        int got = 0;
+        const int code = gbh_cache_reserve(h, rids[e], 1, one.data(), &got);
+        if (code != OK) {
+            for (int k = 0; k < e; ++k) gbh_cache_truncate(h, rids[k], find(c, rids[k])->length);   // give the new pages back
+            return code;
+        }
+        std::memcpy(copies + 3 * nc, one.data(), sizeof(int) * 3 * got);
+        nc += got;
+    }
+    int widest = 1;
+    for (const Group& g : c->groups)
+        for (int e = 0; e < n; ++e) widest = std::max(widest, (int)g.tables.find(rids[e])->second.size());
+    *n_copies = nc;
+    *max_pages = widest;
+    return OK;
+}
+
 // ------------------------------------------------------------------------------ a step's metadata
 // Fills the int32 block that a step copies to the device. Its sections start at the offsets given:
 //   off[0..7]: tokens [n], positions [n], row_seq [n], want [n_want], seq_first_row [S+1], seq_start_pos [S],

@@ -43,3 +43,19 @@ GB_EXPORT int gb_device_arch() {
 }
 
 GB_EXPORT int gb_abi_version() { return 1; }
+
+// One decode step's traffic in one call: the step's metadata block to the device, the step's recorded graph, the
+// sampled tokens back to the host; all on `stream`, nothing is waited for. `graph_exec` is a cudaGraphExec_t.
+GB_EXPORT int gb_step_io(const void* host_meta, void* dev_meta, long long meta_bytes, void* graph_exec, const void* sampled_dev,
+                         void* sampled_host, long long sampled_bytes, cudaStream_t stream) {
+    GB_REQUIRE(host_meta && dev_meta && graph_exec && meta_bytes > 0, "gb_step_io: bad arguments");
+    cudaError_t e = cudaMemcpyAsync(dev_meta, host_meta, (size_t)meta_bytes, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec), stream);
+    if (e == cudaSuccess && sampled_bytes > 0)
+        e = cudaMemcpyAsync(sampled_host, sampled_dev, (size_t)sampled_bytes, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) {
+        gb_set_error("gb_step_io: %s", cudaGetErrorString(e));
+        return 2;
+    }
+    return 0;
+}

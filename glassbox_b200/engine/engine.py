@@ -111,6 +111,8 @@ class Engine:
         self.graph_replays = 0
         self.sampled: Optional[torch.Tensor] = None
         self._sampled_host: Optional[torch.Tensor] = None
+        self._ones = np.ones(self.max_graph_batch, dtype=np.int32)
+        self._zeros = np.zeros(self.max_graph_batch, dtype=np.int32)
         self.h2d_bytes_last = 0
 
     # ---------------------------------------------------------------------------- requests
@@ -412,6 +414,43 @@ class Engine:
         self.graph_replays += 1
         return g["logits"][:S]
 
+    def decode_fast(self, requests, tokens: np.ndarray, sample_mask: np.ndarray):
+        """The steady state of generation in as few host operations as it takes: every request of ``requests`` brings
+        the one token ``tokens[i]`` (int32) and wants its next token, sampled on the device (from the request's own
+        sampling state where ``sample_mask[i]`` is set, else greedily). One native call plans the step (room for one
+        token each, all or nothing), one fills the metadata block, one sends it, launches the step's recorded graph and
+        fetches the sampled tokens, one commits. Returns the sampled tokens (int32 numpy array, valid until the next
+        step), or None when this path does not take the step as it stands (no graphs, too many requests, a request at
+        ``max_position``, pages run out): nothing has changed then, and ``step`` does whatever has to be done."""
+        n = len(requests)
+        if not (self.use_graphs and 0 < n <= self.max_graph_batch and self.model.recordable(True)):
+            return None
+        cache = self.cache
+        ids = cache.native_ids(requests)
+        code, copies, max_pages = cache.decode_plan(ids, self.config.max_position)
+        if code:
+            return None
+        self.run_copies(copies)
+        Sb = 1 << max(n - 1, 0).bit_length()
+        Pb = max(8, 1 << max(max_pages - 1, 0).bit_length())
+        off = self._layout(Sb, Sb, Sb, Pb)
+        g = self._decode_graph(Sb, Pb)
+        ones, zeros = self._ones[:n], self._zeros[:n]
+        host = self._stage_buffer(off["_size"])
+        self._stage_events[self._stage_next] = None      # this step ends with a synchronisation: the buffer is free after it
+        cache.fill_step(ids, ones, tokens, ones, zeros, Sb, Sb, Sb, Pb, off["_array"], host, sample_mask)
+        if self._sampled_host is None or self._sampled_host.numel() < n:
+            self._sampled_host = torch.empty(max(n, 64), dtype=torch.int32).pin_memory()
+        kernels.step_io(host.ctypes.data, g["meta"], off["_size"] * 4, g["exec"], g["sampled"], self._sampled_host, n,
+                        g["nodes"])
+        self.h2d_bytes_last = off["_size"] * 4
+        cache.commit_many(ids, ones, tokens)             # host bookkeeping, while the device works
+        self.graph_replays += 1
+        self.steps += 1
+        self.sampled = None
+        torch.cuda.current_stream().synchronize()
+        return self._sampled_host.numpy()[:n]
+
     def _capture(self, key, off, host, n, S, n_want, Pb, max_rows, decode_only, lead=0):
         """Record the kernels of one step shape into a CUDA graph with a metadata block, logits and
         scratch of its own. The kernels run once outside capture first, on the metadata given (for a
@@ -459,7 +498,7 @@ class Engine:
             if was_enabled:
                 gc.enable()
         g = {"graph": graph, "meta": meta, "logits": logits, "sampled": sampled, "ctx": ctx,
-             "nodes": kernels.launch_count - before}
+             "nodes": kernels.launch_count - before, "exec": int(graph.raw_cuda_graph_exec())}
         self._graphs[key] = g
         return g
 

@@ -37,6 +37,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Deque, Dict, List, Optional, Sequence
 
+import numpy as np
+
 from ..cache.manager import OutOfPages
 from ..sampling.sampler import Sampler, SamplerConfig
 
@@ -83,6 +85,7 @@ class _Seq:
         #: state of the request's random generator while it holds no state slot (before admission, after a preemption)
         self.rng_state = self.sampler.rng.state
         self.slot: Optional[int] = None
+        self.device_sampled = 0 if req.sampler.needs_host else 1
         self.arrival = now
         self.first_token: Optional[float] = None
         self.last_token: Optional[float] = None
@@ -227,9 +230,59 @@ class Scheduler:
         return True
 
     # ---------------------------------------------------------------------------------- step
+    def _decode_step(self, t0: float) -> bool:
+        """The steady state: nobody can be admitted and every running request decodes one token that the device samples.
+        The backend plans, runs and commits such a step in a few native calls (``decode_fast``); what is left here is
+        to hand out the tokens. Returns False when the step is not of that kind (or the backend declines it: pages run
+        out, a request is at its limit): the general path then takes it, from the same state."""
+        run, cfg = self.running, self.config
+        fast = getattr(self.backend, "decode_fast", None)
+        if fast is None or not run or len(run) > cfg.token_budget or (self.waiting and len(run) < cfg.max_seqs):
+            return False
+        for s in run:
+            if len(s.tokens) - s.computed != 1 or not s.device_sampled or s.generated >= s.req.max_tokens:
+                return False
+        n = len(run)
+        tokens = np.fromiter((s.tokens[-1] for s in run), dtype=np.int32, count=n)
+        mask = np.ones(n, dtype=np.uint8)
+        picked = fast([s.id for s in run], tokens, mask)
+        if picked is None:
+            return False
+        now = time.perf_counter()
+        limit = self.backend.max_position
+        done, batch_desc = [], []
+        for i, s in enumerate(run):
+            t = int(picked[i])
+            batch_desc.append((s.id, "decode" if s.generated else "prefill", 1))
+            s.computed += 1
+            if s.first_token is None:
+                s.first_token = now
+            elif s.last_token is not None:
+                self.metrics.itl.append(now - s.last_token)
+            s.last_token = now
+            if t in s.req.stop:
+                done.append((i, STOP))
+                continue
+            s.tokens.append(t)
+            if s.req.on_token:
+                s.req.on_token(s.id, t)
+            if s.generated >= s.req.max_tokens or len(s.tokens) >= limit:
+                done.append((i, LENGTH))
+        finished = []
+        for i, reason in reversed(done):
+            s = run.pop(i)
+            finished.append(s.id)
+            self._finish(s, reason)
+        self.metrics.steps += 1
+        self.metrics.batch_tokens += n
+        self._record(t0, batch_desc, [], finished)
+        return True
+
     def step(self) -> bool:
         """One batch through the model. Returns False when there was nothing to do."""
         t0 = time.perf_counter()
+        if self._decode_step(t0):
+            return True
         cfg, cache = self.config, self.backend.cache
         preempted: List[int] = []
         finished: List[int] = []

@@ -70,6 +70,7 @@ _SIGNATURES = {
     "gb_program_launch": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P],
     "gb_program_launch_with_absent_blocks": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _LL, _P],
     "gb_program_launch_traced": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "gb_step_io": [_P, _P, _LL, _P, _P, _P, _LL, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
 }
@@ -100,6 +101,18 @@ def lib():
             handle.gb_set_pdl(int(os.environ.get("GLASSBOX_B200_PDL", "7")) if USE_PDL else 0)
             _lib = handle
     return _lib
+
+
+def step_io(host_meta_ptr: int, dev_meta: torch.Tensor, meta_bytes: int, graph_exec: int, sampled_dev: torch.Tensor,
+            sampled_host: torch.Tensor, count: int, nodes: int) -> None:
+    """A recorded decode step's traffic in one native call: metadata to the device, the graph, ``count`` sampled tokens
+    back to pinned host memory; nothing is waited for. ``nodes``: the graph's kernel count, for ``launch_count``."""
+    global launch_count
+    rc = lib().gb_step_io(host_meta_ptr, dev_meta.data_ptr(), meta_bytes, graph_exec, sampled_dev.data_ptr(),
+                          sampled_host.data_ptr(), 4 * count, _stream())
+    if rc != 0:
+        raise KernelError(lib().gb_last_error().decode("utf-8", "replace") or "gb_step_io failed")
+    launch_count += nodes
 
 
 def loaded_library_path() -> Optional[str]:

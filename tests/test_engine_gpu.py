@@ -134,6 +134,7 @@ class StepSpy:
         self.engine, self.rows = engine, []
         self.real_step = engine.step
         engine.step = self.step
+        engine.decode_fast = None      # (the scheduler's short cut for pure decode steps hands out tokens, not logits)
 
     def step(self, entries, **kw):
         starts = [self.engine.cache.length(e.request) for e in entries]
