@@ -60,6 +60,9 @@ class DeviceCache:
         # Sampling state of each live request, in its state slot: {generator state low word, high word, temperature
         # bits, unused}; zero (greedy) for a fresh slot, copied on fork like every other per-request state.
         self.sampling = torch.zeros((max_requests, 4), dtype=torch.int32, device=device)
+        # The token the sampling kernel chose last for the request in each slot: the next step can take it from here on
+        # the device, before the host has read it.
+        self.last_token = torch.zeros(max_requests, dtype=torch.int32, device=device)
         self.group_pages = [int(pages_per_group(s)) for s in self.group_specs]
         self.k: List[torch.Tensor] = []
         self.v: List[torch.Tensor] = []
@@ -99,6 +102,7 @@ class DeviceCache:
         for t in self.state.values():
             t[dst].copy_(t[src])
         self.sampling[dst].copy_(self.sampling[src])
+        self.last_token[dst].copy_(self.last_token[src])
 
     def set_sampling(self, slot: int, temperature: float, rng_state: int) -> None:
         import struct

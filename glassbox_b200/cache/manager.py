@@ -75,7 +75,7 @@ _SIGNATURES = {
     "gbh_chain_hash": ([ctypes.c_uint64, _P, _I], ctypes.c_uint64),
     "gbh_plan_step": ([_P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P], _I),
     "gbh_decode_plan": ([_P, _I, _P, _I, _P, _P, _P], _I),
-    "gbh_fill_step": ([_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _P, _I, _P, _P], _I),
+    "gbh_fill_step": ([_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _P, _I, _P, _P, _P], _I),
 }
 _lib = None
 _lock = threading.Lock()
@@ -357,11 +357,14 @@ class CacheManager:
     # ------------------------------------------------------------------------------ a step's metadata
     def fill_step(self, rids, tok_count: np.ndarray, tokens: np.ndarray, want_count: np.ndarray, want: np.ndarray,
                   n: int, S: int, n_want: int, max_pages: int, offsets: np.ndarray, host: np.ndarray,
-                  sample_mask: Optional[np.ndarray] = None, lead: int = 0, pad_after: int = 0):
+                  sample_mask: Optional[np.ndarray] = None, lead: int = 0, pad_after: int = 0,
+                  feedback_mask: Optional[np.ndarray] = None):
         """Write the int32 metadata block of a step into ``host`` (see ``gbh_fill_step``): ``pad_after``
         padding sequences follow the first ``lead`` entries, the rest of the padding the last one.
         ``sample_mask`` (uint8, one per wanted row) marks the wanted rows that are sampled from their request's own
-        sampling state. Returns ((start position, slot, first row) per entry as an int32 array [E, 3], longest context)."""
+        sampling state; ``feedback_mask`` (uint8, one per entry) the single-token entries whose token the device takes from
+        what it sampled for the request in the step before. Returns ((start position, slot, first row) per entry as an
+        int32 array [E, 3], longest context)."""
         E = len(rids)
         ids = rids if isinstance(rids, np.ndarray) else np.fromiter((self._ids[r] for r in rids), dtype=np.int64, count=E)
         info = np.empty((max(E, 1), 3), dtype=np.int32)
@@ -370,7 +373,8 @@ class CacheManager:
         code = self._lib.gbh_fill_step(
             self._h, E, ids.ctypes.data, tok_count.ctypes.data, tokens.ctypes.data, want_count.ctypes.data,
             want.ctypes.data, int(lead), int(pad_after), n, S, n_want, max_pages, offsets.ctypes.data, host.size,
-            host.ctypes.data, sample_mask.ctypes.data if k else None, k, info.ctypes.data, ctypes.byref(longest))
+            host.ctypes.data, sample_mask.ctypes.data if k else None, k,
+            feedback_mask.ctypes.data if feedback_mask is not None else None, info.ctypes.data, ctypes.byref(longest))
         if code:
             self._raise(code)
         return info[:E], longest.value

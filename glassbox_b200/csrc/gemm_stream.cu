@@ -71,13 +71,6 @@ static int launch_stream(const StreamArgs& a, int strips, int split, int pdl, cu
     return gb_check_launch("gb_gemm_stream");
 }
 
-// Overrides for measurements: chunk (0 = choose, 256, 512) and cluster size (0 = choose, 1, 2, 4, 8).
-static int g_tune_chunk = 0, g_tune_split = 0;
-GB_EXPORT void gb_gemm_stream_tune(int chunk, int split) {
-    g_tune_chunk = chunk;
-    g_tune_split = split;
-}
-
 static int stream_sm_count() {
     static int sms = 0;
     if (sms == 0) {
@@ -118,7 +111,6 @@ static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStr
     // have neither the registers nor the shared memory for it).
     const bool wide_fits = nt <= (pair ? 2 : 4);
     int kc = (wide_fits && strips <= slots_of(nt, pair, 512)) ? 512 : 256;
-    if (g_tune_chunk == 256 || (g_tune_chunk == 512 && wide_fits)) kc = g_tune_chunk;
     // Cluster size: one block per 512 k, rounded up to a power of two, as long as all blocks are on the
     // chip at once and the other ranks' sums fit the first block's activation tile. Chunk and cluster
     // size depend on the matrix and on the row bucket (8, 16, 32, 64), not on which rows are in the batch.
@@ -127,7 +119,6 @@ static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStr
     int split = 1;
     while (split < 8 && split < a.K / 512) split *= 2;
     while (split > 1 && (split > max_split || strips * split > slots)) split /= 2;
-    if (g_tune_split >= 1 && g_tune_split <= 8 && g_tune_split <= max_split) split = g_tune_split;
     a.kslice = split == 1 ? a.K : ((a.K + split - 1) / split + kc - 1) / kc * kc;
 #define GB_WS2(NTT, KCC) return pair ? launch_stream<NTT, true, KCC>(a, strips, split, pdl, stream) : launch_stream<NTT, false, KCC>(a, strips, split, pdl, stream);
 #define GB_WS(NTT) if (kc == 512) { GB_WS2(NTT, 512) } else { GB_WS2(NTT, 256) }

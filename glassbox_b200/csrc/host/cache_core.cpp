@@ -606,10 +606,13 @@ GBH_EXPORT int gbh_decode_plan(void* h, int n, const int64_t* rids, int max_posi
 
 // ------------------------------------------------------------------------------ a step's metadata
 // Fills the int32 block that a step copies to the device. Its sections start at the offsets given:
-//   off[0..7]: tokens [n], positions [n], row_seq [n], want [n_want], seq_first_row [S+1], seq_start_pos [S],
-//   seq_slots [S], want_slots [n_want]; then per group g: off[8+2g] slots [n], off[9+2g] tables [S, max_pages].
+//   off[0..8]: tokens [n], positions [n], row_seq [n], want [n_want], seq_first_row [S+1], seq_start_pos [S],
+//   seq_slots [S], want_slots [n_want], token_slots [n]; then per group g: off[9+2g] slots [n], off[10+2g] tables
+//   [S, max_pages].
 // want_slots names, for each wanted row that is to be sampled from its request's own sampling state (sample_mask,
 // one byte per wanted row of the entries, or null: none), the request's state slot, and -1 for every other wanted row.
+// token_slots names, for the one row of each entry whose byte in feedback_mask is set, the request's state slot (the
+// device puts the token it sampled for the request in the step before into that row), and -1 for every other row.
 // The E entries bring tok_count[e] tokens each (flat in tokens) and ask for want_count[e] of their rows
 // (indices within the entry, flat in want). The step has a fixed shape of S >= E sequences and n rows:
 // pad_after padding sequences follow the first `lead` entries (so that a batch whose leading single-token
@@ -623,7 +626,8 @@ GBH_EXPORT int gbh_decode_plan(void* h, int n, const int64_t* rids, int max_posi
 GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok_count, const int32_t* tokens,
                              const int* want_count, const int* want, int lead, int pad_after, int n, int S, int n_want,
                              int max_pages, const long long* off, long long size, int32_t* host,
-                             const unsigned char* sample_mask, int n_mask, int* seq_info, int* max_ctx) {
+                             const unsigned char* sample_mask, int n_mask, const unsigned char* feedback_mask,
+                             int* seq_info, int* max_ctx) {
     Cache* c = static_cast<Cache*>(h);
     const int G = (int)c->groups.size();
     if (S < E + pad_after || lead < 0 || lead > E || pad_after < 0) return fail(BAD_VALUE, "fewer sequences than entries");
@@ -642,11 +646,13 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
     int32_t* h_start = host + off[5];
     int32_t* h_slots = host + off[6];
     int32_t* h_want_slots = host + off[7];
+    int32_t* h_token_slots = host + off[8];
     std::fill(h_pos, h_pos + n, -1);
     std::fill(h_want_slots, h_want_slots + n_want, -1);
+    std::fill(h_token_slots, h_token_slots + n, -1);
     for (int g = 0; g < G; ++g) {
-        std::fill(host + off[8 + 2 * g], host + off[8 + 2 * g] + n, -1);
-        std::fill(host + off[9 + 2 * g], host + off[9 + 2 * g] + (long long)S * max_pages, -1);
+        std::fill(host + off[9 + 2 * g], host + off[9 + 2 * g] + n, -1);
+        std::fill(host + off[10 + 2 * g], host + off[10 + 2 * g] + (long long)S * max_pages, -1);
     }
     std::vector<int> pad_rows;
     int row = 0, wi = 0, longest = 0, tcur = 0, wcur = 0, seq = 0;
@@ -679,14 +685,15 @@ GBH_EXPORT int gbh_fill_step(void* h, int E, const int64_t* rids, const int* tok
         h_first[seq] = row;
         h_start[seq] = start;
         h_slots[seq] = req->slot;
+        if (feedback_mask && feedback_mask[e] && k == 1) h_token_slots[row] = req->slot;
         for (int g = 0; g < G; ++g) {
             const Group& gr = c->groups[g];
             const std::vector<int>& table = gr.tables.find(rids[e])->second;
             if ((int)table.size() > max_pages) return fail(BAD_VALUE, "a block table is wider than the step's tables");
             if ((start + k + gr.page_size - 1) / gr.page_size > (int)table.size())
                 return fail(BAD_VALUE, "a request brings tokens for which no page was reserved");
-            std::memcpy(host + off[9 + 2 * g] + (long long)seq * max_pages, table.data(), sizeof(int) * table.size());
-            int32_t* sl = host + off[8 + 2 * g] + row;
+            std::memcpy(host + off[10 + 2 * g] + (long long)seq * max_pages, table.data(), sizeof(int) * table.size());
+            int32_t* sl = host + off[9 + 2 * g] + row;
             for (int i = 0; i < k; ++i) {
                 const int pos = start + i;
                 sl[i] = table[pos / gr.page_size] * gr.page_size + pos % gr.page_size;

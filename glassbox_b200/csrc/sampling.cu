@@ -11,8 +11,8 @@
 // the device beside the request's other per-request state. The kernel then advances the request's xorshift64*
 // generator itself (sampler.rs:31-47: x ^= x >> 12; x ^= x << 25; x ^= x >> 27; r = (x * 0x2545f4914f6cdd1d) >> 40,
 // r / 2^24), once per sampled token, so that nothing has to be drawn on the host for a step.
-// Every reduction has a fixed shape (thread t owns a contiguous run of the vocabulary, then a
-// serial scan over the threads' sums), so a row's result never depends on the other rows.
+// Every reduction has a fixed shape (a warp owns a contiguous run of the vocabulary, then a serial scan over the
+// warps' sums, then a scan over the lanes), so a row's result never depends on the other rows.
 #include "common.cuh"
 
 #include <float.h>
@@ -24,11 +24,10 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
                                                                 const float* __restrict__ uniform,
                                                                 const int* __restrict__ want_slots,
                                                                 unsigned* __restrict__ state, int num_slots,
+                                                                int* __restrict__ last_token,
                                                                 int* __restrict__ out, int vocab) {
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* l = logits + (size_t)row * stride;
-    const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-    const int lo = min(tid * chunk, vocab), hi = min(lo + chunk, vocab);
     __shared__ float s_val[SAMPLE_THREADS];
     __shared__ int s_idx[SAMPLE_THREADS];
     __shared__ float s_pref[SAMPLE_THREADS + 1];
@@ -58,9 +57,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     const float vmax = s_val[0];
     const int imax = s_idx[0];
     __shared__ float s_draw[2];   // temperature, uniform
+    __shared__ int s_slot;
     if (tid == 0) {
         float temp0 = temperature ? temperature[row] : 0.f, r = uniform ? uniform[row] : 0.f;
         const int slot = want_slots ? want_slots[row] : -1;
+        s_slot = (slot >= 0 && slot < num_slots && last_token != nullptr) ? slot : -1;
         if (slot >= 0 && slot < num_slots) {   // the request's own state: its temperature, and the next draw of its generator
             unsigned* st = state + 4 * (size_t)slot;
             temp0 = __uint_as_float(st[2]);
@@ -80,47 +81,99 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     __syncthreads();
     const float temp = s_draw[0];
     if (!(temp > 0.f)) {
-        if (tid == 0) out[row] = imax;
+        if (tid == 0) {
+            out[row] = imax;
+            if (s_slot >= 0) last_token[s_slot] = imax;
+        }
         return;
     }
-    const float mscaled = vmax / temp;
+    // Temperature: every warp owns a contiguous run of the vocabulary and reads it coalesced. First the runs' sums
+    // (and a serial scan over the sixteen of them), then the one warp whose run holds the target walks it, 32 tokens
+    // at a time, with a scan over its lanes: the walk is in token order, and each pass reads a row once.
+    const float inv_temp = 1.0f / temp;   // exp((l - max) / temperature): the maximum subtracted before the division
+    const int lane = tid & 31, warp = tid >> 5;
+    constexpr int WARPS = SAMPLE_THREADS / 32;
+    const int run = ((vocab + WARPS - 1) / WARPS + 31) / 32 * 32;
+    const int wlo = min(warp * run, vocab), whi = min(wlo + run, vocab);
     float part = 0.f;
-    for (int i = lo; i < hi; ++i) part += expf(l[i] / temp - mscaled);
-    s_val[tid] = part;
+    for (int i = wlo + lane; i < whi; i += 32) part += __expf((l[i] - vmax) * inv_temp);
+    part = gb_warp_sum(part);
+    if (lane == 0) s_val[warp] = part;
     __syncthreads();
     if (tid == 0) {
-        float run = 0.f;
-        for (int t = 0; t < SAMPLE_THREADS; ++t) {
-            s_pref[t] = run;
-            run += s_val[t];
+        float acc = 0.f;
+        for (int w = 0; w < WARPS; ++w) {
+            s_pref[w] = acc;
+            acc += s_val[w];
         }
-        s_pref[SAMPLE_THREADS] = run;
+        s_pref[WARPS] = acc;
         out[row] = max(vocab - 1, 0);  // fallback: the last token, as sampler.rs:163
+        if (s_slot >= 0) last_token[s_slot] = max(vocab - 1, 0);
     }
     __syncthreads();
-    const float target = s_draw[1] * s_pref[SAMPLE_THREADS];
-    // Exactly one thread's half-open interval [pref, pref + part) holds the target (if any does).
-    if (lo < hi && target >= s_pref[tid] && target < s_pref[tid + 1]) {
-        float run = s_pref[tid];
-        int pick = hi - 1;
-        for (int i = lo; i < hi; ++i) {
-            run += expf(l[i] / temp - mscaled);
-            if (target < run) { pick = i; break; }
+    const float target = s_draw[1] * s_pref[WARPS];
+    // Exactly one warp's half-open interval [pref, pref + sum) holds the target (if any does). Inside its run every lane
+    // takes a contiguous piece: the lanes' sums, one scan over them, and the one lane whose piece holds the target walks it.
+    if (wlo < whi && target >= s_pref[warp] && target < s_pref[warp + 1]) {
+        const int piece = (whi - wlo + 31) / 32;
+        const int plo = min(wlo + lane * piece, whi), phi = min(plo + piece, whi);
+        float mine = 0.f;
+        for (int i = plo; i < phi; ++i) mine += __expf((l[i] - vmax) * inv_temp);
+        float upto = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {   // inclusive scan over the lanes, in token order
+            const float up = __shfl_up_sync(0xffffffffu, upto, o);
+            if (lane >= o) upto += up;
         }
-        out[row] = pick;
+        const float before = s_pref[warp] + upto - mine;
+        const unsigned hit = __ballot_sync(0xffffffffu, plo < phi && target < before + mine);
+        // the first lane whose piece reaches past the target; rounding may leave none: then the run's last token
+        const int owner = hit ? __ffs(hit) - 1 : -1;
+        int pick = whi - 1;
+        if (lane == owner) {
+            float acc = before;
+            pick = phi - 1;
+            for (int i = plo; i < phi; ++i) {
+                acc += __expf((l[i] - vmax) * inv_temp);
+                if (target < acc) { pick = i; break; }
+            }
+        }
+        if (lane == (owner >= 0 ? owner : 0)) {
+            out[row] = pick;
+            if (s_slot >= 0) last_token[s_slot] = pick;
+        }
     }
 }
 
+// tokens[i] = last_token[token_slots[i]] where token_slots[i] >= 0: a row whose token is the one the sampling kernel chose
+// for its request in the step before, taken on the device (the host launched this step before it had read that token).
+__global__ void resolve_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ token_slots,
+                                      const int* __restrict__ last_token, int n, int num_slots) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int slot = token_slots[i];
+    if (slot >= 0 && slot < num_slots) tokens[i] = last_token[slot];
+}
+
+GB_EXPORT int gb_resolve_tokens(int* tokens, const int* token_slots, const int* last_token, int n, int num_slots,
+                                cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && tokens && token_slots && last_token && num_slots > 0, "gb_resolve_tokens: bad arguments");
+    if (n == 0) return 0;
+    resolve_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, token_slots, last_token, n, num_slots);
+    return gb_check_launch("gb_resolve_tokens");
+}
+
 // temperature / uniform: per-row arrays (or null: greedy). want_slots / state: per-row state slot (-1: use the arrays)
-// and the [num_slots, 4] sampling states (or null).
+// and the [num_slots, 4] sampling states (or null). last_token (or null): [num_slots], receives the chosen token of
+// every row that names a slot, so that the next step can take it from there without the host in between.
 GB_EXPORT int gb_sample(const float* logits, long long stride, const float* temperature, const float* uniform,
-                        const int* want_slots, void* state, int num_slots, int* out, int rows, int vocab,
+                        const int* want_slots, void* state, int num_slots, int* last_token, int* out, int rows, int vocab,
                         cudaStream_t stream) {
     GB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "gb_sample: bad sizes rows=%d vocab=%d", rows, vocab);
     GB_REQUIRE(temperature == nullptr || uniform != nullptr, "gb_sample: temperature sampling needs uniform draws");
     GB_REQUIRE(want_slots == nullptr || (state != nullptr && num_slots > 0), "gb_sample: state slots need the sampling states");
     if (rows == 0) return 0;
     sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, temperature, uniform, want_slots, (unsigned*)state,
-                                                        num_slots, out, vocab);
+                                                        num_slots, last_token, out, vocab);
     return gb_check_launch("gb_sample");
 }

@@ -115,6 +115,7 @@ class StepContext:
         self.num_seqs = 0
         self.decode_only = False          # every sequence of the step brings exactly one row
         self.leading_single = 0           # the first this many sequences bring one row each (rows 0 .. this - 1)
+        self.token_slots = None           # int32 [rows]: state slot of the rows whose token the device supplies itself, else -1
         self.want_slots = None            # int32 [wanted rows]: state slot of the rows that are sampled from their own state, else -1
         self.weight_order: Optional[WeightOrder] = None
         self.side_stream = None           # a second CUDA stream for work beside the main chain (prefetch)

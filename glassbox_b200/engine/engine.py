@@ -113,6 +113,11 @@ class Engine:
         self._sampled_host: Optional[torch.Tensor] = None
         self._ones = np.ones(self.max_graph_batch, dtype=np.int32)
         self._zeros = np.zeros(self.max_graph_batch, dtype=np.int32)
+        self._ones_u8 = np.ones(self.max_graph_batch, dtype=np.uint8)
+        # sampled tokens of launched decode steps land in pinned buffers that take turns (two steps may be in flight)
+        self._decode_out = [(torch.empty(self.max_graph_batch, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+                            for _ in range(3)]
+        self._decode_turn = 0
         self.h2d_bytes_last = 0
 
     # ---------------------------------------------------------------------------- requests
@@ -181,7 +186,8 @@ class Engine:
             self._layouts.clear()
         off, cur = {}, 0
         for name, size in (("tokens", n), ("positions", n), ("row_seq", n), ("want", n_want),
-                           ("seq_first_row", S + 1), ("seq_start_pos", S), ("seq_slots", S), ("want_slots", n_want)):
+                           ("seq_first_row", S + 1), ("seq_start_pos", S), ("seq_slots", S), ("want_slots", n_want),
+                           ("token_slots", n)):
             off[name] = cur
             cur += size
         for g in range(len(self.cache.groups)):
@@ -190,7 +196,8 @@ class Engine:
             off[f"tables{g}"] = cur
             cur += S * max_pages
         off["_size"] = cur
-        names = ["tokens", "positions", "row_seq", "want", "seq_first_row", "seq_start_pos", "seq_slots", "want_slots"] + \
+        names = ["tokens", "positions", "row_seq", "want", "seq_first_row", "seq_start_pos", "seq_slots", "want_slots",
+                 "token_slots"] + \
             [f"{kind}{g}" for g in range(len(self.cache.groups)) for kind in ("slots", "tables")]
         off["_array"] = np.array([off[k] for k in names], dtype=np.int64)   # the order the host library reads
         self._layouts[key] = off
@@ -232,6 +239,7 @@ class Engine:
         ctx.seq_start_pos = dev[off["seq_start_pos"]:off["seq_start_pos"] + S]
         ctx.seq_slots = dev[off["seq_slots"]:off["seq_slots"] + S]
         ctx.want_slots = dev[off["want_slots"]:off["want_slots"] + n_want]
+        ctx.token_slots = dev[off["token_slots"]:off["token_slots"] + n]
         ctx.group_slots = [dev[off[f"slots{g}"]:off[f"slots{g}"] + n] for g in range(n_groups)]
         ctx.group_tables = [dev[off[f"tables{g}"]:off[f"tables{g}"] + S * max_pages].view(S, max_pages)
                             for g in range(n_groups)]
@@ -358,7 +366,8 @@ class Engine:
                 logits = self.model.forward(ctx)
                 if sampling is not None and n_want:
                     self.sampled = self.scratch.get("sampled", (n_want, 1), torch.int32, grow=True).view(-1)
-                    kernels.sample(logits, self.sampled, want_slots=ctx.want_slots, state=self.device_cache.sampling)
+                    kernels.sample(logits, self.sampled, want_slots=ctx.want_slots, state=self.device_cache.sampling,
+                                   last_token=self.device_cache.last_token)
         if commit:
             self.cache.commit_many([e.request for e in entries], self._tok_count, self._tokens)
         self.steps += 1
@@ -414,14 +423,17 @@ class Engine:
         self.graph_replays += 1
         return g["logits"][:S]
 
-    def decode_fast(self, requests, tokens: np.ndarray, sample_mask: np.ndarray):
-        """The steady state of generation in as few host operations as it takes: every request of ``requests`` brings
-        the one token ``tokens[i]`` (int32) and wants its next token, sampled on the device (from the request's own
-        sampling state where ``sample_mask[i]`` is set, else greedily). One native call plans the step (room for one
-        token each, all or nothing), one fills the metadata block, one sends it, launches the step's recorded graph and
-        fetches the sampled tokens, one commits. Returns the sampled tokens (int32 numpy array, valid until the next
-        step), or None when this path does not take the step as it stands (no graphs, too many requests, a request at
-        ``max_position``, pages run out): nothing has changed then, and ``step`` does whatever has to be done."""
+    def decode_launch(self, requests, tokens: Optional[np.ndarray], sample_mask: np.ndarray):
+        """Launch the steady state of generation in as few host operations as it takes, and do not wait for it: every
+        request of ``requests`` brings one token and wants its next token, sampled on the device (from the request's own
+        sampling state where ``sample_mask[i]`` is set, else greedily). ``tokens`` (int32) are the tokens they bring;
+        None says that each request's token is the one the device sampled for it in the step before, which the host
+        need not have read yet: the step takes it from the device, and the cache learns the token values later
+        (``decode_commit_tokens``). One native call plans the step (room for one token each, all or nothing), one fills
+        the metadata block, one sends it, launches the step's recorded graph and fetches the sampled tokens.
+
+        Returns a handle for ``decode_wait``, or None when this path does not take the step as it stands (no graphs,
+        too many requests, a request at ``max_position``, pages run out): nothing has changed then."""
         n = len(requests)
         if not (self.use_graphs and 0 < n <= self.max_graph_batch and self.model.recordable(True)):
             return None
@@ -437,19 +449,38 @@ class Engine:
         g = self._decode_graph(Sb, Pb)
         ones, zeros = self._ones[:n], self._zeros[:n]
         host = self._stage_buffer(off["_size"])
-        self._stage_events[self._stage_next] = None      # this step ends with a synchronisation: the buffer is free after it
-        cache.fill_step(ids, ones, tokens, ones, zeros, Sb, Sb, Sb, Pb, off["_array"], host, sample_mask)
-        if self._sampled_host is None or self._sampled_host.numel() < n:
-            self._sampled_host = torch.empty(max(n, 64), dtype=torch.int32).pin_memory()
-        kernels.step_io(host.ctypes.data, g["meta"], off["_size"] * 4, g["exec"], g["sampled"], self._sampled_host, n,
-                        g["nodes"])
+        self._stage_events[self._stage_next] = None      # (every such step is waited for before the ring comes round)
+        fed = tokens is None
+        cache.fill_step(ids, ones, zeros if fed else tokens, ones, zeros, Sb, Sb, Sb, Pb, off["_array"], host, sample_mask,
+                        feedback_mask=self._ones_u8[:n] if fed else None)
+        turn = self._decode_turn = (self._decode_turn + 1) % len(self._decode_out)
+        out, event = self._decode_out[turn]
+        kernels.step_io(host.ctypes.data, g["meta"], off["_size"] * 4, g["exec"], g["sampled"], out, n, g["nodes"])
+        event.record()
         self.h2d_bytes_last = off["_size"] * 4
-        cache.commit_many(ids, ones, tokens)             # host bookkeeping, while the device works
+        if not fed:
+            cache.commit_many(ids, ones, tokens)         # host bookkeeping, while the device works
         self.graph_replays += 1
         self.steps += 1
         self.sampled = None
-        torch.cuda.current_stream().synchronize()
-        return self._sampled_host.numpy()[:n]
+        return {"ids": ids, "n": n, "out": out, "event": event, "fed": fed}
+
+    def decode_wait(self, handle) -> np.ndarray:
+        """The sampled tokens of a launched decode step (int32 numpy array, valid until two more steps are launched)."""
+        handle["event"].synchronize()
+        return handle["out"].numpy()[:handle["n"]]
+
+    def decode_commit_tokens(self, handle, tokens: np.ndarray) -> None:
+        """Tell the cache which tokens a launched step that took them from the device was given (the host knows them
+        now): one per request of the step, in its order."""
+        if handle["fed"]:
+            self.cache.commit_many(handle["ids"], self._ones[:handle["n"]], np.ascontiguousarray(tokens, dtype=np.int32))
+            handle["fed"] = False
+
+    def decode_fast(self, requests, tokens: np.ndarray, sample_mask: np.ndarray):
+        """``decode_launch`` and ``decode_wait`` in one: the sampled tokens, or None if the path declines the step."""
+        handle = self.decode_launch(requests, tokens, sample_mask)
+        return None if handle is None else self.decode_wait(handle)
 
     def _capture(self, key, off, host, n, S, n_want, Pb, max_rows, decode_only, lead=0):
         """Record the kernels of one step shape into a CUDA graph with a metadata block, logits and
@@ -473,8 +504,11 @@ class Engine:
         sampled = torch.zeros(max(n_want, 1), dtype=torch.int32, device=self.device)
 
         def run():
+            if decode_only and S == n:      # rows whose token is what the step before sampled take it on the device
+                kernels.resolve_tokens(ctx.tokens, ctx.token_slots, self.device_cache.last_token)
             logits = self.model.forward(ctx)
-            kernels.sample(logits, sampled[:n_want], want_slots=ctx.want_slots, state=self.device_cache.sampling)
+            kernels.sample(logits, sampled[:n_want], want_slots=ctx.want_slots, state=self.device_cache.sampling,
+                           last_token=self.device_cache.last_token)
             return logits
 
         side = torch.cuda.Stream()

@@ -115,6 +115,9 @@ class Scheduler:
         self.metrics = Metrics()
         self.finished: Dict[int, Finished] = {}
         self.trace: Optional[List[dict]] = [] if trace else None
+        #: launch the next pure decode step before the tokens of the running one are read (see ``_decode_step``)
+        self.lookahead = True
+        self._inflight = None
 
     # ------------------------------------------------------------------------------ requests
     def submit(self, req: Request) -> int:
@@ -132,11 +135,12 @@ class Scheduler:
         return sid
 
     def is_idle(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self._inflight is None
 
     def abort(self, sid: int) -> None:
         """Stop a request wherever it is; what it holds goes back to the pool
         (scheduler.rs:200-208)."""
+        self._drain()
         for i, s in enumerate(self.running):
             if s.id == sid:
                 del self.running[i]
@@ -156,6 +160,7 @@ class Scheduler:
         goes its own way. ``max_tokens`` counts the child's own new tokens (default: what the parent has left).
         The parent must be running or waiting; a child of a waiting parent simply waits behind it."""
         import copy
+        self._drain()
         parent = next((s for s in self.running if s.id == sid), None)
         waiting = next((s for s in self.waiting if s.id == sid), None) if parent is None else None
         src = parent or waiting
@@ -230,24 +235,54 @@ class Scheduler:
         return True
 
     # ---------------------------------------------------------------------------------- step
+    def _steady(self, seqs) -> bool:
+        """Whether a step of exactly these requests is the steady state: nobody waits who could be admitted, and each
+        brings one token that the device samples."""
+        cfg = self.config
+        if not seqs or len(seqs) > cfg.token_budget or (self.waiting and len(self.running) < cfg.max_seqs):
+            return False
+        return all(len(s.tokens) - s.computed == 1 and s.device_sampled and s.generated < s.req.max_tokens for s in seqs)
+
     def _decode_step(self, t0: float) -> bool:
         """The steady state: nobody can be admitted and every running request decodes one token that the device samples.
-        The backend plans, runs and commits such a step in a few native calls (``decode_fast``); what is left here is
-        to hand out the tokens. Returns False when the step is not of that kind (or the backend declines it: pages run
-        out, a request is at its limit): the general path then takes it, from the same state."""
-        run, cfg = self.running, self.config
-        fast = getattr(self.backend, "decode_fast", None)
-        if fast is None or not run or len(run) > cfg.token_budget or (self.waiting and len(run) < cfg.max_seqs):
+        The backend plans, runs and commits such a step in a few native calls, and the scheduler stays one step ahead of
+        the device: while step t runs, step t+1 is launched for the requests that will still be running, their tokens
+        taken on the device from what step t samples (who reaches ``max_tokens`` or ``max_position`` with step t is
+        known beforehand; requests with stop tokens are not run ahead, since whether they stop is not). Then the
+        tokens of step t are read and handed out. Returns False when the step is not of that kind (or the backend
+        declines it: pages run out): the general path then takes it, from the same state."""
+        launch = getattr(self.backend, "decode_launch", None)
+        if launch is None:
             return False
-        for s in run:
-            if len(s.tokens) - s.computed != 1 or not s.device_sampled or s.generated >= s.req.max_tokens:
+        if self._inflight is None:
+            run = list(self.running)
+            if not self._steady(run):
                 return False
-        n = len(run)
-        tokens = np.fromiter((s.tokens[-1] for s in run), dtype=np.int32, count=n)
-        mask = np.ones(n, dtype=np.uint8)
-        picked = fast([s.id for s in run], tokens, mask)
-        if picked is None:
-            return False
+            tokens = np.fromiter((s.tokens[-1] for s in run), dtype=np.int32, count=len(run))
+            handle = launch([s.id for s in run], tokens, np.ones(len(run), dtype=np.uint8))
+            if handle is None:
+                return False
+            self._inflight = (run, handle)
+        run, handle = self._inflight
+        limit = self.backend.max_position
+        ahead = None
+        if self.lookahead and not (self.waiting and len(self.running) < self.config.max_seqs) \
+                and not any(s.req.stop for s in run):
+            cont = [s for s in run if s.generated + 1 < s.req.max_tokens and len(s.tokens) + 1 < limit]
+            if cont:
+                h2 = launch([s.id for s in cont], None, np.ones(len(cont), dtype=np.uint8))
+                if h2 is not None:
+                    ahead = (cont, h2)
+        self._retire(run, handle, t0)
+        if ahead is not None:      # the cache learns which tokens the step that is now running was given
+            cont, h2 = ahead
+            self.backend.decode_commit_tokens(h2, np.fromiter((s.tokens[-1] for s in cont), dtype=np.int32, count=len(cont)))
+        self._inflight = ahead
+        return True
+
+    def _retire(self, run, handle, t0: float) -> None:
+        """Wait for a launched decode step and hand out its tokens."""
+        picked = self.backend.decode_wait(handle)
         now = time.perf_counter()
         limit = self.backend.max_position
         done, batch_desc = [], []
@@ -261,28 +296,35 @@ class Scheduler:
                 self.metrics.itl.append(now - s.last_token)
             s.last_token = now
             if t in s.req.stop:
-                done.append((i, STOP))
+                done.append((s, STOP))
                 continue
             s.tokens.append(t)
             if s.req.on_token:
                 s.req.on_token(s.id, t)
             if s.generated >= s.req.max_tokens or len(s.tokens) >= limit:
-                done.append((i, LENGTH))
+                done.append((s, LENGTH))
         finished = []
-        for i, reason in reversed(done):
-            s = run.pop(i)
+        for s, reason in done:
+            self.running.remove(s)
             finished.append(s.id)
             self._finish(s, reason)
         self.metrics.steps += 1
-        self.metrics.batch_tokens += n
+        self.metrics.batch_tokens += len(run)
         self._record(t0, batch_desc, [], finished)
-        return True
+
+    def _drain(self) -> None:
+        """Bring the host level with the device: a decode step that was launched ahead is waited for and handed out."""
+        if self._inflight is not None:
+            run, handle = self._inflight
+            self._inflight = None
+            self._retire(run, handle, time.perf_counter())
 
     def step(self) -> bool:
         """One batch through the model. Returns False when there was nothing to do."""
         t0 = time.perf_counter()
         if self._decode_step(t0):
             return True
+        self._drain()
         cfg, cache = self.config, self.backend.cache
         preempted: List[int] = []
         finished: List[int] = []

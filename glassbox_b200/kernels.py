@@ -40,7 +40,8 @@ _SIGNATURES = {
     "gb_copy_pages": [_P, _P, _P, _I, _LL, _LL, _I, _P],
     "gb_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _LL, _LL, _LL, _P],
     "gb_attention_rows": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
-    "gb_sample": [_P, _LL, _P, _P, _P, _P, _I, _P, _I, _I, _P],
+    "gb_sample": [_P, _LL, _P, _P, _P, _P, _I, _P, _P, _I, _I, _P],
+    "gb_resolve_tokens": [_P, _P, _P, _I, _I, _P],
     "gb_attention_decode": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                             _P, _P, _P],
     "gb_attention_decode_counters": [_I, _I, _I],
@@ -98,7 +99,7 @@ def lib():
                 fn.restype = ctypes.c_int
             handle.gb_set_pdl.argtypes = [ctypes.c_int]
             handle.gb_set_pdl.restype = None
-            handle.gb_set_pdl(int(os.environ.get("GLASSBOX_B200_PDL", "7")) if USE_PDL else 0)
+            handle.gb_set_pdl(7 if USE_PDL else 0)
             _lib = handle
     return _lib
 
@@ -425,15 +426,6 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
           *_prefetch_args(prefetch), 1 if USE_PDL else 0, _stream())
 
 
-def gemm_stream_tune(chunk: int = 0, split: int = 0) -> None:
-    """For measurements: force the weight-streaming kernel's k chunk (256, 512) and cluster size (1, 2, 4,
-    8); 0 gives the choice back to the kernel's own rule."""
-    handle = lib()
-    handle.gb_gemm_stream_tune.argtypes = [ctypes.c_int, ctypes.c_int]
-    handle.gb_gemm_stream_tune.restype = None
-    handle.gb_gemm_stream_tune(int(chunk), int(split))
-
-
 def gemm_stream_qkv_supported(a, w: torch.Tensor, hd: int, q_out: torch.Tensor) -> bool:
     return (gemm_stream_supported(a, w) and a.shape[0] <= STREAM_FUSE_MAX_ROWS and hd % 32 == 0
             and q_out.dtype == torch.bfloat16)
@@ -696,17 +688,26 @@ def kv_prefetch(kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            uniform: Optional[torch.Tensor] = None, want_slots: Optional[torch.Tensor] = None,
-           state: Optional[torch.Tensor] = None) -> None:
+           state: Optional[torch.Tensor] = None, last_token: Optional[torch.Tensor] = None) -> None:
     """out[r] = argmax(logits[r]) where the row's temperature is <= 0 (or none is given), else a draw from
     softmax(logits[r] / temperature) with a uniform number in [0, 1). Temperature and number come from
     ``temperature[r]`` and ``uniform[r]``, or, for rows with ``want_slots[r] >= 0``, from the request's sampling
     state ``state[want_slots[r]]`` (int32 [slots, 4]: generator state low and high word, temperature bits, unused),
-    whose xorshift64* generator the kernel advances by one draw."""
-    _cuda(logits, out, temperature, uniform, want_slots, state)
+    whose xorshift64* generator the kernel advances by one draw. ``last_token`` (int32 [slots]) receives the chosen
+    token of every row that names a slot (see ``resolve_tokens``)."""
+    _cuda(logits, out, temperature, uniform, want_slots, state, last_token)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
     if want_slots is not None:
         assert want_slots.dtype == torch.int32 and want_slots.numel() >= rows
         assert state is not None and state.dtype == torch.int32 and state.shape[1] == 4 and state.is_contiguous()
     _call("gb_sample", _ptr(logits), logits.stride(0), _ptr(temperature), _ptr(uniform), _ptr(want_slots), _ptr(state),
-          state.shape[0] if state is not None else 0, _ptr(out), rows, vocab, _stream())
+          state.shape[0] if state is not None else 0, _ptr(last_token), _ptr(out), rows, vocab, _stream())
+
+
+def resolve_tokens(tokens: torch.Tensor, token_slots: torch.Tensor, last_token: torch.Tensor) -> None:
+    """tokens[i] = last_token[token_slots[i]] where token_slots[i] >= 0 (in place): rows whose token is what the sampling
+    kernel chose for their request in the step before, which the host had not read yet when it launched this step."""
+    _cuda(tokens, token_slots, last_token)
+    assert tokens.dtype == token_slots.dtype == last_token.dtype == torch.int32 and token_slots.numel() >= tokens.numel()
+    _call("gb_resolve_tokens", _ptr(tokens), _ptr(token_slots), _ptr(last_token), tokens.numel(), last_token.numel(), _stream())

@@ -5,8 +5,12 @@ over operands that rotate through more memory than L2 holds.
     python -m glassbox_b200.microbench gemm_tc                           tcgen05 GEMM against torch.matmul
     python -m glassbox_b200.microbench attention_decode [batch ...]      paged decode attention at context 4096
     python -m glassbox_b200.microbench attention_prefill                 flash attention, one 2048-token prompt
+    python -m glassbox_b200.microbench float32                           the 32-bit path's kernels: FMA GEMM, decode and rows attention
+    python -m glassbox_b200.microbench small                             embedding, RMSNorm, rotation + cache write, SwiGLU, sampling
 
-Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops.
+Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops. With ``--once`` after
+the case's name every kernel is launched exactly once and nothing is timed: the form in which a profiler captures one
+launch of each kernel.
 """
 from __future__ import annotations
 
@@ -30,10 +34,15 @@ FAMILIES = {
 }
 
 
+ONCE = False
+
+
 def graph_time(fn, reps: int = 12, outer: int = 5) -> float:
     """Mean microseconds of one ``fn()`` among ``reps`` captured in a graph that is replayed ``outer`` times."""
     fn()
     torch.cuda.synchronize()
+    if ONCE:
+        return float("nan")
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
         for _ in range(reps):
@@ -145,8 +154,86 @@ def bench_attention_prefill() -> None:
     kernels.check_status(status)
 
 
+def bench_float32() -> None:
+    """The kernels of the true 32-bit path at SmolLM2-135M shapes: FMA products for a 2,048-token prompt and for 8
+    decoded rows, split-key decode attention and one-warp-per-row attention over a float32 cache."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for name, m, n, k in [("135m qkv, 2048 rows", 2048, 960, 576), ("135m gate/up, 2048 rows", 2048, 3072, 576),
+                          ("135m down, 2048 rows", 2048, 576, 1536), ("135m qkv, 8 rows", 8, 960, 576),
+                          ("135m head, 8 rows", 8, 49152, 576)]:
+        a, w, c = torch.randn(m, k, device=DEV), torch.randn(n, k, device=DEV), torch.empty(m, n, device=DEV)
+        t = graph_time(lambda: kernels.gemm_simt(a, w, c), reps=6)
+        print(f"gemm_simt {name:24s} {m} x {n} x {k}: {t:8.1f} us {2.0 * m * n * k / t / 1e6:6.2f} TFLOP/s "
+              f"{(m * k + n * k + m * n) * 4 / t / 1e3:6.0f} GB/s", flush=True)
+    nh, nkv, hd, ps, ctx = 9, 3, 64, 16, 4096
+    for m in (1, 8):
+        per = ctx // ps
+        kc = torch.randn(m * per + 4, nkv, ps, hd, device=DEV)
+        vc = torch.randn_like(kc)
+        tables = torch.arange(m * per, dtype=torch.int32, device=DEV).view(m, per).contiguous()
+        row_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+        pos = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
+        q = torch.randn(m, nh * hd, device=DEV)
+        o = torch.empty_like(q)
+        splits = kernels.decode_splits(m, nh, nkv, ctx)
+        pa, pm = torch.empty(m * nh * splits * hd, device=DEV), torch.empty(m * nh * splits * 2, device=DEV)
+        cn = torch.zeros(m * nh, dtype=torch.int32, device=DEV)
+        nbytes = m * ctx * nkv * hd * 4 * 2
+        t = graph_time(lambda: kernels.attention_decode(q, o, kc, vc, tables, row_seq, pos, nh, nkv, hd, ps, hd ** -0.5, None,
+                                                        splits, pa, pm, cn, status))
+        print(f"attention_decode (float32) batch {m} ctx {ctx} splits {splits}: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+        t = graph_time(lambda: kernels.attention_rows(q, o, kc, vc, tables, row_seq, pos, nh, nkv, hd, ps, hd ** -0.5, None, status))
+        print(f"attention_rows   (float32) batch {m} ctx {ctx}: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+    kernels.check_status(status)
+
+
+def bench_small() -> None:
+    """The element-wise kernels and the sampling kernel at SmolLM2-135M sizes, for a 2,048-token prompt and for 8 rows."""
+    from .parts.rope import rotary_table
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    d, inter, vocab, nh, nkv, hd, ps = 576, 1536, 49152, 9, 3, 64, 16
+    table = (torch.randn(vocab, d, device=DEV) * 0.02).bfloat16()
+    gain = torch.ones(d, device=DEV)
+    rope = rotary_table(100000.0, hd, 8192).to(DEV)
+    for n in (2048, 8):
+        tokens = torch.randint(0, vocab, (n,), dtype=torch.int32, device=DEV)
+        x = torch.empty(n, d, device=DEV)
+        h = torch.empty(n, d, device=DEV, dtype=torch.bfloat16)
+        t = graph_time(lambda: kernels.embed(table, tokens, x, status))
+        print(f"embed            {n:5d} rows x {d}: {t:6.1f} us {n * d * 6 / t / 1e3:6.0f} GB/s", flush=True)
+        t = graph_time(lambda: kernels.rmsnorm(x, gain, h, 1e-5))
+        print(f"rmsnorm          {n:5d} rows x {d}: {t:6.1f} us {n * d * 6 / t / 1e3:6.0f} GB/s", flush=True)
+        qkv = torch.randn(n, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+        kc = torch.zeros(n // ps + 2, nkv, ps, hd, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        pos = torch.arange(n, dtype=torch.int32, device=DEV)
+        t = graph_time(lambda: kernels.rope_kv_write(qkv, rope, pos, pos, kc, vc, nh, nkv, hd, hd, ps, True, status))
+        print(f"rope_kv_write    {n:5d} rows: {t:6.1f} us {n * (nh + 2 * nkv) * hd * 2 * 2 / t / 1e3:6.0f} GB/s", flush=True)
+        gu = torch.randn(n, 2 * inter, device=DEV).bfloat16()
+        act = torch.empty(n, inter, device=DEV, dtype=torch.bfloat16)
+        t = graph_time(lambda: kernels.swiglu(gu, act))
+        print(f"swiglu           {n:5d} rows x {inter}: {t:6.1f} us {n * inter * 6 / t / 1e3:6.0f} GB/s", flush=True)
+    for rows in (1, 8, 64):
+        logits = torch.randn(rows, vocab, device=DEV)
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        temp = torch.full((rows,), 0.8, device=DEV)
+        unif = torch.rand(rows, device=DEV)
+        t = graph_time(lambda: kernels.sample(logits, out))
+        t2 = graph_time(lambda: kernels.sample(logits, out, temp, unif))
+        print(f"sample           {rows:3d} rows x {vocab}: greedy {t:6.1f} us {rows * vocab * 4 / t / 1e3:6.0f} GB/s | temperature "
+              f"{t2:6.1f} us {rows * vocab * 4 * 3 / t2 / 1e3:6.0f} GB/s (three passes)", flush=True)
+    kernels.check_status(status)
+
+
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill", "float32", "small")
+
+
 def main(argv) -> int:
-    if not argv or argv[0] not in ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill"):
+    global ONCE
+    if "--once" in argv:
+        ONCE = True
+        argv = [a for a in argv if a != "--once"]
+    if not argv or argv[0] not in CASES:
         print(__doc__)
         return 2
     torch.cuda.set_device(0)
@@ -157,6 +244,10 @@ def main(argv) -> int:
         bench_gemm_tc()
     elif argv[0] == "attention_decode":
         bench_attention_decode([int(x) for x in argv[1:]])
+    elif argv[0] == "float32":
+        bench_float32()
+    elif argv[0] == "small":
+        bench_small()
     else:
         bench_attention_prefill()
     return 0

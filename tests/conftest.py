@@ -21,13 +21,15 @@ from glassbox_b200.models.llama import make_llama_raw_config  # noqa: E402
 FP32_ATOL = 1e-4
 # bf16: weights are identical (bf16 on disk); activations are rounded to 8 mantissa bits (2^-9
 # relative) after each of ~10 operations per layer, so the bound is relative to the spread of the
-# logits: worst element within 5 % of their standard deviation, mean error within 1 %. A model
+# logits: worst element within 5 % of their standard deviation, mean error within 0.8 %. (The largest seen over the
+# whole suite, printed at the end of a run: 3.8 % and 0.55 %, both at SmolLM2-1.7B widths, where K reaches 8,192; the tiny
+# models stay near 1.5 %.) A model
 # whose attention is sharpened (see ``sharpen``) is compared in float32 only: peaked softmax
 # amplifies bfloat16 rounding of the scores until the comparison with a float64 computation says
 # nothing. In bfloat16, faults that hide below this bound are caught by the crafted-model tests, in
 # which every score is either a large constant or zero, so that rounding cannot move the softmax.
 BF16_REL_MAX = 0.05
-BF16_REL_MEAN = 0.01
+BF16_REL_MEAN = 0.008
 
 TINY = {
     # GQA, tied head, power-of-two-free intermediate size
@@ -110,6 +112,17 @@ def sharp_dirs(model_dirs, tmp_path_factory):
     return get
 
 
+#: the largest bfloat16 errors seen in this session, as fractions of the logits' spread (printed at the end of the run)
+WORST_BF16 = {"max": 0.0, "mean": 0.0, "where": ""}
+
+
+def pytest_terminal_summary(terminalreporter):
+    if WORST_BF16["max"] > 0:
+        terminalreporter.write_line(f"bfloat16 logits: worst max error {WORST_BF16['max']:.4f} and worst mean error "
+                                    f"{WORST_BF16['mean']:.4f} of the spread (bounds {BF16_REL_MAX}, {BF16_REL_MEAN}); "
+                                    f"worst at: {WORST_BF16['where']}")
+
+
 def assert_logits_close(got, want, dtype, what=""):
     import numpy as np
     got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
@@ -120,6 +133,10 @@ def assert_logits_close(got, want, dtype, what=""):
         assert diff.max() <= FP32_ATOL, f"{what}: max abs diff {diff.max():.3e} > {FP32_ATOL} at {worst} (float32)"
     else:
         spread = want.std()
+        if spread > 0:
+            if diff.max() / spread > WORST_BF16["max"]:
+                WORST_BF16["max"], WORST_BF16["where"] = float(diff.max() / spread), what
+            WORST_BF16["mean"] = max(WORST_BF16["mean"], float(diff.mean() / spread))
         assert diff.max() <= BF16_REL_MAX * spread, \
             f"{what}: max abs diff {diff.max():.3e} > {BF16_REL_MAX} x spread {spread:.3e} at {worst} (bfloat16)"
         assert diff.mean() <= BF16_REL_MEAN * spread, \

@@ -245,12 +245,13 @@ def test_the_metadata_block_of_a_padded_step():
     for rid, n in (("a", 1), ("b", 1), ("c", 3)):
         m.reserve(rid, n)
     n, S, n_want, P = 12, 6, 8, 4
-    sizes = [n, n, n, n_want, S + 1, S, S, n_want, n, S * P]
+    sizes = [n, n, n, n_want, S + 1, S, S, n_want, n, n, S * P]
     off = np.concatenate(([0], np.cumsum(sizes)[:-1])).astype(np.int64)
     host = np.full(int(sum(sizes)), 77, dtype=np.int32)
     info, longest = m.fill_step(["a", "b", "c"], np.array([1, 1, 3], dtype=np.int32), np.array([5, 6, 7, 8, 9], dtype=np.int32),
                                 np.array([1, 1, 1], dtype=np.int32), np.array([0, 0, 2], dtype=np.int32), n, S, n_want, P, off,
-                                host, np.array([1, 0, 1], dtype=np.uint8), lead=2, pad_after=2)
+                                host, np.array([1, 0, 1], dtype=np.uint8), lead=2, pad_after=2,
+                                feedback_mask=np.array([0, 1, 1], dtype=np.uint8))
     sec = lambda i: host[off[i]:off[i] + sizes[i]]
     assert longest == 33 and info.tolist() == [[17, m.slot_of("a"), 0], [3, m.slot_of("b"), 1], [30, m.slot_of("c"), 4]]
     assert sec(0)[:7].tolist() == [5, 6, 0, 0, 7, 8, 9]                                   # tokens; padding rows hold 0
@@ -261,9 +262,11 @@ def test_the_metadata_block_of_a_padded_step():
     assert sec(3).tolist() == [0, 1, 6, 2, 3, 7, 0, 0]       # wanted: a, b, c's third row, then padding rows, then row 0
     ta, tc = m.table(0, "a"), m.table(0, "c")
     assert sec(7).tolist() == [m.slot_of("a"), -1, m.slot_of("c"), -1, -1, -1, -1, -1]     # who is sampled from its own state
-    assert sec(8).tolist() == [ta[1] * 16 + 1, m.table(0, "b")[0] * 16 + 3, -1, -1, tc[1] * 16 + 14, tc[1] * 16 + 15,
+    # whose token comes from the device: b's one row; c brings three tokens, so its flag does not apply
+    assert sec(8).tolist() == [-1, m.slot_of("b"), -1, -1, -1, -1, -1, -1, -1, -1, -1, -1]
+    assert sec(9).tolist() == [ta[1] * 16 + 1, m.table(0, "b")[0] * 16 + 3, -1, -1, tc[1] * 16 + 14, tc[1] * 16 + 15,
                                tc[2] * 16 + 0, -1, -1, -1, -1, -1]                         # cache slot of every row
-    tables = sec(9).reshape(S, P)
+    tables = sec(10).reshape(S, P)
     assert tables[0, :2].tolist() == ta and tables[4, :3].tolist() == tc and (tables[2:4] == -1).all() and (tables[5] == -1).all()
 
 

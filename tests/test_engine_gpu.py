@@ -134,7 +134,7 @@ class StepSpy:
         self.engine, self.rows = engine, []
         self.real_step = engine.step
         engine.step = self.step
-        engine.decode_fast = None      # (the scheduler's short cut for pure decode steps hands out tokens, not logits)
+        engine.decode_launch = None    # (the scheduler's short cut for pure decode steps hands out tokens, not logits)
 
     def step(self, entries, **kw):
         starts = [self.engine.cache.length(e.request) for e in entries]
@@ -325,3 +325,56 @@ def test_sampling_state_lives_in_the_slot_and_survives_preemption(model_dirs):
     alone = glassbox_b200.load(folder, "float32", blocks=64, budget=64, max_seqs=1)
     for i in (0, 3):
         assert alone.generate([prompts[i]], 16, temperature=0.8, seed=7 + i)[0] == want[i]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_one_step_ahead_of_the_device_changes_nothing(model_dirs, dtype):
+    """Pure decode steps are launched one ahead, their tokens taken on the device from what the step before sampled.
+    Requests of different lengths and limits (so that the batch shrinks as they end), one with a stop token (which is
+    not run ahead), temperature and greedy side by side, an abort and a fork in mid-flight: token for token what the
+    scheduler generates when it waits for every step."""
+    from glassbox_b200.engine.scheduler import Request, Scheduler, SchedulerConfig
+    from glassbox_b200.sampling import SamplerConfig
+    folder = model_dirs("B", dtype)
+    rng = random.Random(31)
+    prompts = [[rng.randrange(512) for _ in range(n)] for n in (5, 33, 17, 60, 9, 2)]
+    limits = [30, 7, 19, 25, 40, 12]
+
+    def run(lookahead, stop_for_last):
+        eng = make_engine(folder, dtype, cache_tokens=1024, max_requests=8)
+        s = Scheduler(eng, SchedulerConfig(token_budget=128, max_seqs=8))
+        s.lookahead = lookahead
+        ids = []
+        for i, (p, n) in enumerate(zip(prompts, limits)):
+            cfg = SamplerConfig(temperature=0.8 if i % 2 else 0.0, seed=50 + i)
+            ids.append(s.submit(Request(prompt=p, max_tokens=n, sampler=cfg, stop=stop_for_last if i == len(prompts) - 1 else ())))
+        steps, extra = 0, []
+        while not s.is_idle():
+            s.step()
+            steps += 1
+            if steps == 6:
+                s.abort(ids[3])
+                extra.append(s.fork(ids[4], max_tokens=5))
+        eng.check()
+        eng.cache.check_invariants()
+        assert eng.cache.free_pages() == eng.cache.num_pages() and len(eng.cache.free_slots) == eng.cache.max_requests
+        child = s.finished[extra[0]]
+        at = child.prompt_tokens - len(prompts[4])        # how far the parent was when it was forked
+        return ([s.finished[i].tokens for i in ids], [s.finished[i].reason for i in ids], child.tokens, at, eng.graph_replays)
+
+    plain_out, plain_why, plain_child, plain_at, _ = run(False, ())
+    ahead_out, ahead_why, ahead_child, ahead_at, replays = run(True, ())
+    assert replays > 20 and plain_why[3] == ahead_why[3] == "aborted"
+    for i in range(len(prompts)):
+        if i == 3:      # aborted in mid-flight: one mode is a step further when the abort arrives; what both have must agree
+            k = min(len(plain_out[3]), len(ahead_out[3]))
+            assert k > 0 and plain_out[3][:k] == ahead_out[3][:k]
+        else:
+            assert ahead_out[i] == plain_out[i] and ahead_why[i] == plain_why[i], f"request {i}"
+    # the forked twin (the parent's sampler state as it stood) generates what the parent goes on to generate, in either mode
+    assert plain_child == plain_out[4][plain_at:plain_at + 5] and ahead_child == ahead_out[4][ahead_at:ahead_at + 5]
+    stop_token = plain_out[5][3]                      # the last request stops at what was its fourth token
+    stopped_plain = run(False, (stop_token,))
+    stopped_ahead = run(True, (stop_token,))
+    assert stopped_ahead[0][5] == stopped_plain[0][5] and stopped_plain[1][5] == stopped_ahead[1][5] == "stop"
+    assert stopped_ahead[0][:3] == stopped_plain[0][:3]

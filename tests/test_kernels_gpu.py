@@ -683,6 +683,23 @@ def test_gemm_stream_qkv_with_norm_rotary_and_cache_write(M, nh, nkv, hd, d, ps,
     assert int(st) == 0
     live = positions >= 0
     t = tol(dtype, 2)
+    # a plain float64 statement of the whole operation: normalise, project, rotate the two halves of each head
+    xd, wd = x.cpu().double(), w.cpu().double()
+    hn = (gain.cpu().double() * (xd / torch.sqrt((xd * xd).mean(dim=1, keepdim=True) + 1e-6))).to(dtype).double()
+    ref = (hn @ wd.T).reshape(M, nh + 2 * nkv, hd)
+    if rotary:
+        cs = table.cpu().double()[positions.clamp(min=0).long()]            # [M, hd/2, 2]
+        c, sn = cs[:, None, :, 0], cs[:, None, :, 1]
+        rot = ref[:, :nh + nkv].clone()
+        a0, a1 = rot[..., :hd // 2].clone(), rot[..., hd // 2:].clone()
+        rot[..., :hd // 2], rot[..., hd // 2:] = a0 * c - a1 * sn, a1 * c + a0 * sn
+        ref[:, :nh + nkv] = rot
+    got_q = q2[:, :nh * hd].cpu().double().reshape(M, nh, hd)
+    assert (got_q[live] - ref[live, :nh]).abs().max() <= t, "queries against the float64 statement"
+    for r in torch.nonzero(live).flatten().tolist():
+        page, offs = int(slots[r]) // ps, int(slots[r]) % ps
+        assert (kc2[page, :, offs].cpu().double() - ref[r, nh:nh + nkv]).abs().max() <= t, "keys against the float64 statement"
+        assert (vc2[page, :, offs].cpu().double() - ref[r, nh + nkv:]).abs().max() <= t, "values against the float64 statement"
     assert (q2[live.to(DEV), :nh * hd].float() - qkv[live.to(DEV), :nh * hd].float()).abs().max() <= t
     assert (kc2.float() - kc.float()).abs().max() <= t and (vc2.float() - vc.float()).abs().max() <= t
     assert float(q2[~live.to(DEV)].abs().max() if (~live).any() else 0.0) == 0.0
