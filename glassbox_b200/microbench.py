@@ -7,6 +7,7 @@ over operands that rotate through more memory than L2 holds.
     python -m glassbox_b200.microbench attention_prefill                 flash attention, one 2048-token prompt
     python -m glassbox_b200.microbench float32                           the 32-bit path's kernels: FMA GEMM, decode and rows attention
     python -m glassbox_b200.microbench small                             embedding, RMSNorm, rotation + cache write, SwiGLU, sampling
+    python -m glassbox_b200.microbench decode_program [batch ...]        a decode step as a kernel chain and as a persistent kernel
 
 Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops. With ``--once`` after
 the case's name every kernel is launched exactly once and nothing is timed: the form in which a profiler captures one
@@ -225,7 +226,71 @@ def bench_small() -> None:
     kernels.check_status(status)
 
 
-CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill", "float32", "small")
+def bench_decode_program(batches) -> None:
+    """A decode step of SmolLM2-135M shapes at context 4096: as the chain of kernels in a CUDA graph, and as a decode
+    program run by the persistent kernel, shared by operations and by rows; for the programs also where the time goes
+    (clock values that the first block notes for each operation: its own share of the work including the wait for the
+    operation before, and the arrival at the barrier behind it), averaged over the layers."""
+    import shutil
+    import tempfile
+
+    import numpy as np
+
+    from . import write_random_model
+    from .engine.engine import Engine, StepEntry
+    from .models.llama import make_llama_raw_config
+    shape = dict(num_hidden_layers=30, hidden_size=576, num_attention_heads=9, num_key_value_heads=3, intermediate_size=1536,
+                 vocab_size=49152, rope_theta=100000.0, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=8192)
+    ctx_len, steps = 4096, 48
+    tmp = tempfile.mkdtemp(prefix="glassbox_b200_microbench_")
+    try:
+        write_random_model(tmp, make_llama_raw_config(**shape), 0, torch.bfloat16)
+        rng = np.random.default_rng(0)
+        for batch in batches or (1, 8):
+            for label, how in (("kernel chain", None), ("program, by operations", kernels.BY_OPERATIONS),
+                               ("program, by rows", kernels.BY_ROWS)):
+                kernels.PROGRAM_HOW = how if how is not None else kernels.BY_ROWS
+                eng = Engine(tmp, "bfloat16", cache_tokens=batch * (ctx_len + 64), max_batch_tokens=2048, max_requests=batch + 2,
+                             use_programs=how is not None)
+                for i in range(batch):
+                    eng.add_request(i)
+                    toks = rng.integers(0, shape["vocab_size"], size=ctx_len - steps - 8)
+                    for j in range(0, len(toks), 2048):
+                        eng.step([StepEntry(i, toks[j:j + 2048].tolist(), [])])
+                flags = [1] * batch
+
+                def one():
+                    eng.step([StepEntry(i, [5], [0]) for i in range(batch)], sampling=flags)
+                for _ in range(4):
+                    one()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(steps):
+                    one()
+                e1.record()
+                torch.cuda.synchronize()
+                line = f"135m batch {batch} context {ctx_len} {label:24s}: {e0.elapsed_time(e1) / steps:7.4f} ms per step"
+                if how is not None:     # one more step outside the graphs, traced
+                    eng.use_graphs = False
+                    eng.ctx.program.trace_next = True
+                    one()
+                    torch.cuda.synchronize()
+                    n, trace, _ = max(eng.ctx.program.traces, key=lambda t: t[0])
+                    t = trace.cpu().numpy().reshape(2, n, 4).astype(np.float64)[0] / 1965.0     # microseconds at 1,965 MHz
+                    k = (n // 5) * 5
+                    parts = []
+                    for j, name in enumerate(("qkv", "attention", "o", "gate/up", "down")):
+                        sel = t[j:k:5]
+                        parts.append(f"{name} {np.mean(sel[:, 2] - sel[:, 0]):.1f}+{np.mean((sel[:, 3] - sel[:, 2])[:-1]):.1f}")
+                    line += f" | per operation, us (work + arrival), {n} operations: " + ", ".join(parts)
+                print(line, flush=True)
+                del eng
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill", "float32", "small", "decode_program")
 
 
 def main(argv) -> int:
@@ -248,6 +313,8 @@ def main(argv) -> int:
         bench_float32()
     elif argv[0] == "small":
         bench_small()
+    elif argv[0] == "decode_program":
+        bench_decode_program([int(x) for x in argv[1:]])
     else:
         bench_attention_prefill()
     return 0
