@@ -31,9 +31,12 @@
 //    order (a fixed order: the result does not depend on timing) and runs the epilogue.
 #include "gemm_stream_body.cuh"
 
-// (the smallest variant is held to 128 registers, four blocks per SM: its choice of cluster size counts on that)
+// (The one-strip variant with wide chunks is held to 128 registers, four blocks per SM: its choice of cluster size
+// counts on that. The others leave the register count to the compiler: naming a minimum of one block per SM makes it
+// spend 20 to 80 registers more per thread, which costs the large matrices a resident block per SM and a fifth of
+// their bandwidth: 16384 x 2048 gated at one row 20.2 us against 14.2 us.)
 template <int NT, bool PAIR, int KC>
-__global__ void __launch_bounds__(128, (NT == 1 && !PAIR) ? 4 : 1) gemm_stream_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(128, (NT == 1 && !PAIR && KC == 512) ? 4 : 0) gemm_stream_kernel(const StreamArgs a) {
     __shared__ __align__(16) unsigned char xs[gemm_stream_smem_bytes<NT, KC>()];
     __shared__ float srow[NT * 8];
     GbPdlSync sync;

@@ -40,6 +40,23 @@ struct TcQkv {
     long long num_slots;
 };
 
+// An RMSNorm split between two products. The product that adds into the residual stream (the producer)
+// knows every new residual value x as it writes it: it also stores bfloat16(x * gain) and, per row and
+// column tile, the sum of x^2 over the tile's columns. The product that reads the normalised rows (the consumer)
+// takes the bfloat16 matrix as its A operand and multiplies each row of its float32 sums by
+// 1 / sqrt(sum x^2 / K + eps): a row's scale factors out of the product, so the result is that of
+// normalising first (crates/glassbox-core/src/kernels.rs:36-52) with the one bfloat16 rounding of the
+// activations in another place. The partial sums are added in column order: the same sums give the same bits.
+struct TcNorm {
+    const float* gain;        // producer: the gain of the norm that reads the residual next (nullptr: emit nothing)
+    __nv_bfloat16* pre;       // producer: [M, N] bfloat16, x * gain
+    long long ldp;
+    float* ss_out;            // producer: [M, column tiles] partial sums of squares
+    const float* ss_in;       // consumer: [M, ss_parts] (nullptr: rows are used as they are)
+    int ss_parts;
+    float eps;
+};
+
 constexpr int TC_MAX_STAGES = 8;
 
 struct __align__(8) TcShared {
@@ -76,7 +93,7 @@ template <int BN, bool GATED>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_w, void* __restrict__ C,
                                                            int mode, int M, int N, int K, long long ldc, int gate_rows,
-                                                           int* __restrict__ status, const TcQkv qkv) {
+                                                           int* __restrict__ status, const TcQkv qkv, const TcNorm norm) {
     using G = TcGeometry<BN, GATED>;
     constexpr int STAGES = G::STAGES, BNO = G::BNO;
     extern __shared__ unsigned char smem_dyn[];
@@ -176,12 +193,20 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BNO;
             const int acc = tcount & 1;
+            const int row = m0 + q * 32 + lane;
+            // consumer half of a split RMSNorm: this thread's row is scaled by 1 / rms of the residual row (read
+            // while the tile's products still run)
+            float inv_rms = 1.0f;
+            if (norm.ss_in != nullptr && row < M) {
+                float ss = 0.f;
+                for (int p = 0; p < norm.ss_parts; ++p) ss += norm.ss_in[(size_t)row * norm.ss_parts + p];
+                inv_rms = 1.0f / sqrtf(ss / (float)K + norm.eps);
+            }
             if (kblocks > 0) {
                 if (!mbar_wait_warp(&sh.tfull[acc], (tcount >> 1) & 1, abort_flag, status)) { ok = false; break; }
                 tc_fence_after();
             }
             const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            const int row = m0 + q * 32 + lane;
             if (!GATED && mode == TC_ROPE_QKV) {
                 // Stacked QKV (crates/glassbox-core/src/model.rs:266-276): a tile holds whole heads (BN is a multiple
                 // of the head size). Query and key heads are rotated, channel i with channel i + hd/2, from the
@@ -222,6 +247,13 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
                         uint32_t x0[32], x1[32];   // the warp-collective loads run for every row; the stores only for live ones
                         tmem_load32(t_base + (uint32_t)(h0 + c), x0);
                         tmem_load32(t_base + (uint32_t)(h0 + half + c), x1);
+                        if (norm.ss_in != nullptr) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                x0[j] = __float_as_uint(__uint_as_float(x0[j]) * inv_rms);
+                                x1[j] = __float_as_uint(__uint_as_float(x1[j]) * inv_rms);
+                            }
+                        }
                         if ((is_q || is_k) && have_cs) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 2) {
@@ -253,6 +285,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
                 if (lane == 0) mbar_arrive(&sh.tempty[acc]);
                 continue;
             }
+            float ssq = 0.f;   // producer half of a split RMSNorm: this thread's row's sum of squares over the tile's columns
 #pragma unroll 1
             for (int c0 = 0; c0 < BNO; c0 += 32) {
                 uint32_t r[32];
@@ -263,6 +296,10 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
                     for (int j = 0; j < 32; ++j) r[j] = 0u;
                 }
                 const int col0 = n0 + c0;
+                if (norm.ss_in != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * inv_rms);
+                }
                 if (GATED) {
                     uint32_t u[32];
                     if (kblocks > 0) {
@@ -274,7 +311,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float g = __uint_as_float(r[j]);
-                        r[j] = __float_as_uint(g / (1.0f + __expf(-g)) * __uint_as_float(u[j]));
+                        r[j] = __float_as_uint(g / (1.0f + __expf(-g)) * (__uint_as_float(u[j]) * inv_rms));
                     }
                 }
                 if (GATED || mode == TC_STORE_BF16) {
@@ -309,9 +346,19 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
                         float old[32];   // read the 32 residual values first (independent loads), then add and write
 #pragma unroll
                         for (int rr = 0; rr < 32; ++rr) old[rr] = rr < rows ? base[(size_t)rr * ldc] : 0.f;
+                        if (norm.gain != nullptr) {
+                            // producer half of a split RMSNorm: the new residual values go back into the tile as well
 #pragma unroll
-                        for (int rr = 0; rr < 32; ++rr)
-                            if (rr < rows) base[(size_t)rr * ldc] = old[rr] + stage[rr * 33 + lane];
+                            for (int rr = 0; rr < 32; ++rr) {
+                                const float v = old[rr] + stage[rr * 33 + lane];
+                                if (rr < rows) base[(size_t)rr * ldc] = v;
+                                stage[rr * 33 + lane] = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int rr = 0; rr < 32; ++rr)
+                                if (rr < rows) base[(size_t)rr * ldc] = old[rr] + stage[rr * 33 + lane];
+                        }
                     } else {
 #pragma unroll
                         for (int rr = 0; rr < 32; ++rr)
@@ -319,11 +366,54 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
                     }
                 }
                 __syncwarp();
+                if (mode == TC_ADD_F32 && norm.gain != nullptr) {
+                    // ... and come back row by row: this thread's row leaves as bfloat16(x * gain), 64 contiguous
+                    // bytes, and adds its squares to the row's sum (columns beyond N hold what the zero-filled
+                    // weight rows gave: nothing is stored or summed for them)
+                    __nv_bfloat16* dst = norm.pre + (size_t)row * norm.ldp + col0;
+                    uint32_t packed[16];
+                    if (col0 + 32 <= N) {
+                        const float4* g4 = reinterpret_cast<const float4*>(norm.gain + col0);   // 16-byte aligned (checked by the host)
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 g = g4[j >> 2];
+                            const float v0 = stage[lane * 33 + j], v1 = stage[lane * 33 + j + 1];
+                            const float v2 = stage[lane * 33 + j + 2], v3 = stage[lane * 33 + j + 3];
+                            ssq = fmaf(v0, v0, ssq); ssq = fmaf(v1, v1, ssq); ssq = fmaf(v2, v2, ssq); ssq = fmaf(v3, v3, ssq);
+                            packed[j >> 1] = pack2(__float_as_uint(v0 * g.x), __float_as_uint(v1 * g.y));
+                            packed[(j >> 1) + 1] = pack2(__float_as_uint(v2 * g.z), __float_as_uint(v3 * g.w));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const bool in0 = col0 + j < N, in1 = col0 + j + 1 < N;
+                            const float v0 = in0 ? stage[lane * 33 + j] : 0.f, v1 = in1 ? stage[lane * 33 + j + 1] : 0.f;
+                            const float g0 = in0 ? norm.gain[col0 + j] : 0.f, g1 = in1 ? norm.gain[col0 + j + 1] : 0.f;
+                            ssq = fmaf(v0, v0, ssq);
+                            ssq = fmaf(v1, v1, ssq);
+                            packed[j >> 1] = pack2(__float_as_uint(v0 * g0), __float_as_uint(v1 * g1));
+                        }
+                    }
+                    if (row < M) {
+                        if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) dst[j] = __ushort_as_bfloat16((unsigned short)(packed[j >> 1] >> ((j & 1) * 16)));
+                        }
+                    }
+                    __syncwarp();
+                }
             }
             // this warp is done with the accumulator: hand it back to the MMA issuer
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.tempty[acc]);
+            if (!GATED && mode == TC_ADD_F32 && norm.gain != nullptr && row < M)
+                norm.ss_out[(size_t)row * tiles_n + (tile / tiles_m)] = ssq;
         }
     }
 
@@ -351,7 +441,8 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 
 template <int BN, bool GATED>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int mode, int M, int N, int K,
-                     long long ldc, int gate_rows, int* status, cudaStream_t stream, const TcQkv& qkv = TcQkv()) {
+                     long long ldc, int gate_rows, int* status, cudaStream_t stream, const TcQkv& qkv = TcQkv(),
+                     const TcNorm& norm = TcNorm()) {
     using G = TcGeometry<BN, GATED>;
     auto kernel = gemm_tcgen05_kernel<BN, GATED>;
     static bool configured = false;
@@ -369,7 +460,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int 
     }
     const int ntiles = gb_ceil_div(M, TC_BM) * gb_ceil_div(N, G::BNO);
     const int grid = ntiles < sms ? ntiles : sms;   // persistent: one block per SM walks the tiles
-    cudaError_t e = gb_launch(GB_PDL_GEMM, kernel, dim3(grid), dim3(192), G::SMEM, stream, ma, mw, c, mode, M, N, K, ldc, gate_rows, status, qkv);
+    cudaError_t e = gb_launch(GB_PDL_GEMM, kernel, dim3(grid), dim3(192), G::SMEM, stream, ma, mw, c, mode, M, N, K, ldc, gate_rows, status, qkv, norm);
     GB_REQUIRE(e == cudaSuccess, "gb_gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return gb_check_launch("gb_gemm_tcgen05");
 }
@@ -382,47 +473,92 @@ GB_EXPORT int gb_gemm_tcgen05_supported(const void* a, const void* w, int M, int
            (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0;
 }
 
-// Output tile width: the widest tile that still gives every SM a tile (wide tiles reuse the A operand
-// more and amortise the epilogue; narrow ones keep small problems spread over the GPU).
-static int pick_bn(int M, int N) {
-    const long long tm = gb_ceil_div(M, TC_BM);
-    if (tm * gb_ceil_div(N, 256) >= 120) return 256;
-    if (tm * gb_ceil_div(N, 128) >= 120) return 128;
-    return 64;
+static int tc_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
 }
 
+// Output tile width. A block's time for one tile is about 0.33 us per 64-wide k-block, whatever the width (at these
+// sizes the operands come from L2 at a rate that the tile count, not the tile size, sets), plus an epilogue that
+// grows with the width and with what it does; a launch takes as many rounds of tiles as its busiest block has.
+// The width with the smallest estimate wins; ties go to the wider tile, which reads the A operand less often.
+// Measured at 2048 rows on a B200, microseconds for widths 64 / 128 / 256: N 960, K 576 store 9.5 / 7.3 / 8.7;
+// N 576, K 1536 add 13.1 / 15.6 / 19.9; N 1600, K 960 store 18.9 / 15.1 / 11.4; N 960, K 2560 add 30.3 / 21.4 / 25.1;
+// gated, I 1536, K 576: 20.0 (128) / 22.3 (256); I 8192, K 2048: 153 / 107.
+enum { TC_EPI_STORE = 0, TC_EPI_ADD = 1, TC_EPI_GATED = 2 };
+static int pick_bn(int M, int N, int K, int epilogue, int narrowest = 64) {
+    static const float epi_us[3][3] = {{1.5f, 2.5f, 4.5f}, {2.8f, 5.5f, 11.0f}, {0.f, 3.0f, 7.0f}};
+    const long long tm = gb_ceil_div(M, TC_BM);
+    const float main_us = 0.33f * (float)gb_ceil_div(K, TC_BK);
+    int best = 0;
+    float best_us = 0.f;
+    for (int i = 0, bn = 64; bn <= 256; ++i, bn *= 2) {
+        if (bn < narrowest) continue;
+        const int out_cols = epilogue == TC_EPI_GATED ? bn / 2 : bn;
+        const long long rounds = gb_ceil_div(tm * gb_ceil_div(N, out_cols), (long long)tc_sm_count());
+        const float us = (float)rounds * (main_us + epi_us[epilogue][i]);
+        if (best == 0 || us <= best_us) { best = bn; best_us = us; }
+    }
+    return best;
+}
+
+// Column tiles of gb_gemm_tcgen05's output for this shape: the second extent of the partial sums of squares
+// that a producer of a split RMSNorm writes.
+GB_EXPORT int gb_gemm_tcgen05_column_tiles(int M, int N, int K) { return gb_ceil_div(N, pick_bn(M, N, K, TC_EPI_ADD)); }
+
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32.
+// Split RMSNorm (see TcNorm): with mode 2 and norm_gain != nullptr the launch also writes pre[M, N] =
+// bfloat16(c * norm_gain) and ss_out[M, gb_gemm_tcgen05_column_tiles(M, N, K)]; with ss_in != nullptr the rows of
+// the product are scaled by 1 / sqrt(sum_p ss_in[row, p] / K + eps) before they are stored or added.
 GB_EXPORT int gb_gemm_tcgen05(const void* a, const void* w, void* c, int mode, int M, int N, int K, long long lda,
-                              long long ldw, long long ldc, int* status, cudaStream_t stream) {
+                              long long ldw, long long ldc, int* status, cudaStream_t stream, const float* norm_gain,
+                              void* pre, long long ldp, float* ss_out, const float* ss_in, int ss_parts, float eps) {
     GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, N, K, lda, ldw),
                "gb_gemm_tcgen05: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d N=%d K=%d)",
                M, N, K);
     GB_REQUIRE(mode >= 0 && mode <= 2 && ldc >= N && status != nullptr, "gb_gemm_tcgen05: bad mode, ldc or status");
-    const int bn = pick_bn(M, N);
+    GB_REQUIRE(norm_gain == nullptr || (mode == TC_ADD_F32 && pre != nullptr && ss_out != nullptr && ldp >= N &&
+                                        (uintptr_t)norm_gain % 16 == 0),
+               "gb_gemm_tcgen05: a norm is prepared only by a product that adds into float32, into pre and ss_out");
+    GB_REQUIRE(ss_in == nullptr || ss_parts > 0, "gb_gemm_tcgen05: ss_parts must be positive");
+    const int bn = pick_bn(M, N, K, mode == TC_ADD_F32 ? TC_EPI_ADD : TC_EPI_STORE);
     CUtensorMap ma, mw;
     if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
     if (make_map(&mw, w, N, K, ldw, bn)) return 1;
-    if (bn == 256) return launch_tc<256, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream);
-    if (bn == 128) return launch_tc<128, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream);
-    return launch_tc<64, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream);
+    TcNorm norm = {};
+    norm.gain = norm_gain; norm.pre = (__nv_bfloat16*)pre; norm.ldp = ldp; norm.ss_out = ss_out;
+    norm.ss_in = ss_in; norm.ss_parts = ss_parts; norm.eps = eps;
+    if (bn == 256) return launch_tc<256, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream, TcQkv(), norm);
+    if (bn == 128) return launch_tc<128, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream, TcQkv(), norm);
+    return launch_tc<64, false>(ma, mw, c, mode, M, N, K, ldc, 0, status, stream, TcQkv(), norm);
 }
 
 // Gated feed-forward input product: w = [gate rows; up rows] (2*inter rows), c bfloat16 [M, inter] =
 // silu(a gate^T) * (a up^T). inter must be a multiple of 8 (TMA row addressing needs nothing more).
+// ss_in != nullptr: a is the bfloat16(x * gain) of a split RMSNorm and the sums are scaled row by row (see TcNorm).
 GB_EXPORT int gb_gemm_tcgen05_gated(const void* a, const void* w, void* c, int M, int inter, int K, long long lda,
-                                    long long ldw, long long ldc, int* status, cudaStream_t stream) {
+                                    long long ldw, long long ldc, int* status, cudaStream_t stream, const float* ss_in,
+                                    int ss_parts, float eps) {
     GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, 2 * inter, K, lda, ldw),
                "gb_gemm_tcgen05_gated: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d I=%d K=%d)",
                M, inter, K);
     GB_REQUIRE(ldc >= inter && status != nullptr, "gb_gemm_tcgen05_gated: bad ldc or status");
     CUtensorMap ma, mw;
     if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
-    const bool wide = (long long)gb_ceil_div(M, TC_BM) * gb_ceil_div(inter, 128) >= 120;
+    const bool wide = pick_bn(M, inter, K, TC_EPI_GATED, 128) == 256;
     // the weight map covers only the rows that exist, so a box that runs past the gate rows of the last
     // tile reads up rows: those columns are >= inter and are never stored
     if (make_map(&mw, w, 2LL * inter, K, ldw, wide ? 128 : 64)) return 1;
-    return wide ? launch_tc<256, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream)
-                : launch_tc<128, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream);
+    GB_REQUIRE(ss_in == nullptr || ss_parts > 0, "gb_gemm_tcgen05_gated: ss_parts must be positive");
+    TcNorm norm = {};
+    norm.ss_in = ss_in; norm.ss_parts = ss_parts; norm.eps = eps;
+    return wide ? launch_tc<256, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream, TcQkv(), norm)
+                : launch_tc<128, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream, TcQkv(), norm);
 }
 
 // 1 if gb_gemm_tcgen05_qkv takes this head size: whole heads must tile the 128 columns of an output tile and half
@@ -435,7 +571,8 @@ GB_EXPORT int gb_gemm_tcgen05_qkv_supported(int hd) { return hd == 64 || hd == 1
 GB_EXPORT int gb_gemm_tcgen05_qkv(const void* a, const void* w, void* q_out, int M, int K, long long lda, long long ldw,
                                   long long ldq, const float* rope, int max_pos, const int* positions, const int* slots,
                                   void* kcache, void* vcache, int nh, int nkv, int hd, int page_size, long long num_pages,
-                                  int write_kv, int* status, cudaStream_t stream) {
+                                  int write_kv, int* status, cudaStream_t stream, const float* ss_in, int ss_parts,
+                                  float eps) {
     const int N = (nh + 2 * nkv) * hd;
     GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, N, K, lda, ldw),
                "gb_gemm_tcgen05_qkv: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d N=%d K=%d)",
@@ -447,13 +584,16 @@ GB_EXPORT int gb_gemm_tcgen05_qkv(const void* a, const void* w, void* q_out, int
     GB_REQUIRE(page_size > 0 && positions && slots && status, "gb_gemm_tcgen05_qkv: bad arguments");
     CUtensorMap ma, mw;
     if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
-    const int bn = pick_bn(M, N) == 256 ? 256 : 128;   // whole heads per tile
+    const int bn = pick_bn(M, N, K, TC_EPI_STORE, 128);   // whole heads per tile
     if (make_map(&mw, w, N, K, ldw, bn)) return 1;
     TcQkv q = {};
     q.rope = (const float2*)rope; q.positions = positions; q.slots = slots;
     q.kcache = (__nv_bfloat16*)kcache; q.vcache = (__nv_bfloat16*)vcache;
     q.nh = nh; q.nkv = nkv; q.hd = hd; q.page_size = page_size; q.max_pos = max_pos; q.write_kv = write_kv;
     q.num_slots = num_pages * page_size;
-    if (bn == 256) return launch_tc<256, false>(ma, mw, q_out, TC_ROPE_QKV, M, N, K, ldq, 0, status, stream, q);
-    return launch_tc<128, false>(ma, mw, q_out, TC_ROPE_QKV, M, N, K, ldq, 0, status, stream, q);
+    GB_REQUIRE(ss_in == nullptr || ss_parts > 0, "gb_gemm_tcgen05_qkv: ss_parts must be positive");
+    TcNorm norm = {};
+    norm.ss_in = ss_in; norm.ss_parts = ss_parts; norm.eps = eps;
+    if (bn == 256) return launch_tc<256, false>(ma, mw, q_out, TC_ROPE_QKV, M, N, K, ldq, 0, status, stream, q, norm);
+    return launch_tc<128, false>(ma, mw, q_out, TC_ROPE_QKV, M, N, K, ldq, 0, status, stream, q, norm);
 }

@@ -120,6 +120,11 @@ class StepContext:
         self.weight_order: Optional[WeightOrder] = None
         self.side_stream = None           # a second CUDA stream for work beside the main chain (prefetch)
         self.program = None               # a kernels.Program: decode steps of few rows run as one persistent kernel
+        # An RMSNorm may be split between the product that completes the residual rows and the product that reads
+        # the normalised rows (parts/linear.py). Whoever wires the parts says which norm comes next:
+        self.next_norm = None             # the norm that will read the residual after the product that adds into it next
+        self.norm_after_layer = None      # the norm that will read the residual after the layer that runs now
+        self.prepared_norm = None         # parts.base.PreparedNorm: what the last such product left for that norm
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)

@@ -116,6 +116,7 @@ class DecoderModel:
 
     def _forward(self, ctx, x, in_program: bool) -> torch.Tensor:
         n, d = ctx.n, self.config.hidden_size
+        ctx.next_norm = ctx.norm_after_layer = ctx.prepared_norm = None
         self.embed.forward(ctx, ctx.tokens, x)
         schedule = self.config.schedule
         # (a program's persistent kernel asks for the next layer's keys and values itself)
@@ -136,11 +137,15 @@ class DecoderModel:
             if pending:
                 torch.cuda.current_stream().wait_stream(side)   # the prefetch kernel must not outlive the step
                 pending = False
+            # which norm reads x after this layer: the next layer's first one, if it says which that is
+            entry = getattr(self.layers[schedule[i + 1].layer], "entry_norm", None) if i + 1 < len(schedule) else None
+            ctx.norm_after_layer = entry() if entry is not None else None
             self.layers[run.layer].forward(ctx, x, ctx.cache_view(run.cache), run.writes_cache, after_mixer=hook) \
                 if hook is not None else self.layers[run.layer].forward(ctx, x, ctx.cache_view(run.cache), run.writes_cache)
             pending = hook is not None
         if pending:
             torch.cuda.current_stream().wait_stream(side)
+        ctx.norm_after_layer = None
         w = ctx.num_wanted
         logits = ctx.scratch("logits", (w, self.config.vocab_size), torch.float32, grow=True)
         if w:

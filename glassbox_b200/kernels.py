@@ -56,13 +56,15 @@ _SIGNATURES = {
     "gb_kv_prefetch": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _LL, _LL, _I, _I, _P],
     "gb_attention_prefill": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_attention_prefill_supported": [_I, _I, _I, _I],
-    "gb_gemm_tcgen05_qkv": [_P, _P, _P, _I, _I, _LL, _LL, _LL, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _I, _P, _P],
+    "gb_gemm_tcgen05_qkv": [_P, _P, _P, _I, _I, _LL, _LL, _LL, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _I, _P, _P,
+                            _P, _I, _F],
     "gb_gemm_tcgen05_qkv_supported": [_I],
     "gb_attention_prefill_tc": [_P, _LL, _I, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_attention_prefill_tc_supported": [_I, _I, _I, _I],
-    "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P],
+    "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P, _P, _P, _LL, _P, _P, _I, _F],
+    "gb_gemm_tcgen05_column_tiles": [_I, _I, _I],
     "gb_gemm_tcgen05_supported": [_P, _P, _I, _I, _I, _LL, _LL],
-    "gb_gemm_tcgen05_gated": [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P],
+    "gb_gemm_tcgen05_gated": [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P, _P, _I, _F],
     "gb_program_encode_gemm": [_P, _P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _I],
     "gb_program_encode_gemm_qkv": [_P, _P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I,
                                    _I, _LL, _I, _P],
@@ -469,14 +471,51 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool
 _tc_status = {}
 
 
+class RowScale:
+    """The consumer half of an RMSNorm split between two tile-kernel products: ``ss`` float32 [M, parts] holds partial
+    sums of squares of the residual rows, and each row of the product is multiplied by
+    1 / sqrt(sum(ss[row]) / K + eps). The product's ``a`` operand is then bfloat16(residual * gain)."""
+    __slots__ = ("ss", "eps")
+
+    def __init__(self, ss: torch.Tensor, eps: float):
+        assert ss.dtype == torch.float32 and ss.dim() == 2 and ss.is_contiguous()
+        self.ss, self.eps = ss, float(eps)
+
+    def args(self, rows: int):
+        assert self.ss.shape[0] == rows
+        return _ptr(self.ss), self.ss.shape[1], self.eps
+
+
+_NO_SCALE = (None, 0, 0.0)
+
+
+def gemm_tc_column_tiles(rows: int, n: int, k: int) -> int:
+    """Column tiles of the output of a ``gemm_tc`` that adds [rows, k] x [n, k]^T into float32: the second extent of
+    the partial sums of squares that a product with ``prepare`` writes."""
+    return int(lib().gb_gemm_tcgen05_column_tiles(rows, n, k))
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False,
-            status: Optional[torch.Tensor] = None) -> None:
+            status: Optional[torch.Tensor] = None, prepare=None, row_scale: Optional[RowScale] = None) -> None:
     """c[M, N] (+)= a[M, K] @ w[N, K]^T with TMA + tcgen05.mma + TMEM. ``status`` receives the
-    wait-timeout bit if a bounded wait inside the kernel ever gives up."""
+    wait-timeout bit if a bounded wait inside the kernel ever gives up.
+
+    ``prepare=(gain, pre, ss)`` (only with ``accumulate``) makes the epilogue the producer half of an RMSNorm of the
+    rows it has just completed: ``pre`` bfloat16 [M, N] receives c * gain and ``ss`` float32
+    [M, gemm_tc_column_tiles(M, N, K)] the partial sums of squares; a later product takes ``pre`` as its ``a`` with
+    ``row_scale=RowScale(ss, eps)``."""
     _cuda(a, w, c, status)
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    prep = (None, None, 0, None)
+    if prepare is not None:
+        gain, pre, ss = prepare
+        _cuda(gain, pre, ss)
+        assert accumulate and gain.dtype == torch.float32 and gain.numel() == N and gain.is_contiguous()
+        assert pre.dtype == torch.bfloat16 and pre.shape == (M, N) and pre.stride(1) == 1
+        assert ss.dtype == torch.float32 and ss.is_contiguous() and ss.shape == (M, gemm_tc_column_tiles(M, N, K))
+        prep = (_ptr(gain), _ptr(pre), pre.stride(0), _ptr(ss))
     if status is None:
         status = _tc_status.get(a.device)
         if status is None:
@@ -487,7 +526,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool 
     else:
         mode = 0 if c.dtype == torch.bfloat16 else 1
     _call("gb_gemm_tcgen05", _ptr(a), _ptr(w), _ptr(c), mode, M, N, K, a.stride(0), w.stride(0), c.stride(0),
-          _ptr(status), _stream())
+          _ptr(status), _stream(), *prep, *(row_scale.args(M) if row_scale is not None else _NO_SCALE))
 
 
 def gemm_tc_qkv_supported(a: torch.Tensor, w: torch.Tensor, hd: int, q_out: torch.Tensor, kcache: torch.Tensor) -> bool:
@@ -498,10 +537,10 @@ def gemm_tc_qkv_supported(a: torch.Tensor, w: torch.Tensor, hd: int, q_out: torc
 
 def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[torch.Tensor],
                 positions: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nh: int, nkv: int,
-                hd: int, page_size: int, write_kv: bool, status: torch.Tensor) -> None:
+                hd: int, page_size: int, write_kv: bool, status: torch.Tensor, row_scale: Optional[RowScale] = None) -> None:
     """Stacked QKV projection on the tcgen05 kernel with the rotation and the cache write in its epilogue:
     q_out[:, :nh*hd] receives the rotated queries, the cache slots of the rows the rotated keys and the
-    values. ``cos_sin`` is float32 [max_pos, hd/2, 2] or None (no rotation)."""
+    values. ``cos_sin`` is float32 [max_pos, hd/2, 2] or None (no rotation). ``row_scale``: see ``RowScale``."""
     _cuda(a, w, q_out, cos_sin, positions, slots, kcache, vcache, status)
     M, K = a.shape
     assert w.shape == ((nh + 2 * nkv) * hd, K) and a.stride(1) == 1 and w.stride(1) == 1 and q_out.stride(1) == 1
@@ -509,13 +548,14 @@ def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_sin: 
     assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape[1:] == (hd // 2, 2) and cos_sin.is_contiguous())
     _call("gb_gemm_tcgen05_qkv", _ptr(a), _ptr(w), _ptr(q_out), M, K, a.stride(0), w.stride(0), q_out.stride(0),
           _ptr(cos_sin), cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slots), _ptr(kcache),
-          _ptr(vcache), nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status), _stream())
+          _ptr(vcache), nh, nkv, hd, page_size, kcache.shape[0], 1 if write_kv else 0, _ptr(status), _stream(),
+          *(row_scale.args(M) if row_scale is not None else _NO_SCALE))
 
 
 def gemm_tc_gated(a: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor,
-                  status: Optional[torch.Tensor] = None) -> None:
+                  status: Optional[torch.Tensor] = None, row_scale: Optional[RowScale] = None) -> None:
     """act[M, I] = silu(a gate^T) * (a up^T) with w_gate_up = [gate rows; up rows], on the tcgen05
-    kernel: gate and up columns of a tile sit side by side in one TMEM accumulator."""
+    kernel: gate and up columns of a tile sit side by side in one TMEM accumulator. ``row_scale``: see ``RowScale``."""
     _cuda(a, w_gate_up, act, status)
     M, K = a.shape
     inter = w_gate_up.shape[0] // 2
@@ -526,7 +566,7 @@ def gemm_tc_gated(a: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor,
         if status is None:
             status = _tc_status[a.device] = torch.zeros(1, dtype=torch.int32, device=a.device)
     _call("gb_gemm_tcgen05_gated", _ptr(a), _ptr(w_gate_up), _ptr(act), M, inter, K, a.stride(0), w_gate_up.stride(0),
-          act.stride(0), _ptr(status), _stream())
+          act.stride(0), _ptr(status), _stream(), *(row_scale.args(M) if row_scale is not None else _NO_SCALE))
 
 
 def attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,

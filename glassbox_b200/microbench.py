@@ -96,7 +96,9 @@ def bench_gemm_stream(families) -> None:
 
 def bench_gemm_tc() -> None:
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for name, m, n, k in [("135m qkv", 2048, 960, 576), ("135m o", 2048, 576, 576), ("135m down", 2048, 576, 1536),
+    for name, m, n, k in [("135m qkv", 2048, 960, 576), ("135m o", 2048, 576, 576), ("135m gate_up", 2048, 3072, 576),
+                          ("135m down", 2048, 576, 1536), ("360m qkv", 2048, 1600, 960), ("360m o", 2048, 960, 960),
+                          ("360m gate_up", 2048, 5120, 960), ("360m down", 2048, 960, 2560),
                           ("1.7b qkv", 2048, 6144, 2048), ("1.7b gate_up", 2048, 16384, 2048),
                           ("1.7b down", 2048, 2048, 8192), ("square", 8192, 8192, 8192)]:
         a = torch.randn(m, k, device=DEV).bfloat16()

@@ -50,7 +50,7 @@ class GqaAttention(Mixer):
         n = h.shape[0]
         qkv = ctx.scratch("qkv", (n, self.qd + 2 * self.kvd))
         table = self.position.fused_table(qkv.device)
-        x, norm, _ = _resolve(h)
+        x, norm, _, scale = _resolve(h)
         plain_rotary = (table is not None and self.position.rotary_dim == self.hd) or \
             (table is None and type(self.position).apply_qk is Position.apply_qk)
         if (plain_rotary and (norm is not None or x.dtype == torch.bfloat16)
@@ -62,8 +62,9 @@ class GqaAttention(Mixer):
         elif (plain_rotary and norm is None and n > kernels.STREAM_MAX_ROWS
               and kernels.gemm_tc_qkv_supported(x, self.params["wqkv"], self.hd, qkv, cache.k)):
             # many rows: the tile kernel projects; its epilogue rotates from the float32 sums and writes the cache
+            # (and completes the norm, if the product before this layer prepared it)
             kernels.gemm_tc_qkv(x, self.params["wqkv"], qkv, table, ctx.positions, cache.slots, cache.k, cache.v,
-                                self.nh, self.nkv, self.hd, cache.page_size, writes_cache, ctx.status)
+                                self.nh, self.nkv, self.hd, cache.page_size, writes_cache, ctx.status, row_scale=scale)
         else:
             linear(ctx, h, self.params["wqkv"], qkv)
             if table is None:

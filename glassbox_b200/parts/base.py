@@ -94,16 +94,41 @@ class Norm(Part):
         return None
 
 
+class PreparedNorm:
+    """What the product that last added into the residual ``x`` left behind for the norm that reads ``x`` next
+    (``ctx.next_norm``, a hint from whoever wires the parts): ``pre`` = bfloat16(x * gain) and the scale that
+    completes the norm in the epilogue of the product that consumes it. Valid only while ``x`` is what that
+    product wrote: same storage, same version counter (every torch operation in place raises it), and no
+    ``linear(..., accumulate=True)`` into it since (which replaces or clears this record)."""
+    __slots__ = ("norm", "x_ptr", "version", "rows", "pre", "scale")
+
+    def __init__(self, norm, x: torch.Tensor, pre: torch.Tensor, scale):
+        self.norm, self.x_ptr, self.version, self.rows = norm, x.data_ptr(), x._version, x.shape[0]
+        self.pre, self.scale = pre, scale
+
+    def matches(self, norm, x: torch.Tensor) -> bool:
+        return (self.norm is norm and self.x_ptr == x.data_ptr() and self.version == x._version
+                and self.rows == x.shape[0])
+
+
 class DeferredNorm:
     """The normalised input of a mixer or feed-forward, not yet computed. A part that sets
     ``accepts_deferred_input`` receives this instead of a tensor and hands it to ``linear``, which
-    either folds the norm into the product (few rows, RMSNorm) or calls ``tensor()``; a part that
-    needs the activations themselves calls ``tensor()`` and gets them (computed once)."""
+    folds the norm into the product (few rows, RMSNorm), or takes what the product before prepared
+    (``prepared()``), or calls ``tensor()``; a part that needs the activations themselves calls
+    ``tensor()`` and gets them (computed once)."""
 
     def __init__(self, ctx, norm: "Norm", x: torch.Tensor, name: str = "h"):
         self.ctx, self.norm, self.x, self.name = ctx, norm, x, name
         self._tensor = None
         self.shape = x.shape
+
+    def prepared(self):
+        """(bfloat16(x * gain), row scale) if the product that wrote ``x`` prepared this norm, else None."""
+        p = getattr(self.ctx, "prepared_norm", None)
+        if p is not None and self._tensor is None and p.matches(self.norm, self.x):
+            return p.pre, p.scale
+        return None
 
     def tensor(self) -> torch.Tensor:
         if self._tensor is None:

@@ -23,15 +23,25 @@ class PreNormBlock(Part):
     def sub_parts(self):
         return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn}
 
+    def entry_norm(self):
+        """The norm that reads the residual first when this layer runs (whoever runs the layer before may tell
+        its last product, through ``ctx.next_norm``, to prepare it)."""
+        return self.mixer_norm
+
     def forward(self, ctx, x, cache, writes_cache: bool, after_mixer=None) -> None:
         """``after_mixer`` (optional) is called once the mixer's kernels are launched: the model uses it
-        to let the next layer's mixer start its prefetch beside this layer's feed-forward."""
+        to let the next layer's mixer start its prefetch beside this layer's feed-forward.
+        ``ctx.norm_after_layer`` (optional) is the norm that will read ``x`` after this layer."""
+        after_layer = getattr(ctx, "norm_after_layer", None)
         h = DeferredNorm(ctx, self.mixer_norm, x)
+        ctx.next_norm = self.ffn_norm          # a hint to the product that adds the mixer's output into x
         self.mixer.forward(ctx, h if self.mixer.accepts_deferred_input else h.tensor(), x, cache, writes_cache)
         if after_mixer is not None:
             after_mixer()
         h = DeferredNorm(ctx, self.ffn_norm, x)
+        ctx.next_norm = after_layer
         self.ffn.forward(ctx, h if self.ffn.accepts_deferred_input else h.tensor(), x)
+        ctx.next_norm = None
 
 
 register_part("arrangement", "pre_norm", lambda kind, *, layer_spec, hidden_size: PreNormBlock(layer_spec, hidden_size=hidden_size),

@@ -781,6 +781,105 @@ def test_gemm_tcgen05_gated(M, inter, K):
     assert float((act[:, inter:].float() - 9.0).abs().max()) == 0.0        # nothing written beside the output
 
 
+@pytest.mark.parametrize("M, d, inner, eps", [(65, 576, 1536, 1e-5), (2048, 576, 576, 1e-5), (300, 960, 2560, 1e-6),
+                                              (1000, 2048, 512, 1e-5), (129, 72, 200, 1e-3), (4500, 576, 64, 1e-5)])
+def test_gemm_tcgen05_norm_split_between_two_products(M, d, inner, eps):
+    """An RMSNorm split between the product that completes the residual rows (it also leaves bfloat16(x * gain) and
+    partial sums of squares) and the products that read the normalised rows (they scale their sums row by row):
+    every output against the float64 statement of add, normalise, multiply."""
+    from glassbox_b200 import kernels
+    g = torch.Generator().manual_seed(M + d)
+    a = torch.randn(M, inner, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(d, inner, generator=g) / math.sqrt(inner)).to(torch.bfloat16).to(DEV)
+    base = (torch.randn(M, d, generator=g) * torch.rand(M, 1, generator=g) * 30).to(DEV)    # rows of very different size
+    gain = (1 + 0.3 * torch.randn(d, generator=g)).to(DEV)
+    st = status()
+    x = base.clone()
+    parts = kernels.gemm_tc_column_tiles(M, d, inner)
+    pre = torch.full((M, d + 8), 7.0, device=DEV, dtype=torch.bfloat16)
+    ss = torch.full((M, parts), -1.0, device=DEV)
+    kernels.gemm_tc(a, w, x, accumulate=True, status=st, prepare=(gain, pre[:, :d], ss))
+    assert int(st) == 0
+    x64 = base.double() + a.double() @ w.double().T
+    assert (x.double() - x64).abs().max() <= 2e-5 * math.sqrt(inner) * 30 + 1e-6
+    plain = base.clone()
+    kernels.gemm_tc(a, w, plain, accumulate=True, status=st)
+    assert torch.equal(plain, x), "preparing the norm must not change the residual"
+    want_pre = x.double() * gain.double()
+    assert ((pre[:, :d].double() - want_pre).abs() / (1e-3 + want_pre.abs())).max() <= 2 ** -8
+    assert float((pre[:, d:].float() - 7.0).abs().max()) == 0.0
+    sums = (x.double() ** 2).sum(1)
+    assert ((ss.double().sum(1) - sums).abs() / sums).max() <= 1e-5
+    inv = 1.0 / torch.sqrt(sums / d + eps)
+    normed = pre[:, :d].double() * inv[:, None]               # what the consumers see, in exact arithmetic
+    scale = kernels.RowScale(ss, eps)
+    # plain consumer, float32 and bfloat16 outputs, and one that adds
+    n_out = 200
+    w2 = (torch.randn(n_out, d, generator=g) / math.sqrt(d)).to(torch.bfloat16).to(DEV)
+    ref = normed @ w2.double().T
+    c32 = torch.empty(M, n_out, device=DEV)
+    kernels.gemm_tc(pre[:, :d], w2, c32, status=st, row_scale=scale)
+    assert (c32.double() - ref).abs().max() <= 2e-5 * math.sqrt(d) * float(gain.abs().max()) + 1e-6
+    other = torch.randn(M, n_out, generator=g).to(DEV)
+    acc = other.clone()
+    kernels.gemm_tc(pre[:, :d], w2, acc, accumulate=True, status=st, row_scale=scale)
+    assert (acc.double() - other.double() - ref).abs().max() <= 2e-5 * math.sqrt(d) * float(gain.abs().max()) + 1e-6
+    # and against the norm as its own kernel in front of the same product
+    h = torch.empty(M, d, device=DEV, dtype=torch.bfloat16)
+    kernels.rmsnorm(x, gain, h, eps)
+    sep = torch.empty(M, n_out, device=DEV)
+    kernels.gemm_tc(h, w2, sep, status=st)
+    assert (sep - c32).abs().max() <= tol(torch.bfloat16, 2)
+    # gated consumer
+    inter = 136
+    wg = (torch.randn(2 * inter, d, generator=g) * (1.5 / math.sqrt(d))).to(torch.bfloat16).to(DEV)
+    act = torch.empty(M, inter, device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_tc_gated(pre[:, :d], wg, act, status=st, row_scale=scale)
+    gu = normed @ wg.double().T
+    gg, uu = gu[:, :inter], gu[:, inter:]
+    ref_act = gg / (1 + torch.exp(-gg)) * uu
+    assert ((act.double() - ref_act).abs() / (1 + ref_act.abs())).max() <= tol(torch.bfloat16, 1)
+    assert int(st) == 0
+
+
+@pytest.mark.parametrize("M", [65, 300, 2048])
+def test_gemm_tcgen05_qkv_completes_a_prepared_norm(M):
+    """The QKV epilogue with a row scale: rotation and cache write of inv_rms * (pre W^T), against float64."""
+    from glassbox_b200 import kernels
+    from glassbox_b200.parts.rope import rotary_table
+    nh, nkv, hd, d, ps, eps = 9, 3, 64, 576, 16, 1e-5
+    g = torch.Generator().manual_seed(M)
+    pre = (torch.randn(M, d, generator=g) * 4).to(torch.bfloat16).to(DEV)
+    parts = 3
+    ss = (torch.rand(M, parts, generator=g) * d * 20).to(DEV)
+    w = (torch.randn((nh + 2 * nkv) * hd, d, generator=g) / math.sqrt(d)).to(torch.bfloat16).to(DEV)
+    table = rotary_table(1e5, hd, 3000).to(DEV)
+    positions = torch.randint(0, 3000, (M,), generator=g).to(torch.int32)
+    pages = -(-M // ps) + 3
+    slots = torch.randperm(pages * ps, generator=g)[:M].to(torch.int32)
+    q = torch.zeros(M, (nh + 2 * nkv) * hd, device=DEV, dtype=torch.bfloat16)
+    kc = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    st = status()
+    kernels.gemm_tc_qkv(pre, w, q, table, positions.to(DEV), slots.to(DEV), kc, vc, nh, nkv, hd, ps, True, st,
+                        row_scale=kernels.RowScale(ss, eps))
+    assert int(st) == 0
+    inv = 1.0 / torch.sqrt(ss.double().sum(1) / d + eps)
+    ref = ((pre.double() * inv[:, None]) @ w.double().T).cpu()
+    half = hd // 2
+    cs = table.double().cpu()[positions.long()]
+    r = ref.reshape(M, nh + 2 * nkv, hd).clone()
+    a, b = r[:, :nh + nkv, :half].clone(), r[:, :nh + nkv, half:].clone()
+    r[:, :nh + nkv, :half] = a * cs[:, None, :, 0] - b * cs[:, None, :, 1]
+    r[:, :nh + nkv, half:] = b * cs[:, None, :, 0] + a * cs[:, None, :, 1]
+    t = tol(torch.bfloat16, 2)
+    assert (q.cpu().double()[:, :nh * hd] - r[:, :nh].reshape(M, -1)).abs().max() <= t
+    for row in range(0, M, 7):
+        page, offs = int(slots[row]) // ps, int(slots[row]) % ps
+        assert (kc[page, :, offs].cpu().double() - r[row, nh:nh + nkv]).abs().max() <= t
+        assert (vc[page, :, offs].cpu().double() - r[row, nh + nkv:]).abs().max() <= t
+
+
 def test_gemm_tcgen05_many_tiles_per_block():
     """More tiles than SMs: every persistent block walks several tiles and both accumulators alternate."""
     from glassbox_b200 import kernels
