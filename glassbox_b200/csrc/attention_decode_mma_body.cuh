@@ -3,6 +3,8 @@
 // virtual blocks, and the persistent decode-program kernel (decode_program.cu), whose resident blocks walk over them.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 struct DecodeAttnArgs {
@@ -79,9 +81,23 @@ struct __align__(16) DecodeAttnSmem {   // (a multiple of 16 bytes, so that arra
     int is_last;
 };
 
-template <int HD, int BK, class Sync>
+// NW warps (NW * 32 threads) work on one virtual block: 4, or 8 where few blocks would otherwise leave the chip's
+// memory system idle (a small batch): each warp then has half as many blocks of keys to walk through.
+// Floats of shared memory that the merge inside a thread-block cluster needs in the cluster's first block: one
+// (output row, maximum, sum) per head of the group and per warp of every split.
+template <int HD>
+__host__ __device__ constexpr int decode_attn_cluster_floats(int group, int splits, int warps) { return group * splits * warps * (HD + 2); }
+
+// CLUSTER: the blocks of one (row, kv head), one per split, are one thread-block cluster (the caller launches them
+// so). Their warps then put their partial results straight into the shared memory of the cluster's first block
+// (`cluster_part`, decode_attn_cluster_floats<HD>() floats, the same offset in every block), meet at the cluster's
+// barrier, and the first block merges from its own shared memory: no trip through global memory, no counter, no
+// second pass over what other blocks wrote. Otherwise the partial results go through `part_acc` / `part_ml` and the
+// block that arrives last at `counters` merges them.
+template <int HD, int BK, class Sync, int NW = 4, bool CLUSTER = false>
 __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& a, const int split, const int kvh, const int row,
-                                                          DecodeAttnSmem& sm, Sync& sync) {
+                                                          DecodeAttnSmem& sm, Sync& sync, float* cluster_part = nullptr) {
+    constexpr int NTHREADS = NW * 32;
     const __nv_bfloat16* __restrict__ q = a.q;
     const long long q_stride = a.q_stride, out_stride = a.out_stride;
     __nv_bfloat16* __restrict__ out = a.out;
@@ -104,11 +120,11 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     constexpr int KT = BK / 8;    // n8 tiles over the keys of a block (scores)
     constexpr int KB = BK / 16;   // k16 steps over the keys of a block (output)
     constexpr int VW = NT / 2;    // 32-bit words of a value row per thread
-    const int tid = sync.thread(), lane = tid & 31, warp = tid >> 5;   // 128 threads work on one virtual block
+    const int tid = sync.thread(), lane = tid & 31, warp = tid >> 5;   // NW * 32 threads work on one virtual block
     const int g = lane >> 2, t = lane & 3;
     const int G = nh / nkv;
     const int head0 = kvh * G;
-    const int S4 = splits * 4;
+    const int S4 = splits * NW;   // partial results per head: one per warp of every split
     int& is_last = sm.is_last;
 
     // Let the next kernel in the stream begin its prologue. This kernel's own prologue (positions,
@@ -125,9 +141,11 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
         sync.wait();
         if (sync.gave_up()) return;
         if (split == 0)
-            for (int i = tid; i < G * HD; i += 128) orow[head0 * HD + i] = __float2bfloat16_rn(0.f);
+            for (int i = tid; i < G * HD; i += NTHREADS) orow[head0 * HD + i] = __float2bfloat16_rn(0.f);
         return;
     }
+    if constexpr (CLUSTER)   // every block of the cluster says that it runs (its shared memory exists); waited for before the first store into another block's
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     const int* table = block_tables + (size_t)row_seq[row] * max_pages;
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_aligned = first / BK * BK;   // blocks of keys start at multiples of BK; keys before `first` are masked
@@ -157,7 +175,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     const bool staged = n_pages <= MMA_MAX_PAGES;
     int bad = 0;
     if (staged) {
-        for (int i = tid; i < n_pages; i += 128) {
+        for (int i = tid; i < n_pages; i += NTHREADS) {
             int page = table[page_lo + i];
             if (page < 0 || page >= num_pages) {
                 // a page wholly before the first visible key may have been given back (window): its
@@ -284,11 +302,11 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
 
     Block A, B;
     if (warp < nblocks) load_block(warp, A);
-    for (int blk = warp; blk < nblocks; blk += 8) {
-        if (blk + 4 < nblocks) load_block(blk + 4, B);
+    for (int blk = warp; blk < nblocks; blk += 2 * NW) {
+        if (blk + NW < nblocks) load_block(blk + NW, B);
         compute_block(blk, A);
-        if (blk + 8 < nblocks) load_block(blk + 8, A);
-        if (blk + 4 < nblocks) compute_block(blk + 4, B);
+        if (blk + 2 * NW < nblocks) load_block(blk + 2 * NW, A);
+        if (blk + NW < nblocks) compute_block(blk + NW, B);
     }
 
     if (bad) atomicOr(status, GB_STATUS_BAD_SLOT);
@@ -298,7 +316,61 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
-    const int sub = split * 4 + warp;
+    const int sub = split * NW + warp;
+    float* weights = sm.weights;
+    if constexpr (CLUSTER) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        // [head of the group][sub-split][HD channels, maximum, sum] in the first block's shared memory
+        float* first = cluster.map_shared_rank(cluster_part, 0);
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int hi = g + 8 * h;
+            if (hi < G) {
+                float* pa = first + ((size_t)hi * S4 + sub) * (HD + 2);
+                if (t == 0) {
+                    pa[HD] = m_run[h];
+                    pa[HD + 1] = l_run[h];
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    pa[NT * (2 * t) + j] = acc[j][2 * h];
+                    pa[NT * (2 * t + 1) + j] = acc[j][2 * h + 1];
+                }
+            }
+        }
+        cluster.sync();                       // (release / acquire: the first block sees what the others stored)
+        if (cluster.block_rank() != 0) return;
+        // one warp per head turns the (maximum, sum) pairs into normalised weights; then every thread adds up its channel
+        for (int hi = warp; hi < G; hi += NW) {
+            const float* ph = cluster_part + (size_t)hi * S4 * (HD + 2);
+            float m = MMA_NEG_BIG;
+            for (int sidx = lane; sidx < S4; sidx += 32) m = fmaxf(m, ph[sidx * (HD + 2) + HD]);
+            m = gb_warp_max(m);
+            float l = 0.f;
+            for (int sidx = lane; sidx < S4; sidx += 32) {
+                const float w = __expf(ph[sidx * (HD + 2) + HD] - m);
+                weights[hi * S4 + sidx] = w;
+                l = fmaf(ph[sidx * (HD + 2) + HD + 1], w, l);
+            }
+            l = gb_warp_sum(l);
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            __syncwarp();
+            for (int sidx = lane; sidx < S4; sidx += 32) weights[hi * S4 + sidx] *= inv;
+        }
+        sync.group_barrier();
+        for (int i = tid; i < G * HD; i += NTHREADS) {
+            const int hi = i / HD, d = i % HD;
+            const float* pa = cluster_part + (size_t)hi * S4 * (HD + 2) + d;
+            const float* w = weights + hi * S4;
+            float v = 0.f;
+#pragma unroll 8
+            for (int sidx = 0; sidx < S4; ++sidx) v = fmaf(pa[(size_t)sidx * (HD + 2)], w[sidx], v);
+            orow[(head0 + hi) * HD + d] = __float2bfloat16_rn(v);
+        }
+        return;
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int hi = g + 8 * h;
@@ -331,11 +403,10 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     // Merge: one warp per head turns the (maximum, sum) pairs of all sub-splits into normalised
     // weights in shared memory; then every thread adds up its channel over the sub-splits with
     // independent loads.
-    float* weights = sm.weights;
     const int per_pass = MMA_MAX_MERGE / S4;                 // heads whose weights fit at once
     for (int h0 = 0; h0 < G; h0 += per_pass) {
         const int hcount = min(per_pass, G - h0);
-        for (int hi = warp; hi < hcount; hi += 4) {
+        for (int hi = warp; hi < hcount; hi += NW) {
             const float* ml = part_ml + ((size_t)row * nh + head0 + h0 + hi) * S4 * 2;
             float m = MMA_NEG_BIG;
             for (int sidx = lane; sidx < S4; sidx += 32) m = fmaxf(m, __ldcg(ml + 2 * sidx));
@@ -352,7 +423,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
             for (int sidx = lane; sidx < S4; sidx += 32) weights[hi * S4 + sidx] *= inv;
         }
         sync.group_barrier();
-        for (int i = tid; i < hcount * HD; i += 128) {
+        for (int i = tid; i < hcount * HD; i += NTHREADS) {
             const int hi = i / HD, d = i % HD;
             const float* pa = part_acc + ((size_t)row * nh + head0 + h0 + hi) * S4 * HD + d;
             const float* w = weights + hi * S4;

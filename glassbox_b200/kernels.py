@@ -49,7 +49,7 @@ _SIGNATURES = {
     "gb_gemm_stream_qkv": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                            _LL, _I, _P, _P, _LL, _I, _P],
     "gb_attention_decode_mma_pdl": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
-                                    _P, _P, _I, _I, _P],
+                                    _P, _P, _I, _I, _I, _P],
     "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
                                 _P, _P],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
@@ -620,17 +620,25 @@ def attention_decode_mma_supported(dtype: torch.dtype, nh: int, nkv: int, hd: in
 
 
 def decode_mma_plan(n: int, nkv: int, hd: int, max_context: int):
-    """(splits, keys per warp iteration) for the tensor-core decode kernel. A small batch needs many
-    blocks per (row, kv head) to fill the GPU, but each block keeps at least 512 keys, below which the
-    fixed cost of a block and of the merge outweighs the parallelism; a batch that fills the GPU by
-    itself takes the 16-key variant (three blocks per SM instead of two) and few splits. Depends on
-    the batch shape and the longest context the step allows, never on the data, so a captured graph
-    can fix it."""
+    """(splits, keys per warp iteration, warps per block) for the tensor-core decode kernel. A small batch needs
+    many blocks per (row, kv head) to fill the GPU, but each block keeps at least 512 keys, below which the
+    fixed cost of a block and of the merge outweighs the parallelism; where that leaves at most one block
+    per SM, a block has eight warps instead of four, so that each warp walks through half as many keys (the
+    splits are then rounded down: a second block of eight warps does not fit beside the first). A batch that
+    fills the GPU by itself takes the 16-key variant (three blocks per SM instead of two) and few splits.
+    Depends on the batch shape and the longest context the step allows, never on the data, so a captured
+    graph can fix it."""
     pairs = max(n * nkv, 1)
     most = max(1, -(-max_context // 512))
     if hd == 64 and pairs >= 96:
-        return max(1, min(-(-296 // pairs), most)), 16
-    return max(1, min(-(-148 // pairs), most)), 0
+        return max(1, min(-(-296 // pairs), most)), 16, 4
+    if hd == 64 and pairs <= 74:
+        # (measured at 9/3 heads, microseconds at context 4096 with 4 warps and the old split count against 8 warps:
+        # batch 8 18.8 -> 12.4, batch 16 18.2 -> 15.1, batch 4 12.7 -> 11.3; eight warps want at least 256 keys a block
+        # and at most 8 splits: context 1024, batch 8: 2 splits 9.3, 4 splits 8.6; context 4096, batch 1: 8 splits
+        # 11.1, 16 splits 12.4)
+        return max(1, min(148 // pairs, 8, -(-max_context // 256))), 0, 8
+    return max(1, min(-(-148 // pairs), most)), 0, 4
 
 
 def decode_mma_splits(n: int, nkv: int, hd: int, max_context: int) -> int:
@@ -641,15 +649,15 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
                          block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int,
                          hd: int, page_size: int, scale: float, window: Optional[int], splits: int,
                          part_acc: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
-                         status: torch.Tensor, block_keys: int = 0) -> None:
+                         status: torch.Tensor, block_keys: int = 0, warps: int = 4) -> None:
     """bfloat16 split-key decode attention on the tensor cores. Scratch: part_acc float32
-    [n, nh, 4*splits, hd], part_ml float32 [n, nh, 4*splits, 2], counters int32 [n*nkv], zero on entry
-    and left zero."""
+    [n, nh, warps*splits, hd], part_ml float32 [n, nh, warps*splits, 2], counters int32 [n*nkv], zero on entry
+    and left zero. ``warps`` per block: 4, or 8 (head size 64, 32 keys per iteration)."""
     _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, part_acc, part_ml, counters, status)
     n = q.shape[0]
     assert q.dtype == out.dtype == kcache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
-    assert part_acc.numel() >= n * nh * 4 * splits * hd and part_ml.numel() >= n * nh * 4 * splits * 2
+    assert part_acc.numel() >= n * nh * warps * splits * hd and part_ml.numel() >= n * nh * warps * splits * 2
     assert counters.numel() >= n * nkv
     prog = _program_for(status)
     if prog is not None and prog.takes_rows(n):
@@ -665,7 +673,7 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     _call("gb_attention_decode_mma_pdl", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
           _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
           kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml), _ptr(counters),
-          _ptr(status), 1 if USE_PDL else 0, int(block_keys), _stream())
+          _ptr(status), 1 if USE_PDL else 0, int(block_keys), int(warps), _stream())
 
 
 def attention_prefill_supported(dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:

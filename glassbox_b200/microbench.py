@@ -124,14 +124,14 @@ def bench_attention_decode(batches) -> None:
         pos = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
         q = torch.randn(m, nh * hd, device=DEV).bfloat16()
         o = torch.empty_like(q)
-        splits, block_keys = kernels.decode_mma_plan(m, nkv, hd, ctx)
-        pa = torch.empty(m * nh * 4 * splits * hd, device=DEV)
-        pm = torch.empty(m * nh * 4 * splits * 2, device=DEV)
+        splits, block_keys, warps = kernels.decode_mma_plan(m, nkv, hd, ctx)
+        pa = torch.empty(m * nh * warps * splits * hd, device=DEV)
+        pm = torch.empty(m * nh * warps * splits * 2, device=DEV)
         cn = torch.zeros(m * nkv, dtype=torch.int32, device=DEV)
         t = graph_time(lambda: kernels.attention_decode_mma(q, o, kc, vc, tables, row_seq, pos, nh, nkv, hd, ps, hd ** -0.5,
-                                                            None, splits, pa, pm, cn, status, block_keys))
+                                                            None, splits, pa, pm, cn, status, block_keys, warps))
         nbytes = m * ctx * nkv * hd * 2 * 2
-        print(f"attention_decode_mma batch {m:3d} ctx {ctx} splits {splits} keys/iteration {block_keys or 32}: {t:7.1f} us "
+        print(f"attention_decode_mma batch {m:3d} ctx {ctx} splits {splits} keys/iteration {block_keys or 32} warps {warps}: {t:7.1f} us "
               f"{nbytes / t / 1e3:6.0f} GB/s", flush=True)
     kernels.check_status(status)
 

@@ -117,13 +117,13 @@ class GqaAttention(Mixer):
     def _attend_decode(self, ctx, q, att, cache, n: int) -> bool:
         """Rows 0 .. n-1, one per request (request i is row i); False if no decode kernel takes the shape."""
         if kernels.attention_decode_mma_supported(q.dtype, self.nh, self.nkv, self.hd, cache.page_size):
-            splits, block_keys = kernels.decode_mma_plan(n, self.nkv, self.hd, ctx.max_context)
-            part_acc = ctx.scratch("decode_part_acc", (n, self.nh * 4 * splits * self.hd), torch.float32, grow=True)
-            part_ml = ctx.scratch("decode_part_ml", (n, self.nh * 4 * splits * 2), torch.float32, grow=True)
+            splits, block_keys, warps = kernels.decode_mma_plan(n, self.nkv, self.hd, ctx.max_context)
+            part_acc = ctx.scratch("decode_part_acc", (n, self.nh * warps * splits * self.hd), torch.float32, grow=True)
+            part_ml = ctx.scratch("decode_part_ml", (n, self.nh * warps * splits * 2), torch.float32, grow=True)
             counters = ctx.zeros_once("decode_counters", ctx.max_rows * self.nh, torch.int32)
             kernels.attention_decode_mma(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq[:n], ctx.positions[:n],
                                          self.nh, self.nkv, self.hd, cache.page_size, self.spec.scale,
-                                         self.spec.window, splits, part_acc, part_ml, counters, ctx.status, block_keys)
+                                         self.spec.window, splits, part_acc, part_ml, counters, ctx.status, block_keys, warps)
             return True
         if self.hd % 16 == 0 and self.hd >= 16:
             splits = kernels.decode_splits(n, self.nh, self.nkv, ctx.max_context)

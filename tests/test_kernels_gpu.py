@@ -400,21 +400,24 @@ MMA_CASES = [  # nh, nkv, hd, page_size, window, lens
 ]
 
 
+@pytest.mark.parametrize("warps", [4, 8])
 @pytest.mark.parametrize("splits", [1, 3, 16])
 @pytest.mark.parametrize("case", MMA_CASES)
-def test_attention_decode_mma(case, splits):
+def test_attention_decode_mma(case, splits, warps):
     from glassbox_b200 import kernels
     nh, nkv, hd, ps, window, lens = case
     dtype = torch.bfloat16
     assert kernels.attention_decode_mma_supported(dtype, nh, nkv, hd)
+    if warps == 8 and hd != 64:
+        pytest.skip("eight warps per block are built for head size 64")
     k, v, tables, dense = make_cache(dtype, len(lens), lens, nkv, hd, ps, seed=3)
     n = len(lens) + 1
     row_seq = list(range(len(lens))) + [0]
     positions = [l - 1 for l in lens] + [-1]
     q = torch.randn(n, nh, hd).to(dtype)
     out = torch.full((n, nh * hd), 7.0, device=DEV, dtype=dtype)
-    part_acc = torch.empty(n * nh * 4 * splits * hd, device=DEV)
-    part_ml = torch.empty(n * nh * 4 * splits * 2, device=DEV)
+    part_acc = torch.empty(n * nh * warps * splits * hd, device=DEV)
+    part_ml = torch.empty(n * nh * warps * splits * 2, device=DEV)
     counters = torch.zeros(n * nkv, dtype=torch.int32, device=DEV)
     st = status()
     ref = ref_attention(q[:-1], dense, row_seq[:-1], positions[:-1], nh, nkv, hd ** -0.5, window)
@@ -422,7 +425,7 @@ def test_attention_decode_mma(case, splits):
         kernels.attention_decode_mma(q.to(DEV).reshape(n, nh * hd), out, k, v, tables,
                                      torch.tensor(row_seq, dtype=torch.int32, device=DEV),
                                      torch.tensor(positions, dtype=torch.int32, device=DEV), nh, nkv, hd, ps, hd ** -0.5,
-                                     window, splits, part_acc, part_ml, counters, st)
+                                     window, splits, part_acc, part_ml, counters, st, 0, warps)
         got = out.cpu().double().reshape(n, nh, hd)
         assert int(st) == 0 and int(counters.abs().max()) == 0
         assert (got[:-1] - ref).abs().max() <= tol(dtype, 2)
@@ -1009,13 +1012,13 @@ def test_decode_attention_at_the_benchmarked_context_lengths(dtype, nh, nkv, B, 
     st = status()
     out = torch.full((B, nh * hd), 7.0, device=DEV, dtype=dtype)
     if dtype == torch.bfloat16:
-        splits, block_keys = kernels.decode_mma_plan(B, nkv, hd, L)
-        for sp, bk in {(splits, block_keys), (1, 0), (max(splits // 2, 1), 16)}:
+        splits, block_keys, warps = kernels.decode_mma_plan(B, nkv, hd, L)
+        for sp, bk, nw in {(splits, block_keys, warps), (1, 0, 4), (max(splits // 2, 1), 16, 4), (3, 0, 8), (1, 0, 8)}:
             kernels.attention_decode_mma(qd, out, k, v, tables, row_seq, positions, nh, nkv, hd, ps, hd ** -0.5, None, sp,
-                                         torch.empty(B * nh * 4 * sp * hd, device=DEV), torch.empty(B * nh * 4 * sp * 2, device=DEV),
-                                         torch.zeros(B * nkv, dtype=torch.int32, device=DEV), st, bk)
+                                         torch.empty(B * nh * nw * sp * hd, device=DEV), torch.empty(B * nh * nw * sp * 2, device=DEV),
+                                         torch.zeros(B * nkv, dtype=torch.int32, device=DEV), st, bk, nw)
             diff = (out.double().reshape(B, nh, hd) - ref).abs()
-            assert int(st) == 0 and diff.max() <= tol(dtype, 2), f"splits {sp}, {bk or 32}-key variant: off by {float(diff.max()):.3e}"
+            assert int(st) == 0 and diff.max() <= tol(dtype, 2), f"splits {sp}, {bk or 32}-key variant, {nw} warps: off by {float(diff.max()):.3e}"
             out.fill_(7.0)
     splits = kernels.decode_splits(B, nh, nkv, L)
     for sp in {splits, 1, 3}:
