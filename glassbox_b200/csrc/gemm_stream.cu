@@ -98,11 +98,12 @@ static int stream_slots() {
 }
 
 static int slots_of(int nt, bool pair, int kc) {
-#define GB_SL(NTT) return pair ? (kc == 512 ? stream_slots<NTT, true, 512>() : stream_slots<NTT, true, 256>()) \
-                               : (kc == 512 ? stream_slots<NTT, false, 512>() : stream_slots<NTT, false, 256>());
+#define GB_SL(NTT) return pair ? (kc == 640 ? stream_slots<NTT, true, 640>() : kc == 512 ? stream_slots<NTT, true, 512>() : stream_slots<NTT, true, 256>()) \
+                               : (kc == 640 ? stream_slots<NTT, false, 640>() : kc == 512 ? stream_slots<NTT, false, 512>() : stream_slots<NTT, false, 256>());
     if (nt == 1) { GB_SL(1) }
     if (nt == 2) { GB_SL(2) }
-    if (nt == 4) { GB_SL(4) }
+    if (nt == 4) { return pair ? (kc == 512 ? stream_slots<4, true, 512>() : stream_slots<4, true, 256>())
+                               : (kc == 512 ? stream_slots<4, false, 512>() : stream_slots<4, false, 256>()); }
     return pair ? stream_slots<8, true, 256>() : stream_slots<8, false, 256>();
 #undef GB_SL
 }
@@ -111,9 +112,12 @@ static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStr
     const int nt = a.M <= 8 ? 1 : a.M <= 16 ? 2 : a.M <= 32 ? 4 : 8;
     // The wide chunk keeps twice the loads in flight per thread, at twice the registers: it is taken
     // where its blocks still fit the chip in one wave (and never by the variants with many rows, which
-    // have neither the registers nor the shared memory for it).
+    // have neither the registers nor the shared memory for it). A K just above 512 (576: SmolLM2-135M)
+    // would leave a second chunk of a few columns that costs a whole round of staging and barriers: with at
+    // most 16 rows such a K goes through as one chunk of 640.
     const bool wide_fits = nt <= (pair ? 2 : 4);
     int kc = (wide_fits && strips <= slots_of(nt, pair, 512)) ? 512 : 256;
+    if (kc == 512 && nt <= 2 && a.K > 512 && a.K <= 640 && strips <= slots_of(nt, pair, 640)) kc = 640;
     // Cluster size: one block per 512 k, rounded up to a power of two, as long as all blocks are on the
     // chip at once and the other ranks' sums fit the first block's activation tile. Chunk and cluster
     // size depend on the matrix and on the row bucket (8, 16, 32, 64), not on which rows are in the batch.
@@ -125,10 +129,12 @@ static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStr
     a.kslice = split == 1 ? a.K : ((a.K + split - 1) / split + kc - 1) / kc * kc;
 #define GB_WS2(NTT, KCC) return pair ? launch_stream<NTT, true, KCC>(a, strips, split, pdl, stream) : launch_stream<NTT, false, KCC>(a, strips, split, pdl, stream);
 #define GB_WS(NTT) if (kc == 512) { GB_WS2(NTT, 512) } else { GB_WS2(NTT, 256) }
-    if (nt == 1) { GB_WS(1) }
-    if (nt == 2) { GB_WS(2) }
+#define GB_WS3(NTT) if (kc == 640) { GB_WS2(NTT, 640) } else GB_WS(NTT)
+    if (nt == 1) { GB_WS3(1) }
+    if (nt == 2) { GB_WS3(2) }
     if (nt == 4) { GB_WS(4) }
     GB_WS2(8, 256)
+#undef GB_WS3
 #undef GB_WS
 #undef GB_WS2
 }
