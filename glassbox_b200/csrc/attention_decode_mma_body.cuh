@@ -403,6 +403,40 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     // Merge: one warp per head turns the (maximum, sum) pairs of all sub-splits into normalised
     // weights in shared memory; then every thread adds up its channel over the sub-splits with
     // independent loads.
+    if (G * HD <= NTHREADS && S4 <= 64) {
+        // The usual case (every output channel of the group has a thread of its own, at most 64 partial results per
+        // head): a thread asks for its channel of every partial result at once, before the weights exist, and a lane
+        // reads its (maximum, sum) pairs once; the merge is then two trips to L2 that overlap instead of four in a row.
+        constexpr int MAXP = 64;
+        const int hi_o = tid / HD, d_o = tid % HD;
+        float pv[MAXP];
+        if (tid < G * HD) {
+            const float* pa = part_acc + ((size_t)row * nh + head0 + hi_o) * S4 * HD + d_o;
+#pragma unroll
+            for (int sidx = 0; sidx < MAXP; ++sidx) pv[sidx] = sidx < S4 ? __ldcg(pa + (size_t)sidx * HD) : 0.f;
+        }
+        for (int hi = warp; hi < G; hi += NW) {
+            const float2* ml = reinterpret_cast<const float2*>(part_ml + ((size_t)row * nh + head0 + hi) * S4 * 2);
+            const float2 p0 = lane < S4 ? __ldcg(ml + lane) : make_float2(MMA_NEG_BIG, 0.f);
+            const float2 p1 = lane + 32 < S4 ? __ldcg(ml + lane + 32) : make_float2(MMA_NEG_BIG, 0.f);
+            const float m = gb_warp_max(fmaxf(p0.x, p1.x));
+            const float w0 = __expf(p0.x - m), w1 = __expf(p1.x - m);
+            const float l = gb_warp_sum(fmaf(p0.y, w0, p1.y * w1));
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            if (lane < S4) weights[hi * S4 + lane] = w0 * inv;
+            if (lane + 32 < S4) weights[hi * S4 + lane + 32] = w1 * inv;
+        }
+        sync.group_barrier();
+        if (tid < G * HD) {
+            const float* w = weights + hi_o * S4;
+            float v = 0.f;
+#pragma unroll
+            for (int sidx = 0; sidx < MAXP; ++sidx)
+                if (sidx < S4) v = fmaf(pv[sidx], w[sidx], v);
+            orow[(head0 + hi_o) * HD + d_o] = __float2bfloat16_rn(v);
+        }
+        return;
+    }
     const int per_pass = MMA_MAX_MERGE / S4;                 // heads whose weights fit at once
     for (int h0 = 0; h0 < G; h0 += per_pass) {
         const int hcount = min(per_pass, G - h0);
