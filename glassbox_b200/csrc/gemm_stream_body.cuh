@@ -171,6 +171,9 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
     };
 
     if (nchunks > 0) fetch(0);   // weights do not depend on the previous kernel
+    constexpr bool EARLY_ROPE = PAIR && NT <= 2;   // (the rotary mode runs with at most 16 rows)
+    int rp_pos[EARLY_ROPE ? NT : 1], rp_slot[EARLY_ROPE ? NT : 1];
+    float2 rp_cs[EARLY_ROPE ? NT : 1];
     {
         if (!PERSIST && a.prefetch != nullptr) {
             // While this kernel waits for its predecessor and works, the weights of a kernel further down
@@ -178,6 +181,28 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             const long long lines = (a.prefetch_bytes + 127) / 128;
             for (long long i = (long long)blockIdx.x * 128 + tid; i < lines; i += (long long)gridDim.x * 128)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(a.prefetch + i * 128));
+        }
+        // Rotary mode: a row's position, its (cos, sin) pair and its cache slot are step metadata that no kernel
+        // writes. They are asked for now, so that the epilogue does not end on two dependent trips to memory.
+        if constexpr (EARLY_ROPE) {
+            if (a.mode == WS_ROPE_QKV) {
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    const int e = tid + i * 128, n = n0 + e % 16, tok = e / 16;
+                    rp_pos[i] = -1;
+                    rp_slot[i] = -1;
+                    rp_cs[i] = make_float2(1.f, 0.f);
+                    if (n < N && tok < M) {
+                        const int pos = a.positions[tok];
+                        rp_pos[i] = pos;
+                        if (pos >= 0) {
+                            rp_slot[i] = a.slots[tok];
+                            if (n / a.hd < a.nh + a.nkv && a.rope != nullptr && pos < a.max_pos)
+                                rp_cs[i] = a.rope[(size_t)pos * (a.hd / 2) + n % a.hd];
+                        }
+                    }
+                }
+            }
         }
         sync.wait();   // everything below reads what earlier work wrote
         if (sync.gave_up()) return;
@@ -321,7 +346,10 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
         if (n >= N || tok >= M) continue;
         float v[2] = {sum[i][0], SETS > 1 ? sum[i][SETS - 1] : 0.f};
         if (a.mode == WS_ROPE_QKV) {
-            const int pos = a.positions[tok];
+            const int ii = i;                    // (the channel index below takes the name i)
+            int pos;
+            if constexpr (EARLY_ROPE) pos = rp_pos[ii];
+            else pos = a.positions[tok];
             if (pos < 0) continue;               // padding row
             const int half = a.hd / 2;
             const int head = n / a.hd, i = n % a.hd;   // i < hd/2: this thread holds channels i and i + hd/2
@@ -330,7 +358,9 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
                 if (pos >= a.max_pos) {
                     atomicOr(a.status, GB_STATUS_BAD_POSITION);
                 } else {
-                    const float2 cs = a.rope[(size_t)pos * half + i];
+                    float2 cs;
+                    if constexpr (EARLY_ROPE) cs = rp_cs[ii];
+                    else cs = a.rope[(size_t)pos * half + i];
                     y0 = v[0] * cs.x - v[1] * cs.y;
                     y1 = v[1] * cs.x + v[0] * cs.y;
                 }
@@ -340,7 +370,9 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
                 q[i] = __float2bfloat16_rn(y0);
                 q[i + half] = __float2bfloat16_rn(y1);
             } else if (a.write_kv) {
-                const long long slot = a.slots[tok];
+                long long slot;
+                if constexpr (EARLY_ROPE) slot = rp_slot[ii];
+                else slot = a.slots[tok];
                 if (slot < 0 || slot >= a.num_slots) {
                     atomicOr(a.status, GB_STATUS_BAD_SLOT);
                 } else {
