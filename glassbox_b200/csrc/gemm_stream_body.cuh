@@ -209,7 +209,59 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
     }
 
     const bool normalise = a.X == nullptr;
-    if (normalise) {
+    // One chunk holds the whole K (and no cluster shares it): a warp takes whole rows, two at a time, asks for all
+    // their values (and the gains) at once, adds up the squares with shuffles and writes the normalised rows into
+    // the tile: one trip to memory. Otherwise: a pass for the sums of squares, then the rows are read again chunk by
+    // chunk. A lane adds up the same values in the same order either way (4 floats every 128), so the sums agree
+    // to the bit.
+    // (not in the 256-wide variant, which the largest matrices take: its register count decides how many blocks an SM holds)
+    const bool norm_once = WS_KC >= 512 && normalise && nchunks == 1 && kbeg == 0 && kend == K;
+    if (WS_KC >= 512 && norm_once) {
+        constexpr int PPL = (WS_KC + 127) / 128;   // 4-float pieces of a row per lane
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 gn[PPL];
+#pragma unroll
+        for (int p = 0; p < PPL; ++p) {
+            const int col = p * 128 + lane * 4;
+            gn[p] = col < K ? *reinterpret_cast<const float4*>(a.gain + col) : zero4;
+        }
+        for (int m0 = warp; m0 < ROWS; m0 += 8) {
+            float4 x[2][PPL];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int m = m0 + 4 * h;
+#pragma unroll
+                for (int p = 0; p < PPL; ++p) {
+                    const int col = p * 128 + lane * 4;
+                    x[h][p] = (m < M && col < K) ? ld_act<PERSIST>(reinterpret_cast<const float4*>(a.xres + (size_t)m * a.ldr + col)) : zero4;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int m = m0 + 4 * h;
+                if (m >= ROWS) continue;
+                float ss = 0.f;
+#pragma unroll
+                for (int p = 0; p < PPL; ++p) {
+                    const float4 v = x[h][p];
+                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                }
+                ss = gb_warp_sum(ss);
+                const float sc = 1.0f / sqrtf(ss / (float)K + a.eps);
+#pragma unroll
+                for (int p = 0; p < PPL; ++p) {
+                    const int col = p * 128 + lane * 4;
+                    if (col >= WS_KC) continue;
+                    // rows beyond M and columns beyond K are zeros in the tile (x and the gain are zero there)
+                    const float4 v = x[h][p], g4 = gn[p];
+                    uint2 w;
+                    w.x = ws_pack(g4.x * (v.x * sc), g4.y * (v.y * sc));
+                    w.y = ws_pack(g4.z * (v.z * sc), g4.w * (v.w * sc));
+                    *reinterpret_cast<uint2*>(&xs[m][col]) = w;
+                }
+            }
+        }
+    } else if (normalise) {
         for (int m = warp; m < ROWS; m += 4) {
             float ss = 0.f;
             if (m < M) {
@@ -241,7 +293,9 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
     for (int chunk = 0; chunk < nchunks; ++chunk) {
         // stage the activations of this chunk: ROWS x 256
         __syncthreads();
-        if (normalise) {
+        if (norm_once) {
+            // (the tile was written above)
+        } else if (normalise) {
             for (int c = tid; c < ROWS * (WS_KC / 8); c += 128) {
                 const int row = c / (WS_KC / 8), col = (c % (WS_KC / 8)) * 8;
                 const int k = kbeg + chunk * WS_KC + col;
