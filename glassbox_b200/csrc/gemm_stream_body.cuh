@@ -266,9 +266,18 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             float ss = 0.f;
             if (m < M) {
                 const float* xr = a.xres + (size_t)m * a.ldr;
-                for (int k = lane * 4; k < K; k += 128) {
-                    const float4 v = ld_act<PERSIST>(reinterpret_cast<const float4*>(xr + k));
-                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                // four loads in flight at a time (the instructions issue in order: a load that is used at once
+                // costs its whole latency, every time round); the squares are added in the order of k all the same
+                for (int k0 = lane * 4; k0 < K; k0 += 512) {
+                    float4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        v[u] = k0 + 128 * u < K ? ld_act<PERSIST>(reinterpret_cast<const float4*>(xr + k0 + 128 * u)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss);
+                        ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+                    }
                 }
             }
             ss = gb_warp_sum(ss);
@@ -296,6 +305,8 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
         if (norm_once) {
             // (the tile was written above)
         } else if (normalise) {
+            constexpr int STAGE_UNROLL = NT <= 2 ? NT * WS_KC / 128 : 1;   // (rows are normalised on the way in only up to 16 of them)
+#pragma unroll STAGE_UNROLL
             for (int c = tid; c < ROWS * (WS_KC / 8); c += 128) {
                 const int row = c / (WS_KC / 8), col = (c % (WS_KC / 8)) * 8;
                 const int k = kbeg + chunk * WS_KC + col;
