@@ -48,13 +48,33 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     int r = blockIdx.x;
     if (r >= n) return;
     const float* src = x + (size_t)(rows ? rows[r] : r) * d;
-    float ss = 0.f;
-    for (int j = threadIdx.x; j < d; j += THREADS) {
-        float v = src[j];
-        ss = fmaf(v, v, ss);
-    }
+    TO* dst = out + (size_t)r * d;
     __shared__ float partial[THREADS / 32];
     __shared__ float total;
+    // A row of up to THREADS * 4 * VMAX values whose pieces of four are aligned is read once, every load in
+    // flight at the same time, and normalised from registers (instructions issue in order: a loop that uses each
+    // value as it arrives pays the memory latency once per round). Longer or unaligned rows take two passes.
+    constexpr int VMAX = 4;
+    const bool quick = d % 4 == 0 && d <= THREADS * 4 * VMAX && ((uintptr_t)src & 15) == 0 && ((uintptr_t)gain & 15) == 0;
+    float4 v[VMAX];
+    float ss = 0.f;
+    if (quick) {
+#pragma unroll
+        for (int i = 0; i < VMAX; ++i) {
+            const int j = (i * THREADS + threadIdx.x) * 4;
+            v[i] = j < d ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < VMAX; ++i) {
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += THREADS) {
+            float t = src[j];
+            ss = fmaf(t, t, ss);
+        }
+    }
     ss = gb_warp_sum(ss);
     if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
     __syncthreads();
@@ -66,8 +86,32 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     }
     __syncthreads();
     float s = total;
-    TO* dst = out + (size_t)r * d;
-    for (int j = threadIdx.x; j < d; j += THREADS) dst[j] = gb_from_float<TO>(gain[j] * (src[j] * s));
+    if (quick) {
+#pragma unroll
+        for (int i = 0; i < VMAX; ++i) {
+            const int j = (i * THREADS + threadIdx.x) * 4;
+            if (j < d) {
+                const float4 g = *reinterpret_cast<const float4*>(gain + j);
+                const float y0 = g.x * (v[i].x * s), y1 = g.y * (v[i].y * s), y2 = g.z * (v[i].z * s), y3 = g.w * (v[i].w * s);
+                if constexpr (sizeof(TO) == 2) {
+                    if (((uintptr_t)(dst + j) & 7) == 0) {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+                        uint2 w;
+                        w.x = *reinterpret_cast<uint32_t*>(&lo);
+                        w.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(dst + j) = w;
+                        continue;
+                    }
+                }
+                dst[j] = gb_from_float<TO>(y0);
+                dst[j + 1] = gb_from_float<TO>(y1);
+                dst[j + 2] = gb_from_float<TO>(y2);
+                dst[j + 3] = gb_from_float<TO>(y3);
+            }
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += THREADS) dst[j] = gb_from_float<TO>(gain[j] * (src[j] * s));
+    }
 }
 
 GB_EXPORT int gb_rmsnorm(const float* x, const int* rows, const float* gain, void* out, int out_dtype, int n, int d,

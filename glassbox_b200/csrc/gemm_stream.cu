@@ -118,13 +118,15 @@ static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStr
     const bool wide_fits = nt <= (pair ? 2 : 4);
     int kc = (wide_fits && strips <= slots_of(nt, pair, 512)) ? 512 : 256;
     if (kc == 512 && nt <= 2 && a.K > 512 && a.K <= 640 && strips <= slots_of(nt, pair, 640)) kc = 640;
-    // Cluster size: one block per 512 k, rounded up to a power of two, as long as all blocks are on the
+    // Cluster size: one block per chunk, rounded up to a power of two, as long as all blocks are on the
     // chip at once and the other ranks' sums fit the first block's activation tile. Chunk and cluster
     // size depend on the matrix and on the row bucket (8, 16, 32, 64), not on which rows are in the batch.
     const int max_split = (kc + 32) / 32 / (pair ? 2 : 1) + 1;   // (split - 1) * sets * 32 <= kc + 32
     const int slots = slots_of(nt, pair, kc);
     int split = 1;
-    while (split < 8 && split < a.K / 512) split *= 2;
+    // (with at most 16 rows a block should see one chunk: a second round of staging costs more than the cluster's
+    // two barriers; with more rows the rounds carry real work and one block per 512 k is enough)
+    while (split < 8 && (nt <= 2 ? split * kc < a.K : split < a.K / 512)) split *= 2;
     while (split > 1 && (split > max_split || strips * split > slots)) split /= 2;
     a.kslice = split == 1 ? a.K : ((a.K + split - 1) / split + kc - 1) / kc * kc;
 #define GB_WS2(NTT, KCC) return pair ? launch_stream<NTT, true, KCC>(a, strips, split, pdl, stream) : launch_stream<NTT, false, KCC>(a, strips, split, pdl, stream);

@@ -199,7 +199,14 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
             float inv_rms = 1.0f;
             if (norm.ss_in != nullptr && row < M) {
                 float ss = 0.f;
-                for (int p = 0; p < norm.ss_parts; ++p) ss += norm.ss_in[(size_t)row * norm.ss_parts + p];
+                const float* sp = norm.ss_in + (size_t)row * norm.ss_parts;
+                for (int p0 = 0; p0 < norm.ss_parts; p0 += 8) {   // eight loads in flight; added in the order of p
+                    float part[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) part[u] = p0 + u < norm.ss_parts ? sp[p0 + u] : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) ss += part[u];
+                }
                 inv_rms = 1.0f / sqrtf(ss / (float)K + norm.eps);
             }
             if (kblocks > 0) {

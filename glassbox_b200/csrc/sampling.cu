@@ -35,9 +35,33 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     // Maximum and its first index: coalesced strided reads, ties go to the lower index.
     float best = -FLT_MAX;
     int best_i = vocab;
-    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
-        float v = l[i];
-        if (best_i == vocab || v > best) { best = v; best_i = i; }   // i ascends, so ties keep the lower index
+    if (vocab % 4 == 0 && ((uintptr_t)l & 15) == 0) {
+        // four 16-byte loads in flight per thread (instructions issue in order: a value used as soon as it is asked
+        // for costs the whole trip to memory every time round); a thread's indices still ascend
+        const float4* l4 = reinterpret_cast<const float4*>(l);
+        const int n4 = vocab / 4;
+        for (int i0 = tid; i0 < n4; i0 += 4 * SAMPLE_THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * SAMPLE_THREADS;
+                v[u] = i < n4 ? l4[i] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = (i0 + u * SAMPLE_THREADS) * 4;
+                if (i >= vocab) continue;
+                if (best_i == vocab || v[u].x > best) { best = v[u].x; best_i = i; }
+                if (v[u].y > best) { best = v[u].y; best_i = i + 1; }
+                if (v[u].z > best) { best = v[u].z; best_i = i + 2; }
+                if (v[u].w > best) { best = v[u].w; best_i = i + 3; }
+            }
+        }
+    } else {
+        for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+            float v = l[i];
+            if (best_i == vocab || v > best) { best = v; best_i = i; }   // i ascends, so ties keep the lower index
+        }
     }
     s_val[tid] = best;
     s_idx[tid] = best_i;
