@@ -43,10 +43,31 @@ __global__ void __launch_bounds__(128, (NT == 1 && !PAIR && KC == 512) ? 4 : 0) 
     gemm_stream_body<NT, PAIR, KC, false>(a, (int)blockIdx.x, xs, srow, sync);
 }
 
+// The same product with the rows in groups of eight along the grid's second dimension: block (x, y) does what block x of
+// the one-group kernel does, for rows 8y .. 8y+7 only. Every group reads the weights again (from L2, after the first),
+// so this is for small matrices, where a launch is a matter of latency and the eight-row variant is the fast one:
+// at SmolLM2-135M shapes the four products of a layer take 11.6 us for 8 rows, 18.3 us for 16 rows in one group.
+template <bool PAIR, int KC>
+__global__ void __launch_bounds__(128, (!PAIR && KC == 512) ? 4 : 0) gemm_stream_rows_kernel(const StreamArgs a) {
+    __shared__ __align__(16) unsigned char xs[gemm_stream_smem_bytes<1, KC>()];
+    __shared__ float srow[8];
+    StreamArgs b = a;
+    const int r0 = (int)blockIdx.y * 8;
+    b.M = min(8, a.M - r0);
+    if (a.X != nullptr) b.X = a.X + (size_t)r0 * a.ldx;
+    if (a.xres != nullptr) b.xres = a.xres + (size_t)r0 * a.ldr;
+    const bool c32 = a.mode == WS_STORE_F32 || a.mode == WS_ADD_F32;
+    b.C = c32 ? (void*)(reinterpret_cast<float*>(a.C) + (size_t)r0 * a.ldc) : (void*)(reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)r0 * a.ldc);
+    if (a.positions != nullptr) b.positions = a.positions + r0;
+    if (a.slots != nullptr) b.slots = a.slots + r0;
+    GbPdlSync sync;
+    gemm_stream_body<1, PAIR, KC, false>(b, (int)blockIdx.x, xs, srow, sync);
+}
+
 template <int NT, bool PAIR, int KC>
-static int launch_stream(const StreamArgs& a, int strips, int split, int pdl, cudaStream_t stream) {
+static int launch_stream(const StreamArgs& a, int strips, int split, int pdl, cudaStream_t stream, int groups = 1) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(strips * split);
+    cfg.gridDim = dim3(strips * split, groups);
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -66,7 +87,12 @@ static int launch_stream(const StreamArgs& a, int strips, int split, int pdl, cu
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, PAIR, KC>, a);
+    cudaError_t e;
+    if constexpr (NT == 1) {
+        e = groups > 1 ? cudaLaunchKernelEx(&cfg, gemm_stream_rows_kernel<PAIR, KC>, a) : cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, PAIR, KC>, a);
+    } else {
+        e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, PAIR, KC>, a);
+    }
     if (e != cudaSuccess) {
         gb_set_error("gb_gemm_stream: launch failed: %s", cudaGetErrorString(e));
         return 2;
@@ -108,16 +134,29 @@ static int slots_of(int nt, bool pair, int kc) {
 #undef GB_SL
 }
 
+// Rows in groups of eight (see gemm_stream_rows_kernel): the number of groups, or 1 where one group takes all rows.
+// Taken when the weights, read once per group, stay within a budget that L2 serves easily.
+constexpr long long WS_GROUPED_WEIGHT_BYTES = 40ll << 20;
+static int stream_row_groups(int M, int N, int K, bool pair) {
+    const int groups = (M + 7) / 8;
+    const long long weight_bytes = (long long)N * (pair ? 2 : 1) * K * 2;
+    return (groups > 1 && weight_bytes * groups <= WS_GROUPED_WEIGHT_BYTES) ? groups : 1;
+}
+
+GB_EXPORT int gb_gemm_stream_row_groups(int M, int N, int K, int pair) { return stream_row_groups(M, N, K, pair != 0); }
+
 static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStream_t stream) {
-    const int nt = a.M <= 8 ? 1 : a.M <= 16 ? 2 : a.M <= 32 ? 4 : 8;
+    const int groups = stream_row_groups(a.M, a.mode == WS_ROPE_QKV ? a.N / 2 : a.N, a.K, pair);
+    const int nt = groups > 1 ? 1 : a.M <= 8 ? 1 : a.M <= 16 ? 2 : a.M <= 32 ? 4 : 8;
     // The wide chunk keeps twice the loads in flight per thread, at twice the registers: it is taken
     // where its blocks still fit the chip in one wave (and never by the variants with many rows, which
     // have neither the registers nor the shared memory for it). A K just above 512 (576: SmolLM2-135M)
     // would leave a second chunk of a few columns that costs a whole round of staging and barriers: with at
     // most 16 rows such a K goes through as one chunk of 640.
     const bool wide_fits = nt <= (pair ? 2 : 4);
-    int kc = (wide_fits && strips <= slots_of(nt, pair, 512)) ? 512 : 256;
-    if (kc == 512 && nt <= 2 && a.K > 512 && a.K <= 640 && strips <= slots_of(nt, pair, 640)) kc = 640;
+    const int blocks = strips * groups;   // per block of a cluster
+    int kc = (wide_fits && blocks <= slots_of(nt, pair, 512)) ? 512 : 256;
+    if (kc == 512 && nt <= 2 && a.K > 512 && a.K <= 640 && blocks <= slots_of(nt, pair, 640)) kc = 640;
     // Cluster size: one block per chunk, rounded up to a power of two, as long as all blocks are on the
     // chip at once and the other ranks' sums fit the first block's activation tile. Chunk and cluster
     // size depend on the matrix and on the row bucket (8, 16, 32, 64), not on which rows are in the batch.
@@ -127,9 +166,9 @@ static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStr
     // (with at most 16 rows a block should see one chunk: a second round of staging costs more than the cluster's
     // two barriers; with more rows the rounds carry real work and one block per 512 k is enough)
     while (split < 8 && (nt <= 2 ? split * kc < a.K : split < a.K / 512)) split *= 2;
-    while (split > 1 && (split > max_split || strips * split > slots)) split /= 2;
+    while (split > 1 && (split > max_split || blocks * split > slots)) split /= 2;
     a.kslice = split == 1 ? a.K : ((a.K + split - 1) / split + kc - 1) / kc * kc;
-#define GB_WS2(NTT, KCC) return pair ? launch_stream<NTT, true, KCC>(a, strips, split, pdl, stream) : launch_stream<NTT, false, KCC>(a, strips, split, pdl, stream);
+#define GB_WS2(NTT, KCC) return pair ? launch_stream<NTT, true, KCC>(a, strips, split, pdl, stream, groups) : launch_stream<NTT, false, KCC>(a, strips, split, pdl, stream, groups);
 #define GB_WS(NTT) if (kc == 512) { GB_WS2(NTT, 512) } else { GB_WS2(NTT, 256) }
 #define GB_WS3(NTT) if (kc == 640) { GB_WS2(NTT, 640) } else GB_WS(NTT)
     if (nt == 1) { GB_WS3(1) }

@@ -179,7 +179,7 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             // While this kernel waits for its predecessor and works, the weights of a kernel further down
             // the stream travel from HBM to L2: each block asks for its share, one 128-byte line per thread.
             const long long lines = (a.prefetch_bytes + 127) / 128;
-            for (long long i = (long long)blockIdx.x * 128 + tid; i < lines; i += (long long)gridDim.x * 128)
+            for (long long i = (long long)blockIdx.x * 128 + tid; i < lines && blockIdx.y == 0; i += (long long)gridDim.x * 128)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(a.prefetch + i * 128));
         }
         // Rotary mode: a row's position, its (cos, sin) pair and its cache slot are step metadata that no kernel

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "gb_attention_decode": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                             _P, _P, _P],
     "gb_attention_decode_counters": [_I, _I, _I],
+    "gb_gemm_stream_row_groups": [_I, _I, _I, _I],
     "gb_gemm_stream": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _LL, _I, _P],
     "gb_gemm_stream_qkv": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                            _LL, _I, _P, _P, _LL, _I, _P],
@@ -364,8 +365,21 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: boo
 
 STREAM_MAX_ROWS = 64
 #: above this many rows the norm is not folded into the stream kernels (every block would repeat
-#: the normalisation of all rows) and QKV keeps one strip per block (twice the blocks)
+#: the normalisation of all rows) and QKV keeps one strip per block (twice the blocks) -- unless the
+#: kernel takes the rows in groups of eight (``stream_folds``)
 STREAM_FUSE_MAX_ROWS = 16
+
+
+def stream_row_groups(rows: int, w: torch.Tensor) -> int:
+    """In how many groups of eight rows the weight-streaming kernel runs a product of ``rows`` rows with ``w`` (1: all
+    rows in one group). Small matrices are taken group by group: every block then works as for eight rows."""
+    return int(lib().gb_gemm_stream_row_groups(rows, w.shape[0], w.shape[1], 0))
+
+
+def stream_folds(rows: int, w: torch.Tensor) -> bool:
+    """Whether a norm in front of this product (and rotation and the cache write behind a QKV product) is folded into
+    the weight-streaming kernel: with few rows, or when the rows go in groups of eight."""
+    return rows <= STREAM_FUSE_MAX_ROWS or (rows <= STREAM_MAX_ROWS and stream_row_groups(rows, w) > 1)
 
 
 #: launch the decode-path kernels under programmatic stream serialisation (they wait for their
@@ -429,7 +443,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
 
 
 def gemm_stream_qkv_supported(a, w: torch.Tensor, hd: int, q_out: torch.Tensor) -> bool:
-    return (gemm_stream_supported(a, w) and a.shape[0] <= STREAM_FUSE_MAX_ROWS and hd % 32 == 0
+    return (gemm_stream_supported(a, w) and stream_folds(a.shape[0], w) and hd % 32 == 0
             and q_out.dtype == torch.bfloat16)
 
 

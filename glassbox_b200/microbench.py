@@ -8,6 +8,7 @@ over operands that rotate through more memory than L2 holds.
     python -m glassbox_b200.microbench float32                           the 32-bit path's kernels: FMA GEMM, decode and rows attention
     python -m glassbox_b200.microbench small                             embedding, RMSNorm, rotation + cache write, SwiGLU, sampling
     python -m glassbox_b200.microbench decode_program [batch ...]        a decode step as a kernel chain and as a persistent kernel
+    python -m glassbox_b200.microbench layer_gemms [rows ...]            the four products of a decode layer as the layer runs them
 
 Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops. With ``--once`` after
 the case's name every kernel is launched exactly once and nothing is timed: the form in which a profiler captures one
@@ -292,7 +293,54 @@ def bench_decode_program(batches) -> None:
         shutil.rmtree(tmp, ignore_errors=True)
 
 
-CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill", "float32", "small", "decode_program")
+def bench_layer_gemms(rows) -> None:
+    """The four products of one SmolLM2-135M decode layer with what the layer folds into them: the norm on the way in,
+    rotation and cache write on the way out of QKV, SwiGLU, the residual additions; each alone (back to back in a
+    graph, cold weights) and the four in a row."""
+    from .parts.rope import rotary_table
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    d, inter, nh, nkv, hd, ps = 576, 1536, 9, 3, 64, 16
+    for m in rows or (1, 8, 16):
+        res = torch.randn(m, d, device=DEV)
+        gain = torch.ones(d, device=DEV)
+        xb = torch.randn(m, d, device=DEV).bfloat16()
+        wq, wo, wg, wd = _rotating(960, d), _rotating(d, d), _rotating(2 * inter, d), _rotating(d, inter)
+        qkv = torch.empty(m, 960, device=DEV, dtype=torch.bfloat16)
+        act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+        table = rotary_table(1e5, hd, 8192).to(DEV)
+        pos = torch.full((m,), 4000, dtype=torch.int32, device=DEV)
+        slots = torch.arange(m, dtype=torch.int32, device=DEV) * ps
+        kc = torch.zeros(m + 2, nkv, ps, hd, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        turn = [0]
+
+        def nxt(ws):
+            turn[0] += 1
+            return ws[turn[0] % len(ws)]
+
+        def qkv_full():
+            kernels.gemm_stream_qkv(res, nxt(wq), qkv, table, pos, slots, kc, vc, nh, nkv, hd, ps, True, st, norm=(gain, 1e-5))
+
+        def layer():
+            qkv_full()
+            kernels.gemm_stream(qkv[:, :d], nxt(wo), res, True)
+            kernels.gemm_stream(res, nxt(wg), act, gated=True, norm=(gain, 1e-5))
+            kernels.gemm_stream(act, nxt(wd), res, True)
+
+        t = [graph_time(lambda: kernels.gemm_stream(xb, nxt(wq), qkv)),
+             graph_time(lambda: kernels.gemm_stream(res, nxt(wq), qkv, norm=(gain, 1e-5))),
+             graph_time(qkv_full),
+             graph_time(lambda: kernels.gemm_stream(xb, nxt(wo), res, True)),
+             graph_time(lambda: kernels.gemm_stream(xb, nxt(wg), act, gated=True)),
+             graph_time(lambda: kernels.gemm_stream(res, nxt(wg), act, gated=True, norm=(gain, 1e-5))),
+             graph_time(lambda: kernels.gemm_stream(act, nxt(wd), res, True)),
+             graph_time(layer, reps=8)]
+        print(f"rows {m:2d}: qkv {t[0]:.2f} us, + norm {t[1]:.2f}, + rotation and cache write {t[2]:.2f} | o + residual {t[3]:.2f} | "
+              f"gate/up + SwiGLU {t[4]:.2f}, + norm {t[5]:.2f} | down + residual {t[6]:.2f} | the four in a row {t[7]:.2f}", flush=True)
+    kernels.check_status(st)
+
+
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill", "float32", "small", "decode_program", "layer_gemms")
 
 
 def main(argv) -> int:
@@ -317,6 +365,8 @@ def main(argv) -> int:
         bench_small()
     elif argv[0] == "decode_program":
         bench_decode_program([int(x) for x in argv[1:]])
+    elif argv[0] == "layer_gemms":
+        bench_layer_gemms([int(x) for x in argv[1:]])
     else:
         bench_attention_prefill()
     return 0

@@ -50,7 +50,7 @@ class GqaAttention(Mixer):
         n = h.shape[0]
         qkv = ctx.scratch("qkv", (n, self.qd + 2 * self.kvd))
         table = self.position.fused_table(qkv.device)
-        x, norm, _, scale = _resolve(h)
+        x, norm, _, scale = _resolve(h, self.params["wqkv"])
         plain_rotary = (table is not None and self.position.rotary_dim == self.hd) or \
             (table is None and type(self.position).apply_qk is Position.apply_qk)
         if (plain_rotary and (norm is not None or x.dtype == torch.bfloat16)

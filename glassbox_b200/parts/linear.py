@@ -20,13 +20,15 @@ def weights_ahead(ctx, w: torch.Tensor):
     return order.ahead(w) if order is not None else None
 
 
-def _resolve(a):
-    """(tensor, norm or None, deferred or None, row scale or None) for an input that may be a ``DeferredNorm``:
+def _resolve(a, w=None):
+    """(tensor, norm or None, deferred or None, row scale or None) for an input that may be a ``DeferredNorm``
+    in front of a product with ``w``:
     the residual rows with the norm that the stream kernel applies on the way in (few rows); or the rows that the
     product before prepared, with the scale that a tile kernel applies on the way out; or the normalised rows."""
     if isinstance(a, DeferredNorm):
         rms = a.norm.as_rms()
-        if rms is not None and a._tensor is None and a.x.shape[0] <= kernels.STREAM_FUSE_MAX_ROWS:
+        if rms is not None and a._tensor is None and (
+                kernels.stream_folds(a.x.shape[0], w) if w is not None else a.x.shape[0] <= kernels.STREAM_FUSE_MAX_ROWS):
             return a.x, rms, a, None
         ready = a.prepared()
         if ready is not None:
@@ -63,7 +65,7 @@ def _tile_kernel_wins(rows: int, w: torch.Tensor) -> bool:
 def linear(ctx, a, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """``a`` is a tensor or a ``DeferredNorm``; the latter is folded into the weight-streaming kernel
     when that kernel runs, and computed first otherwise."""
-    x, norm, deferred, scale = _resolve(a)
+    x, norm, deferred, scale = _resolve(a, w)
     if accumulate:
         ctx.prepared_norm = None      # ``out`` changes: what was prepared from its old values is void
     if scale is not None:
@@ -93,7 +95,7 @@ def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
     """act = silu(a Wgate^T) * (a Wup^T) in one kernel when the shape allows; returns False (and
     does nothing) otherwise, and the caller runs the product and the activation separately."""
     inter = w_gate_up.shape[0] // 2
-    x, norm, _, scale = _resolve(a)
+    x, norm, _, scale = _resolve(a, w_gate_up)
     if scale is not None:
         if (w_gate_up.dtype == torch.bfloat16 and act.dtype == torch.bfloat16
                 and kernels.gemm_tc_supported(x, w_gate_up, act)):
