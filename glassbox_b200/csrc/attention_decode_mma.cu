@@ -120,7 +120,7 @@ GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, voi
     GB_REQUIRE((long long)num_pages * nkv * page_size < (1ll << 31), "gb_attention_decode_mma: the cache has too many rows");
     GB_REQUIRE(max_pages > 0 && splits >= 1 && part_acc && part_ml && counters,
                "gb_attention_decode_mma: bad page geometry, split count or scratch");
-    GB_REQUIRE(warps == 4 || (warps == 8 && hd == 64 && block_keys != 16), "gb_attention_decode_mma: %d warps per block are not built for this variant (4; 8 at head size 64 with 32 keys per iteration)", warps);
+    GB_REQUIRE(warps == 4 || (warps == 8 && hd == 64), "gb_attention_decode_mma: %d warps per block are not built for this variant (4; 8 at head size 64)", warps);
     GB_REQUIRE(n <= 65535 && splits <= MMA_MAX_MERGE / warps, "gb_attention_decode_mma: too many rows or splits for one launch");
     GB_REQUIRE(q_stride % 4 == 0 && (uintptr_t)q % 8 == 0, "gb_attention_decode_mma: q must be 8-byte aligned");
     if (n == 0) return 0;
@@ -132,6 +132,7 @@ GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, voi
     if (hd == 16) { GB_MMA(16, 32) }
     if (hd == 32) { GB_MMA(32, 32) }
     if (hd == 64) {
+        if (block_keys == 16 && warps == 8) { GB_MMAW(64, 16, 8) }   // a small batch: one block per SM that leaves room beside it
         if (block_keys == 16) { GB_MMA(64, 16) }   // fewer registers, three blocks per SM: better for large batches
         if (warps == 8) { GB_MMAW(64, 32, 8) }     // a small batch: one block per SM, twice the warps
         GB_MMA(64, 32)
