@@ -36,19 +36,20 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     float best = -FLT_MAX;
     int best_i = vocab;
     if (vocab % 4 == 0 && ((uintptr_t)l & 15) == 0) {
-        // four 16-byte loads in flight per thread (instructions issue in order: a value used as soon as it is asked
+        // twelve 16-byte loads in flight per thread (instructions issue in order: a value used as soon as it is asked
         // for costs the whole trip to memory every time round); a thread's indices still ascend
         const float4* l4 = reinterpret_cast<const float4*>(l);
         const int n4 = vocab / 4;
-        for (int i0 = tid; i0 < n4; i0 += 4 * SAMPLE_THREADS) {
-            float4 v[4];
+        constexpr int FLY = 12;   // 16-byte loads in flight per thread
+        for (int i0 = tid; i0 < n4; i0 += FLY * SAMPLE_THREADS) {
+            float4 v[FLY];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < FLY; ++u) {
                 const int i = i0 + u * SAMPLE_THREADS;
                 v[u] = i < n4 ? l4[i] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < FLY; ++u) {
                 const int i = (i0 + u * SAMPLE_THREADS) * 4;
                 if (i >= vocab) continue;
                 if (best_i == vocab || v[u].x > best) { best = v[u].x; best_i = i; }
@@ -63,21 +64,34 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
             if (best_i == vocab || v > best) { best = v; best_i = i; }   // i ascends, so ties keep the lower index
         }
     }
-    s_val[tid] = best;
-    s_idx[tid] = best_i;
-    __syncthreads();
-    for (int s = SAMPLE_THREADS / 2; s > 0; s >>= 1) {
-        if (tid < s) {
-            float ov = s_val[tid + s];
-            int oi = s_idx[tid + s];
-            const int ci = s_idx[tid];
-            if (oi < vocab && (ci == vocab || ov > s_val[tid] || (ov == s_val[tid] && oi < ci))) {  // ties: lower index
-                s_val[tid] = ov;
-                s_idx[tid] = oi;
-            }
-        }
-        __syncthreads();
+    // the maximum with its first index: inside each warp with shuffles, then over the sixteen warps (ties: lower index)
+    auto better = [&](float ov, int oi, float cv, int ci) { return oi < vocab && (ci == vocab || ov > cv || (ov == cv && oi < ci)); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_down_sync(0xffffffffu, best, o);
+        const int oi = __shfl_down_sync(0xffffffffu, best_i, o);
+        if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
     }
+    if ((tid & 31) == 0) {
+        s_val[tid >> 5] = best;
+        s_idx[tid >> 5] = best_i;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        float cv = tid < SAMPLE_THREADS / 32 ? s_val[tid] : -FLT_MAX;
+        int ci = tid < SAMPLE_THREADS / 32 ? s_idx[tid] : vocab;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_down_sync(0xffffffffu, cv, o);
+            const int oi = __shfl_down_sync(0xffffffffu, ci, o);
+            if (better(ov, oi, cv, ci)) { cv = ov; ci = oi; }
+        }
+        if (tid == 0) {
+            s_val[0] = cv;
+            s_idx[0] = ci;
+        }
+    }
+    __syncthreads();
     const float vmax = s_val[0];
     const int imax = s_idx[0];
     __shared__ float s_draw[2];   // temperature, uniform
