@@ -318,86 +318,20 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     }
     const int sub = split * NW + warp;
     float* weights = sm.weights;
-    float* head_block = nullptr;   // CLUSTER: the partial results' place in the first block's shared memory
     if constexpr (CLUSTER) {
-        head_block = cooperative_groups::this_cluster().map_shared_rank(cluster_part, 0);
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        // [head of the group][sub-split][HD channels, maximum, sum] in the first block's shared memory
+        float* first = cluster.map_shared_rank(cluster_part, 0);
         asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
-    }
-    // Partial results per head that travel on (to global memory, or to the cluster's first block): one per warp of every
-    // split, or, where the block's warps can first be merged in shared memory (the merge's weight array doubles as the
-    // staging area), one per split. The arithmetic is the same whichever way they travel.
-    int SP = S4;
-    if (NW * G * (HD + 2) <= MMA_MAX_MERGE) {
-        float* stage = weights;   // [warp][head of the group][HD channels, maximum, sum]
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int hi = g + 8 * h;
             if (hi < G) {
-                float* ps = stage + (warp * G + hi) * (HD + 2);
+                float* pa = first + ((size_t)hi * S4 + sub) * (HD + 2);
                 if (t == 0) {
-                    ps[HD] = m_run[h];
-                    ps[HD + 1] = l_run[h];
-                }
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    ps[NT * (2 * t) + j] = acc[j][2 * h];
-                    ps[NT * (2 * t + 1) + j] = acc[j][2 * h + 1];
-                }
-            }
-        }
-        sync.group_barrier();
-        for (int i = tid; i < G * HD; i += NTHREADS) {
-            const int hi = i / HD, d = i % HD;
-            float m = MMA_NEG_BIG;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) m = fmaxf(m, stage[(w * G + hi) * (HD + 2) + HD]);
-            float o = 0.f, l = 0.f;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) {          // in warp order: the sum does not depend on timing
-                const float* ps = stage + (w * G + hi) * (HD + 2);
-                const float wgt = __expf(ps[HD] - m);
-                o = fmaf(ps[d], wgt, o);
-                l = fmaf(ps[HD + 1], wgt, l);
-            }
-            if (splits == 1) {                      // nothing else to wait for: the row is complete
-                orow[(head0 + hi) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
-            } else if constexpr (CLUSTER) {
-                float* pa = head_block + ((size_t)hi * splits + split) * (HD + 2);
-                pa[d] = o;
-                if (d == 0) {
-                    pa[HD] = m;
-                    pa[HD + 1] = l;
-                }
-            } else {
-                const size_t slot = ((size_t)row * nh + head0 + hi) * splits + split;
-                part_acc[slot * HD + d] = o;
-                if (d == 0) {
-                    part_ml[slot * 2] = m;
-                    part_ml[slot * 2 + 1] = l;
-                }
-            }
-        }
-        if (splits == 1) return;
-        SP = splits;
-        sync.group_barrier();                       // the staging area becomes the weight array again below
-    } else {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int hi = g + 8 * h;
-            if (hi < G) {
-                float* pa;
-                float* pml;
-                if constexpr (CLUSTER) {
-                    pa = head_block + ((size_t)hi * S4 + sub) * (HD + 2);
-                    pml = pa + HD;
-                } else {
-                    const size_t slot = ((size_t)row * nh + head0 + hi) * S4 + sub;
-                    pa = part_acc + slot * HD;
-                    pml = part_ml + slot * 2;
-                }
-                if (t == 0) {
-                    pml[0] = m_run[h];
-                    pml[1] = l_run[h];
+                    pa[HD] = m_run[h];
+                    pa[HD + 1] = l_run[h];
                 }
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
@@ -406,41 +340,53 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
                 }
             }
         }
-    }
-    if constexpr (CLUSTER) {
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        // [head of the group][partial result][HD channels, maximum, sum] in the first block's shared memory
         cluster.sync();                       // (release / acquire: the first block sees what the others stored)
         if (cluster.block_rank() != 0) return;
         // one warp per head turns the (maximum, sum) pairs into normalised weights; then every thread adds up its channel
         for (int hi = warp; hi < G; hi += NW) {
-            const float* ph = cluster_part + (size_t)hi * SP * (HD + 2);
+            const float* ph = cluster_part + (size_t)hi * S4 * (HD + 2);
             float m = MMA_NEG_BIG;
-            for (int sidx = lane; sidx < SP; sidx += 32) m = fmaxf(m, ph[sidx * (HD + 2) + HD]);
+            for (int sidx = lane; sidx < S4; sidx += 32) m = fmaxf(m, ph[sidx * (HD + 2) + HD]);
             m = gb_warp_max(m);
             float l = 0.f;
-            for (int sidx = lane; sidx < SP; sidx += 32) {
+            for (int sidx = lane; sidx < S4; sidx += 32) {
                 const float w = __expf(ph[sidx * (HD + 2) + HD] - m);
-                weights[hi * SP + sidx] = w;
+                weights[hi * S4 + sidx] = w;
                 l = fmaf(ph[sidx * (HD + 2) + HD + 1], w, l);
             }
             l = gb_warp_sum(l);
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             __syncwarp();
-            for (int sidx = lane; sidx < SP; sidx += 32) weights[hi * SP + sidx] *= inv;
+            for (int sidx = lane; sidx < S4; sidx += 32) weights[hi * S4 + sidx] *= inv;
         }
         sync.group_barrier();
         for (int i = tid; i < G * HD; i += NTHREADS) {
             const int hi = i / HD, d = i % HD;
-            const float* pa = cluster_part + (size_t)hi * SP * (HD + 2) + d;
-            const float* w = weights + hi * SP;
+            const float* pa = cluster_part + (size_t)hi * S4 * (HD + 2) + d;
+            const float* w = weights + hi * S4;
             float v = 0.f;
 #pragma unroll 8
-            for (int sidx = 0; sidx < SP; ++sidx) v = fmaf(pa[(size_t)sidx * (HD + 2)], w[sidx], v);
+            for (int sidx = 0; sidx < S4; ++sidx) v = fmaf(pa[(size_t)sidx * (HD + 2)], w[sidx], v);
             orow[(head0 + hi) * HD + d] = __float2bfloat16_rn(v);
         }
         return;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int hi = g + 8 * h;
+        if (hi < G) {
+            const size_t slot = ((size_t)row * nh + head0 + hi) * S4 + sub;
+            if (t == 0) {
+                part_ml[slot * 2] = m_run[h];
+                part_ml[slot * 2 + 1] = l_run[h];
+            }
+            float* pa = part_acc + slot * HD;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                pa[NT * (2 * t) + j] = acc[j][2 * h];
+                pa[NT * (2 * t + 1) + j] = acc[j][2 * h + 1];
+            }
+        }
     }
     // ---- the block that arrives last merges every warp of every split
     __threadfence();
@@ -457,7 +403,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     // Merge: one warp per head turns the (maximum, sum) pairs of all sub-splits into normalised
     // weights in shared memory; then every thread adds up its channel over the sub-splits with
     // independent loads.
-    if (G * HD <= NTHREADS && SP <= 64) {
+    if (G * HD <= NTHREADS && S4 <= 64) {
         // The usual case (every output channel of the group has a thread of its own, at most 64 partial results per
         // head): a thread asks for its channel of every partial result at once, before the weights exist, and a lane
         // reads its (maximum, sum) pairs once; the merge is then two trips to L2 that overlap instead of four in a row.
@@ -465,59 +411,59 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
         const int hi_o = tid / HD, d_o = tid % HD;
         float pv[MAXP];
         if (tid < G * HD) {
-            const float* pa = part_acc + ((size_t)row * nh + head0 + hi_o) * SP * HD + d_o;
+            const float* pa = part_acc + ((size_t)row * nh + head0 + hi_o) * S4 * HD + d_o;
 #pragma unroll
-            for (int sidx = 0; sidx < MAXP; ++sidx) pv[sidx] = sidx < SP ? __ldcg(pa + (size_t)sidx * HD) : 0.f;
+            for (int sidx = 0; sidx < MAXP; ++sidx) pv[sidx] = sidx < S4 ? __ldcg(pa + (size_t)sidx * HD) : 0.f;
         }
         for (int hi = warp; hi < G; hi += NW) {
-            const float2* ml = reinterpret_cast<const float2*>(part_ml + ((size_t)row * nh + head0 + hi) * SP * 2);
-            const float2 p0 = lane < SP ? __ldcg(ml + lane) : make_float2(MMA_NEG_BIG, 0.f);
-            const float2 p1 = lane + 32 < SP ? __ldcg(ml + lane + 32) : make_float2(MMA_NEG_BIG, 0.f);
+            const float2* ml = reinterpret_cast<const float2*>(part_ml + ((size_t)row * nh + head0 + hi) * S4 * 2);
+            const float2 p0 = lane < S4 ? __ldcg(ml + lane) : make_float2(MMA_NEG_BIG, 0.f);
+            const float2 p1 = lane + 32 < S4 ? __ldcg(ml + lane + 32) : make_float2(MMA_NEG_BIG, 0.f);
             const float m = gb_warp_max(fmaxf(p0.x, p1.x));
             const float w0 = __expf(p0.x - m), w1 = __expf(p1.x - m);
             const float l = gb_warp_sum(fmaf(p0.y, w0, p1.y * w1));
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            if (lane < SP) weights[hi * SP + lane] = w0 * inv;
-            if (lane + 32 < SP) weights[hi * SP + lane + 32] = w1 * inv;
+            if (lane < S4) weights[hi * S4 + lane] = w0 * inv;
+            if (lane + 32 < S4) weights[hi * S4 + lane + 32] = w1 * inv;
         }
         sync.group_barrier();
         if (tid < G * HD) {
-            const float* w = weights + hi_o * SP;
+            const float* w = weights + hi_o * S4;
             float v = 0.f;
 #pragma unroll
             for (int sidx = 0; sidx < MAXP; ++sidx)
-                if (sidx < SP) v = fmaf(pv[sidx], w[sidx], v);
+                if (sidx < S4) v = fmaf(pv[sidx], w[sidx], v);
             orow[(head0 + hi_o) * HD + d_o] = __float2bfloat16_rn(v);
         }
         return;
     }
-    const int per_pass = MMA_MAX_MERGE / SP;                 // heads whose weights fit at once
+    const int per_pass = MMA_MAX_MERGE / S4;                 // heads whose weights fit at once
     for (int h0 = 0; h0 < G; h0 += per_pass) {
         const int hcount = min(per_pass, G - h0);
         for (int hi = warp; hi < hcount; hi += NW) {
-            const float* ml = part_ml + ((size_t)row * nh + head0 + h0 + hi) * SP * 2;
+            const float* ml = part_ml + ((size_t)row * nh + head0 + h0 + hi) * S4 * 2;
             float m = MMA_NEG_BIG;
-            for (int sidx = lane; sidx < SP; sidx += 32) m = fmaxf(m, __ldcg(ml + 2 * sidx));
+            for (int sidx = lane; sidx < S4; sidx += 32) m = fmaxf(m, __ldcg(ml + 2 * sidx));
             m = gb_warp_max(m);
             float l = 0.f;
-            for (int sidx = lane; sidx < SP; sidx += 32) {
+            for (int sidx = lane; sidx < S4; sidx += 32) {
                 const float w = __expf(__ldcg(ml + 2 * sidx) - m);
-                weights[hi * SP + sidx] = w;
+                weights[hi * S4 + sidx] = w;
                 l = fmaf(__ldcg(ml + 2 * sidx + 1), w, l);
             }
             l = gb_warp_sum(l);
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             __syncwarp();
-            for (int sidx = lane; sidx < SP; sidx += 32) weights[hi * SP + sidx] *= inv;
+            for (int sidx = lane; sidx < S4; sidx += 32) weights[hi * S4 + sidx] *= inv;
         }
         sync.group_barrier();
         for (int i = tid; i < hcount * HD; i += NTHREADS) {
             const int hi = i / HD, d = i % HD;
-            const float* pa = part_acc + ((size_t)row * nh + head0 + h0 + hi) * SP * HD + d;
-            const float* w = weights + hi * SP;
+            const float* pa = part_acc + ((size_t)row * nh + head0 + h0 + hi) * S4 * HD + d;
+            const float* w = weights + hi * S4;
             float v = 0.f;
 #pragma unroll 8
-            for (int sidx = 0; sidx < SP; ++sidx) v = fmaf(__ldcg(pa + (size_t)sidx * HD), w[sidx], v);
+            for (int sidx = 0; sidx < S4; ++sidx) v = fmaf(__ldcg(pa + (size_t)sidx * HD), w[sidx], v);
             orow[(head0 + h0 + hi) * HD + d] = __float2bfloat16_rn(v);
         }
         sync.group_barrier();

@@ -635,8 +635,8 @@ def attention_decode_mma_supported(dtype: torch.dtype, nh: int, nkv: int, hd: in
 
 def decode_mma_plan(n: int, nkv: int, hd: int, max_context: int):
     """(splits, keys per warp iteration, warps per block) for the tensor-core decode kernel. A small batch needs
-    many blocks per (row, kv head) to fill the GPU; with four warps each block keeps at least 512 keys, below
-    which the fixed cost of a block and of the merge outweighs the parallelism; where there is at most one block
+    many blocks per (row, kv head) to fill the GPU, but each block keeps at least 512 keys, below which the
+    fixed cost of a block and of the merge outweighs the parallelism; where that leaves at most one block
     per SM, a block has eight warps instead of four, so that each warp walks through half as many keys (the
     splits are then rounded down: a second block of eight warps does not fit beside the first). A batch that
     fills the GPU by itself takes the 16-key variant (three blocks per SM instead of two) and few splits.
@@ -648,15 +648,15 @@ def decode_mma_plan(n: int, nkv: int, hd: int, max_context: int):
         return max(1, min(-(-296 // pairs), most)), 16, 4
     if hd == 64 and pairs <= 74:
         # (measured at 9/3 heads, microseconds at context 4096 with 4 warps and the old split count against 8 warps:
-        # batch 8 18.8 -> 12.4, batch 16 18.2 -> 15.1, batch 4 12.7 -> 11.3. Since a block merges its warps in shared
-        # memory before anything leaves it, more splits cost little: batch 1, 8 / 16 / 24 / 32 splits: 8.1 / 6.7 / 6.4 /
-        # 6.6; a block keeps at least 128 keys, one iteration of 16 per warp)
+        # batch 8 18.8 -> 12.4, batch 16 18.2 -> 15.1, batch 4 12.7 -> 11.3; eight warps want at least 256 keys a block
+        # and at most 8 splits: context 1024, batch 8: 2 splits 9.3, 4 splits 8.6; context 4096, batch 1: 8 splits
+        # 11.1, 16 splits 12.4)
         # 16 keys per iteration: 160 registers per thread instead of 251, so that a block no longer fills an SM's
         # register file and the product that follows finds room beside it while it waits for it (alone the two variants
         # take the same time; in a 135M decode step: batch 1 0.73 -> 0.65 ms, batch 8 0.80 -> 0.78 ms)
         # (with more than 1,024 keys per block the longer loop of the 16-key variant costs more than the room gains:
         # 360M shapes at batch 8, three splits of 1,365 keys: 1.23 ms with 32 keys per iteration, 1.27 ms with 16)
-        splits = max(1, min(148 // pairs, 24, max_context // 128))
+        splits = max(1, min(148 // pairs, 8, -(-max_context // 256)))
         return splits, (16 if max_context <= 1024 * splits else 0), 8
     return max(1, min(-(-148 // pairs), most)), 0, 4
 
