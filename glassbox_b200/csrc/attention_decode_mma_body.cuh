@@ -197,8 +197,12 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
 #pragma unroll
         for (int s = 0; s < KS; ++s) {
             uint2 a = make_uint2(0, 0), b = make_uint2(0, 0);   // (shadow the argument block inside this scope)
-            if (g < G) a = __ldcg(reinterpret_cast<const uint2*>(q0 + 16 * s + 4 * t));
-            if (g + 8 < G) b = __ldcg(reinterpret_cast<const uint2*>(q1 + 16 * s + 4 * t));
+            // the four channels that stand for this thread's k indices of step s: any assignment works as long as the
+            // keys use the same one; with an even number of steps a thread's channels of two steps are 8 in a row, so
+            // that a key's share is one 16-byte load
+            const int ch = KS % 2 == 0 ? 32 * (s >> 1) + 8 * t + 4 * (s & 1) : 16 * s + 4 * t;
+            if (g < G) a = __ldcg(reinterpret_cast<const uint2*>(q0 + ch));
+            if (g + 8 < G) b = __ldcg(reinterpret_cast<const uint2*>(q1 + ch));
             qf[s][0] = a.x; qf[s][1] = b.x; qf[s][2] = a.y; qf[s][3] = b.y;
         }
     }
@@ -230,9 +234,19 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
         for (int b = 0; b < KB; ++b) hb[b] = half_block_row(base + 16 * b);
 #pragma unroll
         for (int j = 0; j < KT; ++j) {
-            const __nv_bfloat16* kp = kcache + (long long)(hb[j >> 1] + 8 * (j & 1) + g) * HD + 4 * t;
+            if constexpr (KS % 2 == 0) {
+                const __nv_bfloat16* kp = kcache + (long long)(hb[j >> 1] + 8 * (j & 1) + g) * HD + 8 * t;
 #pragma unroll
-            for (int s = 0; s < KS; ++s) B.kf[j][s] = *reinterpret_cast<const uint2*>(kp + 16 * s);
+                for (int s2 = 0; s2 < KS / 2; ++s2) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(kp + 32 * s2);
+                    B.kf[j][2 * s2] = make_uint2(v.x, v.y);
+                    B.kf[j][2 * s2 + 1] = make_uint2(v.z, v.w);
+                }
+            } else {
+                const __nv_bfloat16* kp = kcache + (long long)(hb[j >> 1] + 8 * (j & 1) + g) * HD + 4 * t;
+#pragma unroll
+                for (int s = 0; s < KS; ++s) B.kf[j][s] = *reinterpret_cast<const uint2*>(kp + 16 * s);
+            }
         }
 #pragma unroll
         for (int b = 0; b < KB; ++b)
