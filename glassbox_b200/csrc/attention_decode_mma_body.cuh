@@ -47,6 +47,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Keys and values are read once: they leave no line behind in L1 (which keeps the small things that are read again:
+// page ids, the products' activations). An ordinary load, not a read-only one: in a persistent kernel another block
+// of the same launch has written this step's keys and values.
+__device__ __forceinline__ uint4 kv_load16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 template <int WORDS> struct RowLoad;  // WORDS 32-bit words of a value row, widest loads possible
 template <> struct RowLoad<1> {
     static __device__ __forceinline__ void load(const __nv_bfloat16* p, uint32_t (&w)[1]) {
@@ -61,7 +70,7 @@ template <> struct RowLoad<2> {
 };
 template <> struct RowLoad<4> {
     static __device__ __forceinline__ void load(const __nv_bfloat16* p, uint32_t (&w)[4]) {
-        uint4 v = *reinterpret_cast<const uint4*>(p);
+        uint4 v = kv_load16(p);
         w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     }
 };
@@ -238,7 +247,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
                 const __nv_bfloat16* kp = kcache + (long long)(hb[j >> 1] + 8 * (j & 1) + g) * HD + 8 * t;
 #pragma unroll
                 for (int s2 = 0; s2 < KS / 2; ++s2) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(kp + 32 * s2);
+                    const uint4 v = kv_load16(kp + 32 * s2);
                     B.kf[j][2 * s2] = make_uint2(v.x, v.y);
                     B.kf[j][2 * s2 + 1] = make_uint2(v.z, v.w);
                 }
