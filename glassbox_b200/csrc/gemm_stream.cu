@@ -156,7 +156,9 @@ static int dispatch_stream(StreamArgs a, int strips, bool pair, int pdl, cudaStr
     const bool wide_fits = nt <= (pair ? 2 : 4);
     const int blocks = strips * groups;   // per block of a cluster
     int kc = (wide_fits && blocks <= slots_of(nt, pair, 512)) ? 512 : 256;
-    if (kc == 512 && nt <= 2 && a.K > 512 && a.K <= 640 && blocks <= slots_of(nt, pair, 640)) kc = 640;
+    // (a launch of several row groups takes the one-round chunk even where its blocks then come in more than one wave:
+    // 135M shapes, 64 rows, the four products of a layer: 24.9 -> 21.3 us)
+    if (nt <= 2 && a.K > 512 && a.K <= 640 && (groups > 1 || (kc == 512 && blocks <= slots_of(nt, pair, 640)))) kc = 640;
     // Cluster size: one block per chunk, rounded up to a power of two, as long as all blocks are on the
     // chip at once and the other ranks' sums fit the first block's activation tile. Chunk and cluster
     // size depend on the matrix and on the row bucket (8, 16, 32, 64), not on which rows are in the batch.
