@@ -28,6 +28,7 @@ struct DecodeAttnArgs {
     int* status;
     int n;           // rows (used by the persistent kernel to count its virtual blocks)
     int hd, block_keys;
+    int late_release;   // let the next kernel in the stream go only after this one's own wait (else at its start)
 };
 
 constexpr float MMA_NEG_BIG = -1.0e30f;
@@ -136,10 +137,11 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     const int S4 = splits * NW;   // partial results per head: one per warp of every split
     int& is_last = sm.is_last;
 
-    // Let the next kernel in the stream begin its prologue. This kernel's own prologue (positions,
-    // block table: step metadata that no kernel writes) runs before it waits for its predecessor,
-    // which wrote the queries and this step's keys and values.
-    sync.start();
+    // This kernel's own prologue (positions, block table: step metadata that no kernel writes) runs before it waits
+    // for its predecessor, which wrote the queries and this step's keys and values. The next kernel in the stream is
+    // let go only after that wait: released earlier, kernels pile up on the SMs, resident and waiting, in the way of
+    // the one that works.
+    if (!a.late_release) sync.start();
     int pos = positions[row];
     if (pos >= 0 && (pos >> page_shift) >= max_pages) {   // a position the block table does not reach: reported, and the
         if (tid == 0) atomicOr(status, GB_STATUS_BAD_POSITION);   // row is treated as padding (nothing is read)
@@ -148,6 +150,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     __nv_bfloat16* orow = out + (size_t)row * out_stride;
     if (pos < 0) {  // padding row
         sync.wait();
+        if (a.late_release) sync.start();
         if (sync.gave_up()) return;
         if (split == 0)
             for (int i = tid; i < G * HD; i += NTHREADS) orow[head0 * HD + i] = __float2bfloat16_rn(0.f);
@@ -197,6 +200,7 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
         sync.group_barrier();
     }
     sync.wait();   // the writes of the work before (q, this step's K/V) are visible from here
+    if (a.late_release) sync.start();
     if (sync.gave_up()) return;
     // Q as the A operand: rows g and g+8 are query heads head0+g and head0+g+8 (zero beyond G).
     uint32_t qf[KS][4];

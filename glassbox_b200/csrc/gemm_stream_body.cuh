@@ -41,6 +41,7 @@ struct StreamArgs {
     // a region to pull into L2 for a later kernel (its weights), or nullptr
     const unsigned char* prefetch;
     long long prefetch_bytes;
+    int late_release;         // let the next kernel in the stream go only after this one's own wait (else at its start)
 };
 
 __device__ __forceinline__ void ws_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -115,8 +116,8 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
     const int r = lane >> 2, t = lane & 3;
     const int M = a.M, N = a.N, K = a.K;
 
-    // let the next kernel in the stream start its own prologue
-    sync.start();
+
+    if (!a.late_release) sync.start();
 
     // a cluster shares one strip: block `crank` of `csize` takes k in [kbeg, kend)
     int csize = 1, crank = 0;
@@ -205,6 +206,7 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             }
         }
         sync.wait();   // everything below reads what earlier work wrote
+        if (a.late_release) sync.start();
         if (sync.gave_up()) return;
     }
 
