@@ -46,3 +46,12 @@ GB_EXPORT int gb_kv_prefetch(const void* kcache, const void* vcache, const int* 
                                                   window);
     return gb_check_launch("gb_kv_prefetch");
 }
+
+// A kernel that does nothing: a node of its own on a second stream (see GqaAttention.prefetch, which launches it where
+// a real prefetch does not pay).
+__global__ void stream_marker_kernel() {}
+
+GB_EXPORT int gb_stream_marker(cudaStream_t stream) {
+    stream_marker_kernel<<<1, 32, 0, stream>>>();
+    return gb_check_launch("gb_stream_marker");
+}

@@ -54,6 +54,7 @@ _SIGNATURES = {
     "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
                                 _P, _P],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
+    "gb_stream_marker": [_P],
     "gb_kv_prefetch": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _LL, _LL, _I, _I, _P],
     "gb_attention_prefill": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_attention_prefill_supported": [_I, _I, _I, _I],
@@ -752,6 +753,11 @@ def kv_prefetch(kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.
     _call("gb_kv_prefetch", _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1], _ptr(row_seq),
           _ptr(positions), positions.shape[0], nkv, page_size, kcache.shape[0], tile_bytes, int(window or 0),
           int(blocks_per_row), _stream())
+
+
+def stream_marker() -> None:
+    """An empty kernel on the current stream: a node of its own in a recorded step (see ``GqaAttention.prefetch``)."""
+    _call("gb_stream_marker", _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

@@ -76,10 +76,15 @@ class GqaAttention(Mixer):
         linear(ctx, att, self.params["wo"], residual, accumulate=True)
 
 
-    #: prefetch a layer's share of the cache into L2 only when it is small. Measured on a B200 (decode, context 4096, ms per
-    #: step with / without): 135M shapes batch 1 0.936 / 0.956, batch 8 (25 MB a layer) 1.174 / 1.192; 360M shapes batch 8
-    #: (42 MB a layer) 1.61 / 1.50: beyond some 30 MB the extra kernel and its edges in the graph cost more than they hide.
-    PREFETCH_MAX_BYTES = 32 << 20
+    #: Prefetch a layer's share of the cache into L2 only when it is small; above it the hook launches an empty kernel.
+    #: The hook runs on a second stream beside the feed-forward of the layer before: the step's graph then has a fork
+    #: after that layer's mixer and a join in front of this one. Measured on a B200 (decode, context 4096, ms per step
+    #: with the prefetch / with an empty kernel in its place / with no second stream at all): 135M shapes batch 1
+    #: (3 MB a layer) 0.628 / 0.632 / 0.684, batch 8 (25 MB) 0.735 / 0.713 / 0.779; with the empty kernel against
+    #: nothing: 360M batch 8 1.165 / 1.213, 1.7B batch 1 1.358 / 1.436, batch 8 2.854 / 2.905. Most of the gain
+    #: belongs to the fork and join themselves, not to the bytes moved (why a chain of kernels under programmatic
+    #: dependent launch runs faster with them has not been found out; it is kept because it is measured, at every size).
+    PREFETCH_MAX_BYTES = 8 << 20
 
     def prefetch(self, ctx, cache) -> None:
         if not ctx.decode_only or cache is None:
@@ -87,6 +92,7 @@ class GqaAttention(Mixer):
         n = ctx.n
         step_bytes = 2 * n * min(ctx.max_context, self.spec.window or ctx.max_context) * self.kvd * cache.k.element_size()
         if step_bytes > self.PREFETCH_MAX_BYTES:
+            kernels.stream_marker()
             return
         kernels.kv_prefetch(cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.nkv, self.hd,
                             cache.page_size, self.spec.window, blocks_per_row=max(1, 148 // max(n, 1)))
