@@ -634,19 +634,40 @@ def attention_decode_mma_supported(dtype: torch.dtype, nh: int, nkv: int, hd: in
             and bool(lib().gb_attention_decode_mma_supported(nh, nkv, hd)))
 
 
+DECODE_MMA_WAVE_SINGLE = 444        # blocks of the 16-key, four-warp variant that run at once: 148 SMs x 3
+DECODE_MMA_WAVE_BLOCKS = 410        # the same in clusters of 2 to 4 (measured: 410 fit, 432 do not)
+DECODE_MMA_BLOCK_US = 5.7           # a block's fixed cost, microseconds (measured)
+DECODE_MMA_KEY_US = 0.0147          # and its cost per key
+
+
 def decode_mma_plan(n: int, nkv: int, hd: int, max_context: int):
     """(splits, keys per warp iteration, warps per block) for the tensor-core decode kernel. A small batch needs
     many blocks per (row, kv head) to fill the GPU, but each block keeps at least 512 keys, below which the
     fixed cost of a block and of the merge outweighs the parallelism; where that leaves at most one block
     per SM, a block has eight warps instead of four, so that each warp walks through half as many keys (the
     splits are then rounded down: a second block of eight warps does not fit beside the first). A batch that
-    fills the GPU by itself takes the 16-key variant (three blocks per SM instead of two) and few splits.
+    fills the GPU by itself takes the 16-key variant (three blocks per SM instead of two) and the split count
+    whose waves of resident blocks are estimated to end soonest.
     Depends on the batch shape and the longest context the step allows, never on the data, so a captured
     graph can fix it."""
     pairs = max(n * nkv, 1)
     most = max(1, -(-max_context // 512))
     if hd == 64 and pairs >= 96:
-        return max(1, min(-(-296 // pairs), most)), 16, 4
+        # Blocks of the 16-key variant run three to an SM, in waves: all blocks of a wave take as long as one of them.
+        # A block costs about 5.7 us of start, merge and hand-over and 14.7 ns a key; a wave holds about 410 blocks
+        # (432 no longer fit one; without clusters, at one split, 416 still do: 71.3 us, 3 splits 92.0). The split count that this estimate likes best, among 1 to 4 (clusters of 5 and 7
+        # place badly), is the one measured best at context 4096 for 96 to 2,048 pairs, within 1 %: 128 pairs 3 splits
+        # 26.8 us (2: 34.6, 4: 37.3); 144 pairs 2 splits 35.6 (3: 45.6); 256 pairs 3 splits 51.6 (1: 66.1, 2: 66.3,
+        # 4: 57.7); 320 pairs 1 split 68.4 (2: 72.9, 4: 79.0); 512 pairs 3 splits 99.0 (1: 123.1, 4: 98.2); 2,048 pairs
+        # 1 split 338.7 (2: 354.7). (Filling two blocks per SM once, the rule before, took 2 splits at 256 pairs: a 1.7B
+        # decode step at batch 8 2.85 ms, with 3 splits 2.56 ms.)
+        best, best_cost = 1, None
+        for splits in range(1, min(4, most) + 1):
+            waves = -(-pairs * splits // (DECODE_MMA_WAVE_BLOCKS if splits > 1 else DECODE_MMA_WAVE_SINGLE))
+            cost = waves * (DECODE_MMA_BLOCK_US + DECODE_MMA_KEY_US * -(-max_context // splits))
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = splits, cost
+        return best, 16, 4
     if hd == 64 and pairs <= 74:
         # (measured at 9/3 heads, microseconds at context 4096 with 4 warps and the old split count against 8 warps:
         # batch 8 18.8 -> 12.4, batch 16 18.2 -> 15.1, batch 4 12.7 -> 11.3; eight warps want at least 256 keys a block

@@ -14,6 +14,8 @@ def test_decode_attention_plan_keeps_its_promises(nkv, context):
         splits, block_keys, warps = kernels.decode_mma_plan(rows, nkv, 64, context)
         assert splits >= 1 and warps in (4, 8) and block_keys in (0, 16)
         assert (splits, block_keys, warps) == kernels.decode_mma_plan(rows, nkv, 64, context)
+        if warps == 4 and block_keys == 16:
+            assert splits <= 4                                           # clusters of 5 and 7 place badly
         if warps == 8:
             assert rows * nkv * splits <= 148
             assert splits * warps <= 64
@@ -31,3 +33,9 @@ def test_decode_attention_plan_examples():
     assert kernels.decode_mma_plan(8, 3, 64, 4096) == (6, 16, 8)
     assert kernels.decode_mma_plan(16, 3, 64, 4096) == (3, 0, 8)        # 1,365 keys a block: 32 keys per iteration
     assert kernels.decode_mma_plan(64, 3, 64, 4096) == (2, 16, 4)
+    # large batches: the split count whose waves of resident blocks end soonest
+    assert kernels.decode_mma_plan(8, 32, 64, 4096) == (3, 16, 4)       # 256 pairs: 2 splits would leave a short second wave
+    assert kernels.decode_mma_plan(48, 3, 64, 4096) == (2, 16, 4)       # 144 pairs: 3 splits no longer fit one wave
+    assert kernels.decode_mma_plan(13, 32, 64, 4096) == (1, 16, 4)      # 416 pairs fit one wave by themselves
+    assert kernels.decode_mma_plan(64, 32, 64, 4096) == (1, 16, 4)
+    assert kernels.decode_mma_plan(64, 5, 64, 4096) == (1, 16, 4)

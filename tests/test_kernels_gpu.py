@@ -1014,7 +1014,7 @@ def test_decode_attention_at_the_benchmarked_context_lengths(dtype, nh, nkv, B, 
     out = torch.full((B, nh * hd), 7.0, device=DEV, dtype=dtype)
     if dtype == torch.bfloat16:
         splits, block_keys, warps = kernels.decode_mma_plan(B, nkv, hd, L)
-        for sp, bk, nw in {(splits, block_keys, warps), (1, 0, 4), (max(splits // 2, 1), 16, 4), (3, 0, 8), (1, 0, 8), (2, 16, 8)}:
+        for sp, bk, nw in {(splits, block_keys, warps), (1, 0, 4), (max(splits // 2, 1), 16, 4), (3, 16, 4), (3, 0, 8), (1, 0, 8), (2, 16, 8)}:
             kernels.attention_decode_mma(qd, out, k, v, tables, row_seq, positions, nh, nkv, hd, ps, hd ** -0.5, None, sp,
                                          torch.empty(B * nh * nw * sp * hd, device=DEV), torch.empty(B * nh * nw * sp * 2, device=DEV),
                                          torch.zeros(B * nkv, dtype=torch.int32, device=DEV), st, bk, nw)
