@@ -12,7 +12,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..cache.device import DeviceCache, PagedLayerView, StateLayerView
+from ..cache.device import DeviceCache, PagedLayerView
 
 
 @dataclass

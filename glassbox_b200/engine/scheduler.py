@@ -39,7 +39,6 @@ from typing import Callable, Deque, Dict, List, Optional, Sequence
 
 import numpy as np
 
-from ..cache.manager import OutOfPages
 from ..sampling.sampler import Sampler, SamplerConfig
 
 STOP, LENGTH, ABORTED = "stop", "length", "aborted"

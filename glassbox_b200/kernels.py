@@ -8,7 +8,6 @@ no library stand-in: if the shared library cannot be built or loaded, the first 
 from __future__ import annotations
 
 import ctypes
-import os
 import threading
 from typing import Optional
 

@@ -15,7 +15,7 @@ from typing import Dict
 
 import torch
 
-from .binding import ParamSpec, Stacked, Tied
+from .binding import ParamSpec, Tied
 from .safetensors_io import SafetensorsFile, WeightsError
 
 

@@ -4,7 +4,6 @@ import json
 import pytest
 
 from glassbox_b200.config import ConfigError, architecture_names, load_config, parse_config
-from glassbox_b200.models.llama import make_llama_raw_config
 
 from conftest import TINY, tiny_raw
 

@@ -6,7 +6,6 @@ import pytest
 import torch
 
 import glassbox_b200
-from glassbox_b200.config import parse_config
 from glassbox_b200.config.registry import get_architecture
 from glassbox_b200.engine.model import DecoderModel
 from glassbox_b200.weights import SafetensorsFile, WeightsError, load_parameters, random_tensors, write_safetensors

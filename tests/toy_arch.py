@@ -14,7 +14,6 @@ the same public calls a user would make, without touching the framework's files:
 These are test fixtures for the framework's interfaces, not models of anything.
 """
 from dataclasses import dataclass
-from typing import Optional
 
 import numpy as np
 import torch
