@@ -4,6 +4,8 @@ over operands that rotate through more memory than L2 holds.
     python -m glassbox_b200.microbench gemm_stream [135m|360m|1.7b ...]   weight-streaming GEMM, 1..64 rows
     python -m glassbox_b200.microbench gemm_tc                           tcgen05 GEMM against torch.matmul
     python -m glassbox_b200.microbench attention_decode [batch ...]      paged decode attention at context 4096
+    python -m glassbox_b200.microbench attention_splits HEADS KV_HEADS BATCH [CONTEXT]
+                                                                         the large-batch decode attention at 1 to 6 splits
     python -m glassbox_b200.microbench attention_prefill                 flash attention, one 2048-token prompt
     python -m glassbox_b200.microbench float32                           the 32-bit path's kernels: FMA GEMM, decode and rows attention
     python -m glassbox_b200.microbench small                             embedding, RMSNorm, rotation + cache write, SwiGLU, sampling
@@ -113,8 +115,9 @@ def bench_gemm_tc() -> None:
     kernels.check_status(status)
 
 
-def bench_attention_decode(batches) -> None:
-    nh, nkv, hd, ps, ctx = 9, 3, 64, 16, 4096
+def bench_attention_decode(batches, nh: int = 9, nkv: int = 3, ctx: int = 4096, sweep: bool = False) -> None:
+    """The planner's variant for each batch; with ``sweep`` the four-warp, 16-key variant at 1 to 6 splits as well."""
+    hd, ps = 64, 16
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     for m in batches or (1, 8, 64):
         per = ctx // ps
@@ -125,15 +128,16 @@ def bench_attention_decode(batches) -> None:
         pos = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
         q = torch.randn(m, nh * hd, device=DEV).bfloat16()
         o = torch.empty_like(q)
-        splits, block_keys, warps = kernels.decode_mma_plan(m, nkv, hd, ctx)
-        pa = torch.empty(m * nh * warps * splits * hd, device=DEV)
-        pm = torch.empty(m * nh * warps * splits * 2, device=DEV)
-        cn = torch.zeros(m * nkv, dtype=torch.int32, device=DEV)
-        t = graph_time(lambda: kernels.attention_decode_mma(q, o, kc, vc, tables, row_seq, pos, nh, nkv, hd, ps, hd ** -0.5,
-                                                            None, splits, pa, pm, cn, status, block_keys, warps))
-        nbytes = m * ctx * nkv * hd * 2 * 2
-        print(f"attention_decode_mma batch {m:3d} ctx {ctx} splits {splits} keys/iteration {block_keys or 32} warps {warps}: {t:7.1f} us "
-              f"{nbytes / t / 1e3:6.0f} GB/s", flush=True)
+        plans = [kernels.decode_mma_plan(m, nkv, hd, ctx)] + ([(s, 16, 4) for s in range(1, 7)] if sweep else [])
+        for splits, block_keys, warps in plans:
+            pa = torch.empty(m * nh * warps * splits * hd, device=DEV)
+            pm = torch.empty(m * nh * warps * splits * 2, device=DEV)
+            cn = torch.zeros(m * nkv, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.attention_decode_mma(q, o, kc, vc, tables, row_seq, pos, nh, nkv, hd, ps, hd ** -0.5,
+                                                                None, splits, pa, pm, cn, status, block_keys, warps))
+            nbytes = m * ctx * nkv * hd * 2 * 2
+            print(f"attention_decode_mma heads {nh}/{nkv} batch {m:3d} ctx {ctx} splits {splits} keys/iteration {block_keys or 32} "
+                  f"warps {warps}: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
     kernels.check_status(status)
 
 
@@ -340,7 +344,7 @@ def bench_layer_gemms(rows) -> None:
     kernels.check_status(st)
 
 
-CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_prefill", "float32", "small", "decode_program", "layer_gemms")
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms")
 
 
 def main(argv) -> int:
@@ -348,7 +352,7 @@ def main(argv) -> int:
     if "--once" in argv:
         ONCE = True
         argv = [a for a in argv if a != "--once"]
-    if not argv or argv[0] not in CASES:
+    if not argv or argv[0] not in CASES or (argv[0] == "attention_splits" and len(argv) < 4):
         print(__doc__)
         return 2
     torch.cuda.set_device(0)
@@ -359,6 +363,9 @@ def main(argv) -> int:
         bench_gemm_tc()
     elif argv[0] == "attention_decode":
         bench_attention_decode([int(x) for x in argv[1:]])
+    elif argv[0] == "attention_splits":
+        nh, nkv, m = (int(x) for x in argv[1:4])
+        bench_attention_decode([m], nh, nkv, int(argv[4]) if len(argv) > 4 else 4096, sweep=True)
     elif argv[0] == "float32":
         bench_float32()
     elif argv[0] == "small":
